@@ -1,0 +1,361 @@
+#!/usr/bin/env python
+"""Generate the golden fixtures in this directory from the reference itself.
+
+Run in a container that has the reference checkout (default
+``/root/reference``, override with ``TRIATTN_REFERENCE_ROOT``)::
+
+    python tests/golden/make_golden.py
+
+The reference is imported unmodified, on CPU, with three test-side shims:
+
+1. ``triattention.vllm.core.scoring.compute_scores_triton`` is replaced by the
+   reference's own ``compute_scores_pytorch`` applied to ``K.float()`` (the
+   selector calls the Triton entry unconditionally, selector_hf.py:59,314; the
+   Triton kernel upcasts K in-kernel, triton_scoring.py:263-264).
+2. ``TriAttentionConfig`` defaults to ``device='cpu'`` (core/config.py:85 says cuda).
+3. ``inv_freq`` is stored in the stats metadata so no model config is fetched.
+
+Each fixture stores the seeds/parameters that regenerate the inputs with
+``triattention_b200.synth`` plus a SHA-256 of those inputs, and the
+reference's outputs.  Tiny cases also store the inputs themselves.
+"""
+from __future__ import annotations
+
+import hashlib
+import json
+import os
+import sys
+import tempfile
+from pathlib import Path
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+REPO = HERE.parent.parent
+REF = Path(os.environ.get("TRIATTN_REFERENCE_ROOT", "/root/reference"))
+sys.dont_write_bytecode = True
+sys.path.insert(0, str(REPO))
+sys.path.insert(0, str(REF))
+
+from triattention_b200 import synth  # noqa: E402
+
+
+def sha(*tensors) -> str:
+    h = hashlib.sha256()
+    for t in tensors:
+        t = t.contiguous()
+        if t.dtype == torch.bfloat16:
+            t = t.view(torch.int16)
+        h.update(t.numpy().tobytes())
+    return h.hexdigest()
+
+
+def bf16_to_np(t: torch.Tensor) -> np.ndarray:
+    return t.contiguous().view(torch.int16).numpy().copy()
+
+
+def install_shims():
+    import triattention.vllm.core.scoring as ref_scoring
+    import triattention.vllm.core.config as ref_config
+
+    pyt = ref_scoring.compute_scores_pytorch
+
+    def _triton_shim(**kw):
+        kw.pop("trig_cache", None)
+        kw["key_states"] = kw["key_states"].float()
+        return pyt(**kw)
+
+    ref_scoring.compute_scores_triton = _triton_shim
+    orig_init = ref_config.TriAttentionConfig.__init__
+
+    def _init(self, *a, **kw):
+        kw.setdefault("device", torch.device("cpu"))
+        orig_init(self, *a, **kw)
+
+    ref_config.TriAttentionConfig.__init__ = _init
+    return ref_scoring, ref_config
+
+
+# --------------------------------------------------------------------------
+# Case builders (shared with the tests through the stored parameters)
+# --------------------------------------------------------------------------
+
+def build_paged_case(p: dict):
+    """Regenerate (stats, layer caches, block ids) from the parameter dict ``p``."""
+    gen = torch.Generator().manual_seed(int(p["seed"]))
+    inv_freq = synth.rope_inv_freq(p["head_dim"], p["theta"], p.get("llama3"))
+    stats = synth.make_stats(p["num_layers"], p["num_q_heads"], p["head_dim"], inv_freq, gen,
+                             rope_style=p.get("rope_style", "half"))
+    T = p["total_tokens"]
+    bs = p["block_size"]
+    nblk = (T + bs - 1) // bs
+    nb_total = nblk + p.get("spare_blocks", 5)
+    if p.get("consecutive_blocks", False):
+        block_ids = list(range(2, 2 + nblk))
+        nb_total = max(nb_total, 2 + nblk)
+    else:
+        block_ids = synth.random_block_ids(nblk, nb_total, gen)
+    caches = []
+    for _l in range(p["num_layers"]):
+        cache = synth.make_paged_layer(nb_total, bs, p["num_kv_heads"], p["head_dim"], kv_axis=p["kv_axis"])
+        k = synth.make_rotated_keys(p["num_kv_heads"], T, p["head_dim"], inv_freq, gen,
+                                    rope_style=p.get("rope_style", "half"))
+        v = synth.make_values(p["num_kv_heads"], T, p["head_dim"], gen)
+        synth.write_tokens_to_paged(cache, p["kv_axis"], block_ids, bs, k, v)
+        caches.append(cache)
+    return stats, caches, block_ids
+
+
+def runtime_config(ref_runtime_config, stats_path, p):
+    cfg = ref_runtime_config.TriAttentionRuntimeConfig(
+        kv_budget=p["budget"],
+        window_size=p["window"],
+        sparse_stats_path=Path(stats_path),
+        sparse_score_aggregation=p.get("aggregation", "mean"),
+        sparse_normalize_scores=p.get("normalize", True),
+        pruning_mode=p.get("pruning_mode", "per_head"),
+        per_head_selection_semantics=p.get("semantics", "hf_aligned_global_per_head"),
+        layer_perhead_aggregation=p.get("layer_perhead_aggregation", "max"),
+        allow_per_layer_mode=p.get("pruning_mode", "per_head") == "per_layer",
+        disable_mlr=p.get("disable_mlr", False),
+        disable_trig=p.get("disable_trig", False),
+        protect_prefill=p.get("protect_prefill", False),
+    )
+    cfg.validate()
+    return cfg
+
+
+def gen_score_cases(ref_scoring, ref_config, out: dict):
+    """Direct calls of compute_scores_pytorch on K.float() (scoring.py:207-362)."""
+    gen = torch.Generator().manual_seed(synth.seed_for(90, 0))
+    H, T, D = 4, 100, 128
+    inv_freq = synth.rope_inv_freq(D, 1e6)
+    stats = synth.make_stats(1, H, D, inv_freq, gen)
+    fs = 0.5 + torch.rand((H, D // 2), generator=gen)
+    offsets = torch.tensor([float(2 ** i) for i in range(17)])
+    variants = [
+        dict(aggregation="mean", disable_mlr=False, disable_trig=False, rope_style="half", round_start=100),
+        dict(aggregation="max", disable_mlr=False, disable_trig=False, rope_style="half", round_start=100),
+        dict(aggregation="mean", disable_mlr=True, disable_trig=False, rope_style="half", round_start=33000),
+        dict(aggregation="mean", disable_mlr=False, disable_trig=True, rope_style="half", round_start=100),
+        dict(aggregation="mean", disable_mlr=False, disable_trig=False, rope_style="interleaved", round_start=100001),
+        dict(aggregation="max", disable_mlr=True, disable_trig=False, rope_style="interleaved", round_start=7),
+    ]
+    arrays = {
+        "q_mean_real": stats.q_mean_real[0].numpy(),
+        "q_mean_imag": stats.q_mean_imag[0].numpy(),
+        "q_abs_mean": stats.q_abs_mean[0].numpy(),
+        "freq_scale_sq": fs.numpy(),
+        "omega": inv_freq.numpy(),
+        "offsets": offsets.numpy(),
+    }
+    meta = []
+    for i, v in enumerate(variants):
+        k = synth.make_rotated_keys(H, T, D, inv_freq, gen, rope_style=v["rope_style"])  # [T,H,D]
+        keys = k.permute(1, 0, 2).unsqueeze(0).contiguous()  # [1,H,T,D]
+        cfg = ref_config.TriAttentionConfig(
+            score_aggregation=v["aggregation"], disable_mlr=v["disable_mlr"], disable_trig=v["disable_trig"],
+            rope_style=v["rope_style"], pruning_mode="per_head",
+        )
+        head_stats = {
+            "q_mean_complex": torch.stack([stats.q_mean_real[0], stats.q_mean_imag[0]], dim=-1),
+            "q_abs_mean": stats.q_abs_mean[0],
+        }
+        ref = ref_scoring.compute_scores_pytorch(
+            key_states=keys.float(), cache_positions=None, head_stats=head_stats, omega=inv_freq,
+            offsets=offsets, freq_scale_sq=fs, config=cfg, round_start=v["round_start"],
+        )
+        ref_bf16 = ref_scoring.compute_scores_pytorch(
+            key_states=keys, cache_positions=None, head_stats=head_stats, omega=inv_freq,
+            offsets=offsets, freq_scale_sq=fs, config=cfg, round_start=v["round_start"],
+        )
+        arrays[f"keys_{i}"] = bf16_to_np(keys)
+        arrays[f"scores_{i}"] = ref.numpy()
+        arrays[f"scores_bf16k_{i}"] = ref_bf16.float().numpy()
+        meta.append(v)
+    np.savez_compressed(HERE / "score_cases.npz", **arrays)
+    out["score_cases"] = {"file": "score_cases.npz", "variants": meta, "shape": [1, H, T, D]}
+
+
+def gen_selector_cases(out: dict):
+    """Group selector + per-layer selectors + compaction through the reference's own runtime code."""
+    import triattention.vllm.runtime.config as ref_runtime_config
+    from triattention.vllm.runtime.selector_hf import build_triattention_selector
+    from triattention.vllm.runtime.kv_compaction import (
+        compact_request_kv_in_place,
+        compact_request_kv_in_place_per_head,
+        register_kv_layout_axis_hint,
+    )
+
+    cases = {
+        # tiny: inputs stored in the fixture
+        "tiny_group": dict(seed=synth.seed_for(91, 0), num_layers=2, num_q_heads=8, num_kv_heads=2, head_dim=128,
+                           theta=1e6, total_tokens=200, block_size=16, kv_axis=0, budget=64, window=16,
+                           round_start=200, spare_blocks=2, store_inputs=True),
+        # chunked (>4096 tokens), K/V axis 1, random block order
+        "chunked_group": dict(seed=synth.seed_for(91, 1), num_layers=3, num_q_heads=8, num_kv_heads=2, head_dim=128,
+                              theta=1e6, total_tokens=4500, block_size=16, kv_axis=1, budget=1024, window=128,
+                              round_start=4500),
+        # BASELINE config-0 head shapes, shorter, round_start != T, consecutive blocks (view fast path)
+        "c0_like": dict(seed=synth.seed_for(91, 2), num_layers=1, num_q_heads=32, num_kv_heads=8, head_dim=128,
+                        theta=1e6, total_tokens=2100, block_size=16, kv_axis=0, budget=512, window=128,
+                        round_start=9000, consecutive_blocks=True),
+        # llama3-scaled frequencies, ragged last block, no normalisation
+        "llama3_nonorm": dict(seed=synth.seed_for(91, 3), num_layers=2, num_q_heads=8, num_kv_heads=4, head_dim=128,
+                              theta=5e5, llama3=dict(factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                                     original_max_position_embeddings=8192),
+                              total_tokens=1003, block_size=16, kv_axis=0, budget=256, window=32, round_start=20000,
+                              normalize=False),
+        # max over offsets, prefill protection
+        "max_agg_prefill": dict(seed=synth.seed_for(91, 4), num_layers=2, num_q_heads=4, num_kv_heads=2, head_dim=128,
+                                theta=1e6, total_tokens=700, block_size=16, kv_axis=0, budget=200, window=16,
+                                round_start=700, aggregation="max", protect_prefill=True, prefill_len=40),
+        # head_dim 64, group 8
+        "d64_g8": dict(seed=synth.seed_for(91, 5), num_layers=2, num_q_heads=16, num_kv_heads=2, head_dim=64,
+                       theta=1.5e5, total_tokens=900, block_size=16, kv_axis=1, budget=300, window=64,
+                       round_start=1234),
+        # legacy per-layer selection (z-norm -> group max -> guards -> top-k per layer)
+        "legacy_layer_local": dict(seed=synth.seed_for(91, 6), num_layers=2, num_q_heads=8, num_kv_heads=2,
+                                   head_dim=128, theta=1e6, total_tokens=640, block_size=16, kv_axis=0, budget=128,
+                                   window=16, round_start=640, semantics="legacy_layer_local"),
+        # shared keep set: max over heads (opt-in per_layer mode)
+        "per_layer_shared": dict(seed=synth.seed_for(91, 7), num_layers=2, num_q_heads=8, num_kv_heads=2,
+                                 head_dim=128, theta=1e6, total_tokens=640, block_size=16, kv_axis=0, budget=128,
+                                 window=16, round_start=640, pruning_mode="per_layer"),
+        # per_layer_per_head with mean over the GQA group
+        "plph_mean": dict(seed=synth.seed_for(91, 8), num_layers=2, num_q_heads=8, num_kv_heads=2, head_dim=128,
+                          theta=1e6, total_tokens=640, block_size=16, kv_axis=0, budget=128, window=16,
+                          round_start=640, pruning_mode="per_layer_per_head", layer_perhead_aggregation="mean"),
+    }
+    arrays = {}
+    with tempfile.TemporaryDirectory() as td:
+        for name, p in cases.items():
+            stats, caches, block_ids = build_paged_case(p)
+            stats_path = Path(td) / f"{name}.pt"
+            synth.save_stats_pt(stats, stats_path)
+            cfg = runtime_config(ref_runtime_config, stats_path, p)
+            sel_layer, sel_group, status = build_triattention_selector(cfg)
+            assert status == "enabled", status
+            for c in caches:
+                if int(c.shape[0]) == 2 and int(c.shape[1]) == 2:
+                    register_kv_layout_axis_hint(c, p["kv_axis"])
+            T, bs = p["total_tokens"], p["block_size"]
+            kw = dict(total_tokens=T, prefill_len=p.get("prefill_len", 0),
+                      protect_prefill=p.get("protect_prefill", False), round_start=p["round_start"],
+                      budget_total=min(p["budget"], T))
+            p["input_sha256"] = sha(stats.q_mean_real, stats.q_mean_imag, stats.q_abs_mean, *caches)
+            p["block_ids"] = block_ids
+            group_mode = (p.get("pruning_mode", "per_head") == "per_head"
+                          and p.get("semantics", "hf_aligned_global_per_head") == "hf_aligned_global_per_head")
+            if group_mode:
+                def _iter():
+                    for l, c in enumerate(caches):
+                        yield l, c, block_ids, bs
+                res = sel_group(layer_inputs=None, layer_input_iter=None, layer_kv_iter=_iter, **kw)
+                assert res["mode"] == "per_head"
+                keep = res["indices"]
+                arrays[f"{name}/keep"] = keep.numpy().astype(np.int32)
+                keeps = [keep] * len(caches)
+                modes = ["per_head"] * len(caches)
+            else:
+                keeps, modes = [], []
+                for l, c in enumerate(caches):
+                    res = sel_layer(keys_dense=None, kv_cache=c, block_ids=torch.as_tensor(block_ids),
+                                    block_size=bs, layer_idx=l, **kw)
+                    keeps.append(torch.as_tensor(res["indices"]))
+                    modes.append(res["mode"])
+                    arrays[f"{name}/keep_l{l}"] = keeps[-1].numpy().astype(np.int32)
+            p["modes"] = modes
+            # compaction through the reference (preserve_dropped_tokens=True, as layout_engine.py:71-80 forces)
+            if p.get("store_inputs"):
+                for l, c in enumerate(caches):
+                    arrays[f"{name}/cache_in_l{l}"] = bf16_to_np(c)
+                arrays[f"{name}/q_mean_real"] = stats.q_mean_real.numpy()
+                arrays[f"{name}/q_mean_imag"] = stats.q_mean_imag.numpy()
+                arrays[f"{name}/q_abs_mean"] = stats.q_abs_mean.numpy()
+                arrays[f"{name}/inv_freq"] = stats.inv_freq.numpy()
+            out_hashes = []
+            for l, c in enumerate(caches):
+                bt = torch.as_tensor(block_ids, dtype=torch.long)
+                if modes[l] == "per_head":
+                    n = compact_request_kv_in_place_per_head(
+                        kv_cache=c, block_ids=bt, block_size=bs, keep_token_indices_per_head=keeps[l],
+                        total_tokens=T, preserve_dropped_tokens=True)
+                else:
+                    n = compact_request_kv_in_place(
+                        kv_cache=c, block_ids=bt, block_size=bs, keep_token_indices=keeps[l],
+                        total_tokens=T, preserve_dropped_tokens=True)
+                assert n == min(p["budget"], T)
+                out_hashes.append(sha(c))
+                if p.get("store_inputs"):
+                    arrays[f"{name}/cache_out_l{l}"] = bf16_to_np(c)
+            p["cache_out_sha256"] = out_hashes
+    np.savez_compressed(HERE / "selector_cases.npz", **arrays)
+    out["selector_cases"] = {"file": "selector_cases.npz", "cases": cases}
+
+
+def gen_real_stats_case(out: dict):
+    """Two layers of the shipped Qwen3-8B statistics as a non-synthetic stats source."""
+    import triattention.vllm.runtime.config as ref_runtime_config
+    from triattention.vllm.runtime.selector_hf import build_triattention_selector
+
+    src = REF / "triattention/calibration/for_aime25_experiment/qwen3_8b.pt"
+    payload = torch.load(src, map_location="cpu", weights_only=False)
+    L, H, D = 2, 32, 128
+    qr = torch.stack([torch.stack([payload["stats"][f"layer{l:02d}_head{h:02d}"]["q_mean_real"] for h in range(H)])
+                      for l in range(L)]).float()
+    qi = torch.stack([torch.stack([payload["stats"][f"layer{l:02d}_head{h:02d}"]["q_mean_imag"] for h in range(H)])
+                      for l in range(L)]).float()
+    qa = torch.stack([torch.stack([payload["stats"][f"layer{l:02d}_head{h:02d}"]["q_abs_mean"] for h in range(H)])
+                      for l in range(L)]).float()
+    inv_freq = synth.rope_inv_freq(D, 1e6)
+    stats = synth.SyntheticStats(qr, qi, qa, inv_freq, D, "half")
+    p = dict(seed=synth.seed_for(92, 0), num_layers=L, num_q_heads=H, num_kv_heads=8, head_dim=D, theta=1e6,
+             total_tokens=1500, block_size=16, kv_axis=0, budget=512, window=128, round_start=1500)
+    gen = torch.Generator().manual_seed(p["seed"])
+    T, bs = p["total_tokens"], p["block_size"]
+    nblk = (T + bs - 1) // bs
+    block_ids = synth.random_block_ids(nblk, nblk + 7, gen)
+    caches = []
+    for _l in range(L):
+        cache = synth.make_paged_layer(nblk + 7, bs, 8, D, kv_axis=0)
+        k = synth.make_rotated_keys(8, T, D, inv_freq, gen)
+        v = synth.make_values(8, T, D, gen)
+        synth.write_tokens_to_paged(cache, 0, block_ids, bs, k, v)
+        caches.append(cache)
+    with tempfile.TemporaryDirectory() as td:
+        sp = Path(td) / "real.pt"
+        synth.save_stats_pt(stats, sp)
+        cfg = runtime_config(ref_runtime_config, sp, p)
+        _, sel_group, status = build_triattention_selector(cfg)
+        assert status == "enabled"
+
+        def _iter():
+            for l, c in enumerate(caches):
+                yield l, c, block_ids, bs
+        res = sel_group(layer_inputs=None, layer_input_iter=None, layer_kv_iter=_iter, total_tokens=T,
+                        prefill_len=0, protect_prefill=False, round_start=p["round_start"], budget_total=p["budget"])
+    p["block_ids"] = block_ids
+    p["input_sha256"] = sha(*caches)
+    np.savez_compressed(
+        HERE / "real_stats_case.npz",
+        q_mean_real=qr.numpy(), q_mean_imag=qi.numpy(), q_abs_mean=qa.numpy(), inv_freq=inv_freq.numpy(),
+        keep=res["indices"].numpy().astype(np.int32),
+    )
+    out["real_stats_case"] = {"file": "real_stats_case.npz", "params": p,
+                              "source": "layers 0-1 of triattention/calibration/for_aime25_experiment/qwen3_8b.pt"}
+
+
+def main():
+    ref_scoring, ref_config = install_shims()
+    out = {"torch": torch.__version__, "reference_root": str(REF)}
+    gen_score_cases(ref_scoring, ref_config, out)
+    gen_selector_cases(out)
+    gen_real_stats_case(out)
+    (HERE / "manifest.json").write_text(json.dumps(out, indent=1, sort_keys=True))
+    print("wrote", [p.name for p in HERE.iterdir()])
+
+
+if __name__ == "__main__":
+    main()
