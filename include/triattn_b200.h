@@ -1,0 +1,216 @@
+/*
+ * triattn_b200.h - C ABI of libtriattn_b200.so: TriAttention runtime KV compression
+ * (score -> select -> compact on a paged bf16 KV cache) for NVIDIA B200 (sm_100a).
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless its comment says "host";
+ *   - every function enqueues work on `stream` (a cudaStream_t passed as void*) and
+ *     returns without synchronising; it allocates nothing and frees nothing;
+ *   - the return value is a triattn_status; kernels never trap: bad metadata seen on
+ *     the device (block id out of range, keep index out of range, a bounded wait that
+ *     ran out) sets bits in the caller's `device_status` word (may be NULL) and the
+ *     offending element is skipped;
+ *   - strides are in ELEMENTS (bf16) unless named *_bytes.
+ *
+ * Each entry point names the function of the reference implementation
+ * (WeianMao/triattention, paths relative to that project) whose work it replaces.
+ */
+#ifndef TRIATTN_B200_H
+#define TRIATTN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TRIATTN_ABI_VERSION 1
+
+typedef enum triattn_status {
+  TRIATTN_OK = 0,
+  TRIATTN_ERR_INVALID_ARGUMENT = 1,   /* NULL pointer, non-positive size, inconsistent sizes      */
+  TRIATTN_ERR_UNSUPPORTED_SHAPE = 2,  /* head_dim / group size / block geometry outside the build */
+  TRIATTN_ERR_MISALIGNED = 3,         /* base pointer or stride breaks the 16-byte copy rule      */
+  TRIATTN_ERR_WORKSPACE_TOO_SMALL = 4,
+  TRIATTN_ERR_CUDA = 5,               /* a CUDA runtime call or launch failed                     */
+  TRIATTN_ERR_LIMIT_EXCEEDED = 6      /* size beyond a fixed maximum of a no-allocation entry     */
+} triattn_status;
+
+/* bits of the device status word */
+#define TRIATTN_DEV_BAD_BLOCK_ID   0x1u  /* block_table entry outside [0, num_blocks)          */
+#define TRIATTN_DEV_BAD_KEEP_INDEX 0x2u  /* keep index outside [0, seq_len) or not ascending   */
+#define TRIATTN_DEV_WAIT_TIMEOUT   0x4u  /* a bounded wait on an async copy ran out            */
+#define TRIATTN_DEV_BAD_LENGTH     0x8u  /* seq_len exceeds the request's block-table capacity */
+
+typedef enum triattn_offset_agg { TRIATTN_OFFSETS_MEAN = 0, TRIATTN_OFFSETS_MAX = 1 } triattn_offset_agg;
+typedef enum triattn_reduce { TRIATTN_REDUCE_NONE = 0, TRIATTN_REDUCE_MEAN = 1, TRIATTN_REDUCE_MAX = 2 } triattn_reduce;
+
+#define TRIATTN_FLAG_DISABLE_MLR  0x1  /* magnitude coefficient = q_abs_mean (scoring.py:346-348) */
+#define TRIATTN_FLAG_DISABLE_TRIG 0x2  /* drop the trigonometric series (scoring.py:321-329)      */
+
+/*
+ * Geometry of one worker's paged KV cache as the kernels see it.  One K (and one V)
+ * base pointer per layer; inside a layer, element (block, token, head, d) lives at
+ * block*block_stride + token*token_stride + head*head_stride + d.  Covers vLLM's
+ * [2, nb, bs, H, D] and [nb, 2, bs, H, D] tensors in NHD or HND stride order
+ * (kv_compaction.py:94-117 _split_kv_axes).  The K region of a block must be one dense
+ * run of block_size*num_kv_heads*head_dim elements.
+ */
+typedef struct triattn_paged_layout {
+  int32_t num_layers;          /* L: layers sharing the block table (one KV-cache group)    */
+  int32_t num_reqs;            /* B: requests compressed by this call                      */
+  int32_t num_kv_heads;        /* Hkv on this rank                                          */
+  int32_t group_size;          /* g: statistic (query) heads per KV head                    */
+  int32_t head_dim;            /* D (64 or 128 for the fast scorer)                         */
+  int32_t block_size;          /* tokens per cache block                                    */
+  int32_t num_blocks;          /* blocks in the cache (bound for block_table entries)       */
+  int32_t max_blocks_per_req;  /* row pitch of block_table                                  */
+  int64_t block_stride;
+  int64_t token_stride;
+  int64_t head_stride;
+  int32_t rope_interleaved;    /* 0: [r0..,i0..] "half" layout, 1: [r0,i0,r1,i1,..]         */
+  int32_t reserved;
+} triattn_paged_layout;
+
+/* ABI version of the loaded library (== TRIATTN_ABI_VERSION it was built with). */
+int triattn_abi_version(void);
+
+/* Static, human-readable text for a triattn_status. */
+const char* triattn_status_string(int status);
+
+/* Query-head slots per KV head in the raw-score layout: group_size rounded up to 1, 2, 4 or 8
+ * (0 if group_size is unsupported by the fast scorer, i.e. > 8). */
+int triattn_padded_group(int group_size);
+
+/* Number of weight rows per (layer, request, query head): 3 for MEAN (w_re, w_im, w_mag),
+ * 2*num_offsets + 1 for MAX. */
+int triattn_weight_rows(int offset_agg, int num_offsets);
+
+/* Floats of scratch triattn_prep_weights needs. */
+size_t triattn_prep_scratch_floats(int num_reqs, int num_freqs, int num_offsets, int offset_agg);
+
+/*
+ * Fold the calibrated query statistics and the future-offset phases of each request into
+ * per-(layer, request, query head) weight rows, so that a key's score is a dot product:
+ *   MEAN: s = sum_f k_re*w_re + k_im*w_im + |k|*w_mag, with
+ *         w_re = fs*(q_re*C - q_im*S), w_im = fs*(q_im*C + q_re*S), C/S = mean over offsets of
+ *         cos/sin(fl32(round_start+offset)*omega_f), w_mag = (q_abs - sqrt(q_re^2+q_im^2+1e-8))*fs;
+ *   MAX : one (w_re, w_im) row pair per offset and one w_mag row.
+ * Replaces the per-call statistics handling of compute_scores_pytorch
+ * (triattention/vllm/core/scoring.py:258-271, :313-332, :346-356) and the trig tables of
+ * triattention/vllm/core/kernels/triton_scoring.py:38-122.
+ *   q_mean_real/q_mean_imag/q_abs_mean/freq_scale_sq : [L, Hq, F] fp32
+ *   omega [F], offsets [num_offsets] fp32; round_start [B] int32
+ *   weights_out : [L, B, Hq, triattn_weight_rows(), F] fp32
+ */
+int triattn_prep_weights(const float* q_mean_real, const float* q_mean_imag, const float* q_abs_mean,
+                         const float* freq_scale_sq, const float* omega, const float* offsets,
+                         const int32_t* round_start, int num_layers, int num_reqs, int num_q_heads,
+                         int num_freqs, int num_offsets, int offset_agg, int flags,
+                         float* scratch, float* weights_out, void* stream);
+
+/*
+ * Score every cached key of every (layer, request, KV head) against the g query heads of its
+ * group: streams each cache block once with bulk async copies into shared memory and writes
+ *   raw_scores [L, B, Hkv, t_pad, Gp] fp32 (Gp = triattn_padded_group(g); slot q of token t is
+ *              query head kvh*g + q; t_pad = max_blocks_per_req*block_size)
+ *   moments    [L, B, Hkv*g, 2] fp64: sum and sum of squares over the request's tokens
+ *              (zeroed by this call).
+ * Replaces gather_request_k_dense_range (triattention/vllm/runtime/kv_compaction.py:322-352),
+ * the repeat_interleave expansion and scorer call (triattention/vllm/runtime/selector_hf.py:299-328),
+ * the Triton kernels (triattention/vllm/core/kernels/triton_scoring.py:160-490) and the moment
+ * accumulation (selector_hf.py:884-894).
+ *   k_layer_ptrs : [L] device array of per-layer K base pointers (bf16)
+ *   block_table  : [B, max_blocks_per_req] int32; seq_lens : [B] int32
+ *   weights      : output of triattn_prep_weights with the same offset_agg / num_offsets
+ */
+int triattn_score_paged(const triattn_paged_layout* layout /* host */, const void* const* k_layer_ptrs,
+                        const int32_t* block_table, const int32_t* seq_lens, const float* weights,
+                        int offset_agg, int num_offsets, float* raw_scores, double* moments,
+                        uint32_t* device_status, void* stream);
+
+/*
+ * Turn raw scores into the scores the top-k runs on: z-normalise per (layer, query head) with the
+ * unbiased streaming variance (sigma < 1e-8 -> 1), force +inf on the last `window` tokens and on
+ * tokens < prefill_lens[b] (prefill_lens may be NULL), reduce the g query heads of each KV head
+ * (group_reduce: MAX or MEAN), optionally the KV heads (head_reduce: NONE or MAX) and the layers
+ * (layer_reduce: NONE, MEAN, MAX).
+ *   scores_out : [Lo, B, Ho, t_pad] fp32, Lo = 1 if layer_reduce != NONE else L,
+ *                Ho = 1 if head_reduce != NONE else Hkv.
+ * Replaces selector_hf.py:896-913 (mean/std), :916-989 (normalise, guards, group max, layer mean)
+ * and, with layer_reduce NONE, the per-layer path :584-602 / :636-637.
+ */
+int triattn_finalize_scores(const triattn_paged_layout* layout /* host */, const float* raw_scores,
+                            const double* moments, const int32_t* seq_lens, const int32_t* prefill_lens,
+                            int window, int normalize, int group_reduce, int head_reduce, int layer_reduce,
+                            float* mean_std_scratch /* [L,B,Hkv*g,2] fp32 */, float* scores_out, void* stream);
+
+/*
+ * Per-row top-k with deterministic lowest-index tie-break; indices come out ascending.
+ * Row r belongs to request b = (r / rows_per_req_inner) % num_reqs, has seq_lens[b] valid scores and
+ * keeps keep_counts[b] of them (clamped to the row length).
+ *   scores : [num_rows, row_stride] fp32;  keep_out : [num_rows, keep_pitch] int32 (tail filled with -1)
+ * Replaces the chunked torch.topk / merge / torch.sort of selector_hf.py:990-1025 (and :604-677, :721-747).
+ */
+int triattn_select_topk(const float* scores, int num_rows, int64_t row_stride, const int32_t* seq_lens,
+                        const int32_t* keep_counts, int num_reqs, int rows_per_req_inner,
+                        int32_t* keep_out, int keep_pitch, uint32_t* device_status, void* stream);
+
+/*
+ * In-place compaction of K and V: for every (layer, request, KV head) move token keep[r] to slot r,
+ * r < keep_counts[b], inside the request's own blocks.  The keep rows must be strictly ascending.
+ * Row used for (layer l, request b, head h) is keep + l*keep_layer_stride + b*keep_req_stride +
+ * h*keep_head_stride (a stride of 0 shares the row: 0 layer stride = one keep set for all layers,
+ * 0 head stride = the "shared" mode).  Slots >= keep_counts[b] are left untouched.
+ * Replaces compact_request_kv_in_place_per_head (triattention/vllm/runtime/kv_compaction.py:461-599)
+ * and compact_request_kv_in_place (:355-458) for the kept prefix.
+ */
+int triattn_compact_paged(const triattn_paged_layout* layout /* host */, void* const* k_layer_ptrs,
+                          void* const* v_layer_ptrs, const int32_t* block_table, const int32_t* seq_lens,
+                          const int32_t* keep, int64_t keep_layer_stride, int64_t keep_req_stride,
+                          int64_t keep_head_stride, const int32_t* keep_counts, uint32_t* device_status,
+                          void* stream);
+
+/* Bytes of scratch triattn_compact_paged_preserve needs when no request drops more than
+ * max_dropped_rows = max_b (seq_lens[b] - keep_counts[b]) tokens. */
+size_t triattn_compact_preserve_scratch_bytes(const triattn_paged_layout* layout /* host */, int max_dropped_rows);
+
+/*
+ * Same as triattn_compact_paged but additionally writes the dropped tokens, in ascending order,
+ * to slots keep_counts[b] .. seq_lens[b]-1, i.e. the full [kept..., dropped...] permutation of
+ * kv_compaction.py:518-546 (preserve_dropped_tokens=True).  Uses `scratch` to stage dropped rows.
+ */
+int triattn_compact_paged_preserve(const triattn_paged_layout* layout /* host */, void* const* k_layer_ptrs,
+                                   void* const* v_layer_ptrs, const int32_t* block_table,
+                                   const int32_t* seq_lens, const int32_t* keep, int64_t keep_layer_stride,
+                                   int64_t keep_req_stride, int64_t keep_head_stride,
+                                   const int32_t* keep_counts, int max_dropped_rows, void* scratch,
+                                   size_t scratch_bytes, uint32_t* device_status, void* stream);
+
+/* Bytes of workspace triattn_compress_paged needs for this geometry. */
+size_t triattn_compress_workspace_bytes(const triattn_paged_layout* layout /* host */, int num_offsets,
+                                        int offset_agg, int keep_pitch);
+
+/*
+ * The whole default-mode step for a batch of requests in one call and no host synchronisation:
+ * prep -> score -> finalize (z-norm, window/prefill guards, group max, layer mean) -> per-KV-head
+ * top-k -> in-place compaction of every layer with the shared keep set.
+ * keep_out [B, Hkv, keep_pitch] int32 receives the ascending keep indices.
+ * Replaces, for all requests of a step at once, select_keep_indices_for_group
+ * (selector_hf.py:749-1033) followed by execute_group_compaction's per-layer calls
+ * (triattention/vllm/runtime/layout_engine.py:112-139).
+ */
+int triattn_compress_paged(const triattn_paged_layout* layout /* host */, void* const* k_layer_ptrs,
+                           void* const* v_layer_ptrs, const int32_t* block_table, const int32_t* seq_lens,
+                           const int32_t* round_start, const int32_t* prefill_lens,
+                           const int32_t* keep_counts, const float* q_mean_real, const float* q_mean_imag,
+                           const float* q_abs_mean, const float* freq_scale_sq, const float* omega,
+                           const float* offsets, int num_offsets, int offset_agg, int flags, int window,
+                           int normalize, int layer_reduce, void* workspace, size_t workspace_bytes,
+                           int32_t* keep_out, int keep_pitch, uint32_t* device_status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TRIATTN_B200_H */

@@ -1,0 +1,416 @@
+// C ABI of libtriattn_b200.so: argument validation, launch geometry and kernel launches.
+// No allocation, no synchronisation, no exceptions: every entry returns a triattn_status.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdint>
+
+#include "../../include/triattn_b200.h"
+#include "common.cuh"
+#include "compact.cuh"
+#include "finalize.cuh"
+#include "prep.cuh"
+#include "score.cuh"
+#include "select.cuh"
+
+using namespace triattn;
+
+namespace {
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+int check_launch() { return cudaGetLastError() == cudaSuccess ? TRIATTN_OK : TRIATTN_ERR_CUDA; }
+
+int validate_layout(const triattn_paged_layout* L) {
+  if (L == nullptr) return TRIATTN_ERR_INVALID_ARGUMENT;
+  if (L->num_layers <= 0 || L->num_reqs <= 0 || L->num_kv_heads <= 0 || L->group_size <= 0 || L->head_dim <= 0 ||
+      L->block_size <= 0 || L->num_blocks <= 0 || L->max_blocks_per_req <= 0)
+    return TRIATTN_ERR_INVALID_ARGUMENT;
+  if (L->head_dim % 8 != 0) return TRIATTN_ERR_UNSUPPORTED_SHAPE;
+  if (L->num_reqs > 65535 || L->num_layers > 65535) return TRIATTN_ERR_UNSUPPORTED_SHAPE;
+  if (L->block_stride % 8 != 0 || L->token_stride % 8 != 0 || L->head_stride % 8 != 0) return TRIATTN_ERR_MISALIGNED;
+  return TRIATTN_OK;
+}
+
+// true when the K region of a block is one dense run of bs*Hkv*D elements in NHD or HND order
+bool block_is_dense(const triattn_paged_layout* L) {
+  const int64_t D = L->head_dim, H = L->num_kv_heads, bs = L->block_size;
+  const bool nhd = L->head_stride == D && L->token_stride == H * D;
+  const bool hnd = L->token_stride == D && L->head_stride == bs * D;
+  return nhd || hnd || (H == 1 && L->token_stride == D) || (bs == 1 && L->head_stride == D);
+}
+
+template <int D, bool IL>
+int launch_score_fast(const ScoreParams& p, int gp, dim3 grid, size_t smem, cudaStream_t st) {
+#define TRIATTN_LAUNCH(GP)                                                                                    \
+  {                                                                                                           \
+    auto kern = score_paged_mean_kernel<D, GP, IL>;                                                           \
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)   \
+      return TRIATTN_ERR_CUDA;                                                                                \
+    kern<<<grid, kScoreThreads, smem, st>>>(p);                                                               \
+    return check_launch();                                                                                    \
+  }
+  switch (gp) {
+    case 1: TRIATTN_LAUNCH(1)
+    case 2: TRIATTN_LAUNCH(2)
+    case 4: TRIATTN_LAUNCH(4)
+    case 8: TRIATTN_LAUNCH(8)
+    default: return TRIATTN_ERR_UNSUPPORTED_SHAPE;
+  }
+#undef TRIATTN_LAUNCH
+}
+
+}  // namespace
+
+extern "C" {
+
+int triattn_abi_version(void) { return TRIATTN_ABI_VERSION; }
+
+const char* triattn_status_string(int status) {
+  switch (status) {
+    case TRIATTN_OK: return "ok";
+    case TRIATTN_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case TRIATTN_ERR_UNSUPPORTED_SHAPE: return "unsupported shape";
+    case TRIATTN_ERR_MISALIGNED: return "pointer or stride not 16-byte aligned";
+    case TRIATTN_ERR_WORKSPACE_TOO_SMALL: return "workspace too small";
+    case TRIATTN_ERR_CUDA: return "CUDA runtime error";
+    case TRIATTN_ERR_LIMIT_EXCEEDED: return "size exceeds the fixed maximum of this entry point";
+    default: return "unknown status";
+  }
+}
+
+int triattn_padded_group(int g) {
+  if (g <= 0 || g > 8) return 0;
+  int gp = 1;
+  while (gp < g) gp <<= 1;
+  return gp;
+}
+
+int triattn_weight_rows(int offset_agg, int num_offsets) {
+  return offset_agg == TRIATTN_OFFSETS_MAX ? 2 * num_offsets + 1 : 3;
+}
+
+size_t triattn_prep_scratch_floats(int num_reqs, int num_freqs, int num_offsets, int offset_agg) {
+  const size_t rows = offset_agg == TRIATTN_OFFSETS_MAX ? 2 * (size_t)num_offsets : 2;
+  return (size_t)num_reqs * rows * (size_t)num_freqs;
+}
+
+int triattn_prep_weights(const float* q_mean_real, const float* q_mean_imag, const float* q_abs_mean,
+                         const float* freq_scale_sq, const float* omega, const float* offsets,
+                         const int32_t* round_start, int num_layers, int num_reqs, int num_q_heads, int num_freqs,
+                         int num_offsets, int offset_agg, int flags, float* scratch, float* weights_out,
+                         void* stream) {
+  if (!q_mean_real || !q_mean_imag || !q_abs_mean || !freq_scale_sq || !omega || !offsets || !round_start ||
+      !scratch || !weights_out)
+    return TRIATTN_ERR_INVALID_ARGUMENT;
+  if (num_layers <= 0 || num_reqs <= 0 || num_q_heads <= 0 || num_freqs <= 0 || num_offsets <= 0)
+    return TRIATTN_ERR_INVALID_ARGUMENT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int agg_max = offset_agg == TRIATTN_OFFSETS_MAX ? 1 : 0;
+  trig_table_kernel<<<num_reqs, 64, 0, st>>>(omega, offsets, round_start, num_freqs, num_offsets, agg_max, scratch);
+  const size_t n = (size_t)num_layers * num_reqs * num_q_heads * num_freqs;
+  fold_weights_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(q_mean_real, q_mean_imag, q_abs_mean, freq_scale_sq,
+                                                                   scratch, num_layers, num_reqs, num_q_heads,
+                                                                   num_freqs, num_offsets, agg_max, flags, weights_out);
+  return check_launch();
+}
+
+int triattn_score_paged(const triattn_paged_layout* layout, const void* const* k_layer_ptrs,
+                        const int32_t* block_table, const int32_t* seq_lens, const float* weights, int offset_agg,
+                        int num_offsets, float* raw_scores, double* moments, uint32_t* device_status, void* stream) {
+  int rc = validate_layout(layout);
+  if (rc != TRIATTN_OK) return rc;
+  if (!k_layer_ptrs || !block_table || !seq_lens || !weights || !raw_scores || !moments)
+    return TRIATTN_ERR_INVALID_ARGUMENT;
+  const triattn_paged_layout& Y = *layout;
+  const int gp = triattn_padded_group(Y.group_size);
+  if (gp == 0) return TRIATTN_ERR_UNSUPPORTED_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int Hq = Y.num_kv_heads * Y.group_size;
+  if (cudaMemsetAsync(moments, 0, sizeof(double) * 2 * (size_t)Y.num_layers * Y.num_reqs * Hq, st) != cudaSuccess)
+    return TRIATTN_ERR_CUDA;
+
+  ScoreParams p{};
+  p.k_ptrs = k_layer_ptrs;
+  p.block_table = block_table;
+  p.seq_lens = seq_lens;
+  p.weights = weights;
+  p.raw = raw_scores;
+  p.moments = moments;
+  p.status = device_status;
+  p.L = Y.num_layers;
+  p.B = Y.num_reqs;
+  p.Hkv = Y.num_kv_heads;
+  p.g = Y.group_size;
+  p.bs = Y.block_size;
+  p.num_blocks = Y.num_blocks;
+  p.max_blocks = Y.max_blocks_per_req;
+  p.t_pad = Y.max_blocks_per_req * Y.block_size;
+  p.block_stride_bytes = (long long)Y.block_stride * 2;
+  p.token_stride = (int)Y.token_stride;
+  p.head_stride = (int)Y.head_stride;
+  p.num_offsets = num_offsets;
+  p.agg_max = offset_agg == TRIATTN_OFFSETS_MAX ? 1 : 0;
+
+  const long long block_bytes = (long long)Y.block_size * Y.num_kv_heads * Y.head_dim * 2;
+  const bool fast = !p.agg_max && (Y.head_dim == 64 || Y.head_dim == 128) && block_is_dense(layout) &&
+                    block_bytes <= 64 * 1024 && (p.block_stride_bytes % 16) == 0;
+  if (fast) {
+    constexpr int kNG = kScoreThreads / kLPK;
+    // cache blocks per stage: enough (head, token-batch) items to occupy all 16 key groups, stage <= 32 KB
+    const int nt = kLPK / gp;
+    const int items_per_block = Y.num_kv_heads * ((Y.block_size + nt - 1) / nt);
+    int mb = 1;
+    while (mb * items_per_block < 2 * kNG && (mb * 2) * block_bytes <= 32 * 1024) mb *= 2;
+    const long long stage_bytes = (long long)mb * block_bytes;
+    // two CTAs per SM share ~200 KB of shared memory; 8x128 keeps one CTA per SM
+    const long long budget = (gp * Y.head_dim >= 8 * 128) ? 160 * 1024 : 96 * 1024;
+    int stages = (int)std::min<long long>(4, budget / stage_bytes);
+    if (stages < 2) stages = 2;
+    p.block_bytes = (int)block_bytes;
+    p.mb = mb;
+    p.stages = stages;
+    const int max_tiles = (Y.max_blocks_per_req + mb - 1) / mb;
+    const long long total_tiles = (long long)max_tiles * Y.num_layers * Y.num_reqs;
+    const long long target_ctas = (long long)kSMs * 2 * 8;
+    // at least ~64 KB and at most ~2 MB of keys per CTA
+    const int min_tpc = (int)std::max<long long>(1, (64 * 1024) / stage_bytes);
+    const int max_tpc = (int)std::max<long long>(min_tpc, (2 * 1024 * 1024) / stage_bytes);
+    int tpc = (int)std::min<long long>(max_tpc, std::max<long long>(min_tpc, total_tiles / target_ctas));
+    p.tiles_per_cta = tpc;
+    dim3 grid((unsigned)((max_tiles + tpc - 1) / tpc), (unsigned)Y.num_layers, (unsigned)Y.num_reqs);
+    const size_t smem = (size_t)stages * stage_bytes;
+    if (Y.head_dim == 128)
+      return Y.rope_interleaved ? launch_score_fast<128, true>(p, gp, grid, smem, st)
+                                : launch_score_fast<128, false>(p, gp, grid, smem, st);
+    return Y.rope_interleaved ? launch_score_fast<64, true>(p, gp, grid, smem, st)
+                              : launch_score_fast<64, false>(p, gp, grid, smem, st);
+  }
+  dim3 grid((unsigned)((p.t_pad + 127) / 128), (unsigned)Y.num_kv_heads, (unsigned)(Y.num_layers * Y.num_reqs));
+  if ((long long)Y.num_layers * Y.num_reqs > 65535) return TRIATTN_ERR_UNSUPPORTED_SHAPE;
+  score_paged_generic_kernel<<<grid, 128, 0, st>>>(p, Y.head_dim, gp, Y.rope_interleaved);
+  return check_launch();
+}
+
+int triattn_finalize_scores(const triattn_paged_layout* layout, const float* raw_scores, const double* moments,
+                            const int32_t* seq_lens, const int32_t* prefill_lens, int window, int normalize,
+                            int group_reduce, int head_reduce, int layer_reduce, float* mean_std_scratch,
+                            float* scores_out, void* stream) {
+  int rc = validate_layout(layout);
+  if (rc != TRIATTN_OK) return rc;
+  if (!raw_scores || !moments || !seq_lens || !mean_std_scratch || !scores_out) return TRIATTN_ERR_INVALID_ARGUMENT;
+  if (group_reduce != TRIATTN_REDUCE_MAX && group_reduce != TRIATTN_REDUCE_MEAN) return TRIATTN_ERR_INVALID_ARGUMENT;
+  if (head_reduce != TRIATTN_REDUCE_NONE && head_reduce != TRIATTN_REDUCE_MAX) return TRIATTN_ERR_INVALID_ARGUMENT;
+  if (layer_reduce < TRIATTN_REDUCE_NONE || layer_reduce > TRIATTN_REDUCE_MAX) return TRIATTN_ERR_INVALID_ARGUMENT;
+  const triattn_paged_layout& Y = *layout;
+  const int gp = triattn_padded_group(Y.group_size);
+  if (gp == 0) return TRIATTN_ERR_UNSUPPORTED_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int Hq = Y.num_kv_heads * Y.group_size;
+  const int t_pad = Y.max_blocks_per_req * Y.block_size;
+  const int n = Y.num_layers * Y.num_reqs * Hq;
+  moments_to_mean_std_kernel<<<(n + 127) / 128, 128, 0, st>>>(moments, seq_lens, Y.num_layers, Y.num_reqs, Hq, t_pad,
+                                                             mean_std_scratch);
+  FinalizeParams p{};
+  p.raw = raw_scores;
+  p.mean_std = mean_std_scratch;
+  p.seq_lens = seq_lens;
+  p.prefill_lens = prefill_lens;
+  p.out = scores_out;
+  p.L = Y.num_layers;
+  p.B = Y.num_reqs;
+  p.Hkv = Y.num_kv_heads;
+  p.g = Y.group_size;
+  p.t_pad = t_pad;
+  p.window = window;
+  p.normalize = normalize;
+  p.group_reduce = group_reduce;
+  p.head_reduce = head_reduce;
+  p.layer_reduce = layer_reduce;
+  const int Ho = head_reduce != TRIATTN_REDUCE_NONE ? 1 : Y.num_kv_heads;
+  dim3 grid((unsigned)((t_pad + 255) / 256), (unsigned)Ho, (unsigned)Y.num_reqs);
+  switch (gp) {
+    case 1: finalize_scores_kernel<1><<<grid, 256, 0, st>>>(p); break;
+    case 2: finalize_scores_kernel<2><<<grid, 256, 0, st>>>(p); break;
+    case 4: finalize_scores_kernel<4><<<grid, 256, 0, st>>>(p); break;
+    default: finalize_scores_kernel<8><<<grid, 256, 0, st>>>(p); break;
+  }
+  return check_launch();
+}
+
+int triattn_select_topk(const float* scores, int num_rows, int64_t row_stride, const int32_t* seq_lens,
+                        const int32_t* keep_counts, int num_reqs, int rows_per_req_inner, int32_t* keep_out,
+                        int keep_pitch, uint32_t* device_status, void* stream) {
+  if (!scores || !seq_lens || !keep_counts || !keep_out) return TRIATTN_ERR_INVALID_ARGUMENT;
+  if (num_rows <= 0 || row_stride <= 0 || num_reqs <= 0 || rows_per_req_inner <= 0 || keep_pitch <= 0)
+    return TRIATTN_ERR_INVALID_ARGUMENT;
+  SelectParams p{};
+  p.scores = scores;
+  p.row_stride = row_stride;
+  p.seq_lens = seq_lens;
+  p.keep_counts = keep_counts;
+  p.num_reqs = num_reqs;
+  p.rows_inner = rows_per_req_inner;
+  p.keep_out = keep_out;
+  p.keep_pitch = keep_pitch;
+  p.status = device_status;
+  select_topk_kernel<<<num_rows, kSelectThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return check_launch();
+}
+
+static int compact_common(const triattn_paged_layout* layout, void* const* k_layer_ptrs, void* const* v_layer_ptrs,
+                          const int32_t* block_table, const int32_t* seq_lens, const int32_t* keep,
+                          int64_t keep_ls, int64_t keep_rs, int64_t keep_hs, const int32_t* keep_counts,
+                          void* scratch, long long scratch_stream_bytes, int scratch_rows, bool preserve,
+                          uint32_t* device_status, void* stream) {
+  int rc = validate_layout(layout);
+  if (rc != TRIATTN_OK) return rc;
+  if (!k_layer_ptrs || !v_layer_ptrs || !block_table || !seq_lens || !keep || !keep_counts)
+    return TRIATTN_ERR_INVALID_ARGUMENT;
+  const triattn_paged_layout& Y = *layout;
+  const int row_bytes = Y.head_dim * 2;
+  if (row_bytes % 16 != 0 || kCompactThreads % (row_bytes / 16) != 0 || row_bytes / 16 > kCompactThreads)
+    return TRIATTN_ERR_UNSUPPORTED_SHAPE;
+  CompactParams p{};
+  p.k_ptrs = k_layer_ptrs;
+  p.v_ptrs = v_layer_ptrs;
+  p.block_table = block_table;
+  p.seq_lens = seq_lens;
+  p.keep = keep;
+  p.keep_ls = keep_ls;
+  p.keep_rs = keep_rs;
+  p.keep_hs = keep_hs;
+  p.keep_counts = keep_counts;
+  p.status = device_status;
+  p.L = Y.num_layers;
+  p.B = Y.num_reqs;
+  p.Hkv = Y.num_kv_heads;
+  p.bs = Y.block_size;
+  p.num_blocks = Y.num_blocks;
+  p.max_blocks = Y.max_blocks_per_req;
+  p.block_stride = Y.block_stride;
+  p.token_stride = Y.token_stride;
+  p.head_stride = Y.head_stride;
+  p.row_bytes = row_bytes;
+  p.scratch = static_cast<unsigned char*>(scratch);
+  p.scratch_stream_bytes = scratch_stream_bytes;
+  p.scratch_rows = scratch_rows;
+  dim3 grid((unsigned)(Y.num_kv_heads * 2), (unsigned)Y.num_layers, (unsigned)Y.num_reqs);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (preserve)
+    compact_paged_kernel<true><<<grid, kCompactThreads, 0, st>>>(p);
+  else
+    compact_paged_kernel<false><<<grid, kCompactThreads, 0, st>>>(p);
+  return check_launch();
+}
+
+int triattn_compact_paged(const triattn_paged_layout* layout, void* const* k_layer_ptrs, void* const* v_layer_ptrs,
+                          const int32_t* block_table, const int32_t* seq_lens, const int32_t* keep,
+                          int64_t keep_layer_stride, int64_t keep_req_stride, int64_t keep_head_stride,
+                          const int32_t* keep_counts, uint32_t* device_status, void* stream) {
+  return compact_common(layout, k_layer_ptrs, v_layer_ptrs, block_table, seq_lens, keep, keep_layer_stride,
+                        keep_req_stride, keep_head_stride, keep_counts, nullptr, 0, 0, false, device_status, stream);
+}
+
+size_t triattn_compact_preserve_scratch_bytes(const triattn_paged_layout* layout, int max_dropped_rows) {
+  if (validate_layout(layout) != TRIATTN_OK || max_dropped_rows < 0) return 0;
+  const size_t per_stream = round_up((size_t)max_dropped_rows * layout->head_dim * 2, 256);
+  return per_stream * 2 * (size_t)layout->num_layers * layout->num_reqs * layout->num_kv_heads;
+}
+
+int triattn_compact_paged_preserve(const triattn_paged_layout* layout, void* const* k_layer_ptrs,
+                                   void* const* v_layer_ptrs, const int32_t* block_table, const int32_t* seq_lens,
+                                   const int32_t* keep, int64_t keep_layer_stride, int64_t keep_req_stride,
+                                   int64_t keep_head_stride, const int32_t* keep_counts, int max_dropped_rows,
+                                   void* scratch, size_t scratch_bytes, uint32_t* device_status, void* stream) {
+  int rc = validate_layout(layout);
+  if (rc != TRIATTN_OK) return rc;
+  if (!scratch || !aligned16(scratch) || max_dropped_rows < 0) return TRIATTN_ERR_INVALID_ARGUMENT;
+  const size_t need = triattn_compact_preserve_scratch_bytes(layout, max_dropped_rows);
+  if (scratch_bytes < need) return TRIATTN_ERR_WORKSPACE_TOO_SMALL;
+  const size_t per_stream = round_up((size_t)max_dropped_rows * layout->head_dim * 2, 256);
+  return compact_common(layout, k_layer_ptrs, v_layer_ptrs, block_table, seq_lens, keep, keep_layer_stride,
+                        keep_req_stride, keep_head_stride, keep_counts, scratch, (long long)per_stream,
+                        max_dropped_rows, true, device_status, stream);
+}
+
+// ------------------------------------------------------------------------- fused step
+namespace {
+struct CompressWs {
+  size_t trig, weights, raw, moments, mean_std, final_scores, total;
+};
+CompressWs compress_ws_layout(const triattn_paged_layout& Y, int num_offsets, int offset_agg) {
+  CompressWs w{};
+  const int F = Y.head_dim / 2;
+  const int Hq = Y.num_kv_heads * Y.group_size;
+  const int gp = std::max(1, triattn_padded_group(Y.group_size));
+  const size_t t_pad = (size_t)Y.max_blocks_per_req * Y.block_size;
+  size_t off = 0;
+  w.trig = off;
+  off += round_up(sizeof(float) * triattn_prep_scratch_floats(Y.num_reqs, F, num_offsets, offset_agg), 256);
+  w.weights = off;
+  off += round_up(sizeof(float) * (size_t)Y.num_layers * Y.num_reqs * Hq * triattn_weight_rows(offset_agg, num_offsets) * F, 256);
+  w.raw = off;
+  off += round_up(sizeof(float) * (size_t)Y.num_layers * Y.num_reqs * Y.num_kv_heads * t_pad * gp, 256);
+  w.moments = off;
+  off += round_up(sizeof(double) * 2 * (size_t)Y.num_layers * Y.num_reqs * Hq, 256);
+  w.mean_std = off;
+  off += round_up(sizeof(float) * 2 * (size_t)Y.num_layers * Y.num_reqs * Hq, 256);
+  w.final_scores = off;
+  off += round_up(sizeof(float) * (size_t)Y.num_reqs * Y.num_kv_heads * t_pad, 256);
+  w.total = off;
+  return w;
+}
+}  // namespace
+
+size_t triattn_compress_workspace_bytes(const triattn_paged_layout* layout, int num_offsets, int offset_agg,
+                                        int keep_pitch) {
+  (void)keep_pitch;
+  if (validate_layout(layout) != TRIATTN_OK || num_offsets <= 0) return 0;
+  return compress_ws_layout(*layout, num_offsets, offset_agg).total;
+}
+
+int triattn_compress_paged(const triattn_paged_layout* layout, void* const* k_layer_ptrs, void* const* v_layer_ptrs,
+                           const int32_t* block_table, const int32_t* seq_lens, const int32_t* round_start,
+                           const int32_t* prefill_lens, const int32_t* keep_counts, const float* q_mean_real,
+                           const float* q_mean_imag, const float* q_abs_mean, const float* freq_scale_sq,
+                           const float* omega, const float* offsets, int num_offsets, int offset_agg, int flags,
+                           int window, int normalize, int layer_reduce, void* workspace, size_t workspace_bytes,
+                           int32_t* keep_out, int keep_pitch, uint32_t* device_status, void* stream) {
+  int rc = validate_layout(layout);
+  if (rc != TRIATTN_OK) return rc;
+  if (!workspace || !aligned16(workspace) || !keep_out || keep_pitch <= 0 || num_offsets <= 0)
+    return TRIATTN_ERR_INVALID_ARGUMENT;
+  if (layer_reduce != TRIATTN_REDUCE_MEAN && layer_reduce != TRIATTN_REDUCE_MAX) return TRIATTN_ERR_INVALID_ARGUMENT;
+  const triattn_paged_layout& Y = *layout;
+  const CompressWs w = compress_ws_layout(Y, num_offsets, offset_agg);
+  if (workspace_bytes < w.total) return TRIATTN_ERR_WORKSPACE_TOO_SMALL;
+  unsigned char* ws = static_cast<unsigned char*>(workspace);
+  float* trig = reinterpret_cast<float*>(ws + w.trig);
+  float* weights = reinterpret_cast<float*>(ws + w.weights);
+  float* raw = reinterpret_cast<float*>(ws + w.raw);
+  double* moments = reinterpret_cast<double*>(ws + w.moments);
+  float* mean_std = reinterpret_cast<float*>(ws + w.mean_std);
+  float* fin = reinterpret_cast<float*>(ws + w.final_scores);
+  const int Hq = Y.num_kv_heads * Y.group_size;
+  const int64_t t_pad = (int64_t)Y.max_blocks_per_req * Y.block_size;
+
+  rc = triattn_prep_weights(q_mean_real, q_mean_imag, q_abs_mean, freq_scale_sq, omega, offsets, round_start,
+                            Y.num_layers, Y.num_reqs, Hq, Y.head_dim / 2, num_offsets, offset_agg, flags, trig,
+                            weights, stream);
+  if (rc != TRIATTN_OK) return rc;
+  rc = triattn_score_paged(layout, reinterpret_cast<const void* const*>(k_layer_ptrs), block_table, seq_lens,
+                           weights, offset_agg, num_offsets, raw, moments, device_status, stream);
+  if (rc != TRIATTN_OK) return rc;
+  rc = triattn_finalize_scores(layout, raw, moments, seq_lens, prefill_lens, window, normalize, TRIATTN_REDUCE_MAX,
+                               TRIATTN_REDUCE_NONE, layer_reduce, mean_std, fin, stream);
+  if (rc != TRIATTN_OK) return rc;
+  rc = triattn_select_topk(fin, Y.num_reqs * Y.num_kv_heads, t_pad, seq_lens, keep_counts, Y.num_reqs,
+                           Y.num_kv_heads, keep_out, keep_pitch, device_status, stream);
+  if (rc != TRIATTN_OK) return rc;
+  return triattn_compact_paged(layout, k_layer_ptrs, v_layer_ptrs, block_table, seq_lens, keep_out, 0,
+                               (int64_t)Y.num_kv_heads * keep_pitch, keep_pitch, keep_counts, device_status, stream);
+}
+
+}  // extern "C"

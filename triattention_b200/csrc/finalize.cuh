@@ -1,0 +1,104 @@
+// Score finalisation: moments -> (mean, std), z-normalisation, window / prefill guards, reduction
+// over the query heads of a KV head, over KV heads (optional) and over layers (optional).
+#pragma once
+
+#include "common.cuh"
+
+namespace triattn {
+
+// mean_std[l][b][h] = (mean, std_safe) from (sum, sumsq): mean = S1/n, var = (S2 - n*mean^2)/(n-1)
+// clamped at 0, std < 1e-8 -> 1 (streaming formula of the reference selector), evaluated in double.
+__global__ void moments_to_mean_std_kernel(const double* __restrict__ moments, const int32_t* __restrict__ seq_lens,
+                                           int L, int B, int Hq, int t_pad, float* __restrict__ mean_std) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= L * B * Hq) return;
+  const int b = (i / Hq) % B;
+  const int n = min(seq_lens[b], t_pad);
+  const double s1 = moments[2 * (size_t)i], s2 = moments[2 * (size_t)i + 1];
+  double mean = 0.0, var = 0.0;
+  if (n > 0) mean = s1 / (double)n;
+  if (n > 1) var = (s2 - (double)n * mean * mean) / (double)(n - 1);
+  if (var < 0.0) var = 0.0;
+  float sd = (float)sqrt(var);
+  if (sd < 1e-8f) sd = 1.0f;
+  mean_std[2 * (size_t)i] = (float)mean;
+  mean_std[2 * (size_t)i + 1] = sd;
+}
+
+struct FinalizeParams {
+  const float* raw;        // [L, B, Hkv, t_pad, GP]
+  const float* mean_std;   // [L, B, Hq, 2]
+  const int32_t* seq_lens;
+  const int32_t* prefill_lens;  // may be null
+  float* out;              // [Lo, B, Ho, t_pad]
+  int L, B, Hkv, g, t_pad;
+  int window, normalize, group_reduce, head_reduce, layer_reduce;
+};
+
+// one thread per (request, output head, token)
+template <int GP>
+__global__ void __launch_bounds__(256) finalize_scores_kernel(const __grid_constant__ FinalizeParams p) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  const int ho = blockIdx.y, b = blockIdx.z;
+  const int seq_len = min(p.seq_lens[b], p.t_pad);
+  if (t >= seq_len) return;
+  const int Hq = p.Hkv * p.g;
+  const int Ho = p.head_reduce != TRIATTN_REDUCE_NONE ? 1 : p.Hkv;
+  const int recent = p.window > 0 ? min(p.window, seq_len) : 0;
+  bool guarded = recent > 0 && t >= seq_len - recent;
+  if (p.prefill_lens != nullptr && t < p.prefill_lens[b]) guarded = true;
+  const int h_begin = p.head_reduce != TRIATTN_REDUCE_NONE ? 0 : ho;
+  const int h_end = p.head_reduce != TRIATTN_REDUCE_NONE ? p.Hkv : ho + 1;
+  float acc = 0.f;
+  for (int l = 0; l < p.L; ++l) {
+    float lv = -INFINITY;
+    for (int kvh = h_begin; kvh < h_end; ++kvh) {
+      float gv;
+      if (guarded) {
+        gv = INFINITY;
+      } else {
+        const float* r = p.raw + ((((size_t)l * p.B + b) * p.Hkv + kvh) * (size_t)p.t_pad + t) * GP;
+        float s[GP];
+        if constexpr (GP == 4) {
+          const float4 q = *reinterpret_cast<const float4*>(r);
+          s[0] = q.x; s[1] = q.y; s[2] = q.z; s[3] = q.w;
+        } else if constexpr (GP == 2) {
+          const float2 q = *reinterpret_cast<const float2*>(r);
+          s[0] = q.x; s[1] = q.y;
+        } else if constexpr (GP == 8) {
+          const float4 q0 = *reinterpret_cast<const float4*>(r);
+          const float4 q1 = *reinterpret_cast<const float4*>(r + 4);
+          s[0] = q0.x; s[1] = q0.y; s[2] = q0.z; s[3] = q0.w;
+          s[4] = q1.x; s[5] = q1.y; s[6] = q1.z; s[7] = q1.w;
+        } else {
+#pragma unroll
+          for (int j = 0; j < GP; ++j) s[j] = r[j];
+        }
+        const float* ms = p.mean_std + (((size_t)l * p.B + b) * Hq + (size_t)kvh * p.g) * 2;
+        float mx = -INFINITY, sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < GP; ++j) {
+          if (j < p.g) {
+            float z = s[j];
+            if (p.normalize) z = __fdiv_rn(__fsub_rn(z, __ldg(ms + 2 * j)), __ldg(ms + 2 * j + 1));
+            mx = fmaxf(mx, z);
+            sum = __fadd_rn(sum, z);
+          }
+        }
+        gv = p.group_reduce == TRIATTN_REDUCE_MEAN ? __fdiv_rn(sum, (float)p.g) : mx;
+      }
+      lv = fmaxf(lv, gv);  // single head unless head_reduce == MAX
+    }
+    if (p.layer_reduce == TRIATTN_REDUCE_NONE) {
+      p.out[(((size_t)l * p.B + b) * Ho + ho) * (size_t)p.t_pad + t] = lv;
+    } else if (p.layer_reduce == TRIATTN_REDUCE_MAX) {
+      acc = l == 0 ? lv : fmaxf(acc, lv);
+    } else {
+      acc = l == 0 ? lv : __fadd_rn(acc, lv);
+    }
+  }
+  if (p.layer_reduce == TRIATTN_REDUCE_MEAN) acc = __fdiv_rn(acc, (float)p.L);
+  if (p.layer_reduce != TRIATTN_REDUCE_NONE) p.out[((size_t)b * Ho + ho) * (size_t)p.t_pad + t] = acc;
+}
+
+}  // namespace triattn
