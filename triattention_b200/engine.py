@@ -1,0 +1,145 @@
+"""Batched compression engine: one native call for all requests that triggered in a step.
+
+The reference compresses one request at a time in a Python loop
+(runtime/runner_compression_actions.py:11-237 -> hook_impl.py:59-163) and does
+several host synchronisations per layer.  Here the per-step metadata of every
+triggered request (block ids, lengths, round starts, budgets) is packed into
+one pinned host buffer, copied once, and a single ``triattn_compress_paged``
+call scores, selects and compacts all requests and layers; one device->host
+read returns the status word.  Block tables are then truncated on the host
+exactly like ``truncate_tail_reclaim_group`` (runtime/layout_engine.py:209-227).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import torch
+
+from . import _native, ops
+
+
+@dataclass
+class CompressResult:
+    """Outcome of one batched compression step."""
+
+    keep: torch.Tensor                     # [B, Hkv, keep_pitch] int32 on device, ascending per row
+    keep_counts: list[int]                 # per request: tokens kept (cache_len_after)
+    kept_block_ids: list[list[int]]        # block table after tail truncation
+    removed_block_ids: list[list[int]]     # blocks handed back to the allocator
+    device_status: int                     # 0 or TRIATTN_DEV_* bits
+    h2d_bytes: int = 0
+    d2h_bytes: int = 0
+
+
+def num_required_blocks(total_tokens: int, block_size: int) -> int:
+    """Blocks needed for ``total_tokens`` (runtime/layout_engine.py:24-27)."""
+    if total_tokens <= 0:
+        return 0
+    return (total_tokens + block_size - 1) // block_size
+
+
+@dataclass
+class PagedCompressor:
+    """Score -> select -> compact for a batch of requests of one KV-cache group.
+
+    ``stats`` holds one row of statistics per layer of the group, in the order
+    of the layers of the ``PagedCacheView`` passed to :meth:`compress`.
+    """
+
+    stats: ops.DeviceStats
+    window: int = 128
+    normalize: bool = True
+    offset_agg: int = _native.OFFSETS_MEAN
+    flags: int = 0
+    layer_reduce: int = _native.REDUCE_MEAN
+    _workspace: Optional[torch.Tensor] = field(default=None, repr=False)
+    _staging: Optional[torch.Tensor] = field(default=None, repr=False)
+    _dev_meta: Optional[torch.Tensor] = field(default=None, repr=False)
+    _status_host: Optional[torch.Tensor] = field(default=None, repr=False)
+
+    def _buffers(self, n_ints: int, ws_bytes: int, device: torch.device):
+        if self._staging is None or self._staging.numel() < n_ints:
+            self._staging = torch.empty(n_ints, dtype=torch.int32).pin_memory()
+            self._dev_meta = torch.empty(n_ints, dtype=torch.int32, device=device)
+        if self._workspace is None or self._workspace.numel() < ws_bytes:
+            self._workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=device)
+        if self._status_host is None:
+            self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+
+    def compress(
+        self,
+        view: ops.PagedCacheView,
+        block_ids: Sequence[Sequence[int]],
+        seq_lens: Sequence[int],
+        round_starts: Sequence[int],
+        budgets: Sequence[int],
+        prefill_lens: Optional[Sequence[int]] = None,
+    ) -> CompressResult:
+        """Compress every listed request in place; returns keep sets and the truncated block tables.
+
+        ``budgets[b]`` is the number of tokens request ``b`` keeps (``min(budget_total, T)`` of
+        hook_runtime_context.py:187); ``prefill_lens`` guards tokens ``< prefill_lens[b]`` when given.
+        """
+        B = len(block_ids)
+        if not (B == len(seq_lens) == len(round_starts) == len(budgets)) or B == 0:
+            raise ValueError("block_ids, seq_lens, round_starts and budgets must be non-empty and of equal length")
+        bs = view.block_size
+        for ids, n in zip(block_ids, seq_lens):
+            if num_required_blocks(int(n), bs) > len(ids):
+                raise IndexError(
+                    f"token indices require block_idx={num_required_blocks(int(n), bs) - 1}, "
+                    f"but only {len(ids)} blocks exist")
+        g, rem = divmod(self.stats.num_heads, view.num_kv_heads)
+        if rem or g <= 0:
+            raise RuntimeError(
+                f"{_native.TRITON_SCORING_REQUIRED_MARKER}:incompatible_head_mapping:"
+                f"source={self.stats.num_heads},target={view.num_kv_heads}")
+        if self.stats.num_layers != view.num_layers:
+            raise ValueError(f"stats cover {self.stats.num_layers} layers, the cache group has {view.num_layers}")
+        max_blocks = max(num_required_blocks(int(n), bs) for n in seq_lens)
+        keep_counts = [min(int(k), int(n)) for k, n in zip(budgets, seq_lens)]
+        keep_pitch = max(max(keep_counts), 1)
+        layout = view.layout(B, g, max_blocks, rope_interleaved=self.stats.rope_interleaved)
+        O = int(self.stats.offsets.numel())
+        ws_bytes = ops.compress_workspace_bytes(layout, O, self.offset_agg, keep_pitch)
+        keep_bytes = B * view.num_kv_heads * keep_pitch * 4
+        # one staging buffer: block table rows, then seq_lens, round_start, keep_counts, prefill_lens, status
+        n_ints = B * max_blocks + 4 * B + 4
+        self._buffers(n_ints, ws_bytes + keep_bytes + 256, view.device)
+        st = self._staging[:n_ints]
+        st.zero_()
+        bt_host = st[: B * max_blocks].view(B, max_blocks)
+        for b, ids in enumerate(block_ids):
+            nb = num_required_blocks(int(seq_lens[b]), bs)
+            bt_host[b, :nb] = torch.as_tensor(list(ids[:nb]), dtype=torch.int32)
+        off = B * max_blocks
+        st[off : off + B] = torch.as_tensor(list(seq_lens), dtype=torch.int32)
+        st[off + B : off + 2 * B] = torch.as_tensor(list(round_starts), dtype=torch.int32)
+        st[off + 2 * B : off + 3 * B] = torch.as_tensor(keep_counts, dtype=torch.int32)
+        if prefill_lens is not None:
+            st[off + 3 * B : off + 4 * B] = torch.as_tensor(list(prefill_lens), dtype=torch.int32)
+        dm = self._dev_meta[:n_ints]
+        dm.copy_(st, non_blocking=True)
+        bt = dm[: B * max_blocks].view(B, max_blocks)
+        d_seq = dm[off : off + B]
+        d_rs = dm[off + B : off + 2 * B]
+        d_kc = dm[off + 2 * B : off + 3 * B]
+        d_pre = dm[off + 3 * B : off + 4 * B] if prefill_lens is not None else None
+        d_status = dm[off + 4 * B : off + 4 * B + 1]
+        ws = self._workspace
+        keep = ws[ws_bytes // 256 * 256 + 256 :][:keep_bytes].view(torch.int32).view(B, view.num_kv_heads, keep_pitch)
+        ops.compress_paged(
+            view, layout, self.stats, bt, d_seq, d_rs, d_pre, d_kc, keep_pitch, self.window, self.normalize,
+            self.offset_agg, self.flags, self.layer_reduce, workspace=ws, keep_out=keep, status=d_status)
+        self._status_host.copy_(d_status, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        status = int(self._status_host.item())
+        kept, removed = [], []
+        for b, ids in enumerate(block_ids):
+            req = num_required_blocks(keep_counts[b], bs)
+            ids = [int(x) for x in ids]
+            kept.append(ids[:req])
+            removed.append(ids[req:])
+        return CompressResult(keep=keep, keep_counts=keep_counts, kept_block_ids=kept, removed_block_ids=removed,
+                              device_status=status, h2d_bytes=n_ints * 4, d2h_bytes=4)
