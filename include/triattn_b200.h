@@ -110,6 +110,39 @@ int triattn_prep_weights(const float* q_mean_real, const float* q_mean_imag, con
                          int num_freqs, int num_offsets, int offset_agg, int flags,
                          float* scratch, float* weights_out, void* stream);
 
+/* Capacity, in floats, of the built-in scratch of triattn_prep_weights_noalloc (256 KiB). */
+#define TRIATTN_NOALLOC_PREP_SCRATCH_FLOATS 65536
+
+/*
+ * triattn_prep_weights for callers that must not allocate device memory.  (No counterpart in the
+ * reference: its scorer allocates torch temporaries on every call.)
+ *
+ * Who needs it: a serving worker that has already handed every free byte of HBM to its KV-cache
+ * pool, so a late cudaMalloc can fail or fragment the pool; and a hook that runs inside the
+ * engine's step loop, where cudaMalloc / cudaFree synchronise the whole device and would stall the
+ * other streams.  Such callers still pass their own inputs and `weights_out`; only the trig-table
+ * scratch (triattn_prep_scratch_floats() floats) is taken from an array that lives inside the
+ * library image.  Every GPU that loads the library holds those 256 KiB until the process exits.
+ *
+ * Limits and rules:
+ *   - triattn_prep_scratch_floats(num_reqs, num_freqs, num_offsets, offset_agg) must not exceed
+ *     TRIATTN_NOALLOC_PREP_SCRATCH_FLOATS (MEAN, 64 frequencies: up to 512 requests per call; MAX with
+ *     17 offsets: up to 30); larger requests return TRIATTN_ERR_LIMIT_EXCEEDED and launch nothing;
+ *   - the first call on a device looks up the array's device address (once per device, with that
+ *     device current); make that first call before starting any stream capture;
+ *   - all calls share the one array, which keeps the previous call's contents.  Nothing in it has
+ *     to start at zero - each call overwrites every entry it later reads - but two calls whose
+ *     kernels can overlap on the GPU (different streams, no ordering between them) race on it:
+ *     order them on one stream or with events;
+ *   - calls no cudaMalloc, cudaFree or allocating library routine.
+ * Arguments and results are those of triattn_prep_weights without `scratch`.
+ */
+int triattn_prep_weights_noalloc(const float* q_mean_real, const float* q_mean_imag, const float* q_abs_mean,
+                                 const float* freq_scale_sq, const float* omega, const float* offsets,
+                                 const int32_t* round_start, int num_layers, int num_reqs, int num_q_heads,
+                                 int num_freqs, int num_offsets, int offset_agg, int flags,
+                                 float* weights_out, void* stream);
+
 /*
  * Score every cached key of every (layer, request, KV head) against the g query heads of its
  * group: streams each cache block once with bulk async copies into shared memory and writes

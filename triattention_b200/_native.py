@@ -16,6 +16,8 @@ LIB_NAME = "libtriattn_b200.so"
 LIB_PATH = Path(__file__).resolve().parent / LIB_NAME
 
 OK = 0
+ERR_LIMIT_EXCEEDED = 6
+NOALLOC_PREP_SCRATCH_FLOATS = 65536
 OFFSETS_MEAN, OFFSETS_MAX = 0, 1
 REDUCE_NONE, REDUCE_MEAN, REDUCE_MAX = 0, 1, 2
 FLAG_DISABLE_MLR, FLAG_DISABLE_TRIG = 0x1, 0x2
@@ -29,6 +31,7 @@ EXPORTED_SYMBOLS = (
     "triattn_weight_rows",
     "triattn_prep_scratch_floats",
     "triattn_prep_weights",
+    "triattn_prep_weights_noalloc",
     "triattn_score_paged",
     "triattn_finalize_scores",
     "triattn_select_topk",
@@ -82,6 +85,8 @@ def _declare(lib) -> None:
     lib.triattn_prep_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
     lib.triattn_prep_weights.restype = c_int
     lib.triattn_prep_weights.argtypes = [P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, P, P]
+    lib.triattn_prep_weights_noalloc.restype = c_int
+    lib.triattn_prep_weights_noalloc.argtypes = [P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, P]
     lib.triattn_score_paged.restype = c_int
     lib.triattn_score_paged.argtypes = [LP, P, P, P, P, c_int, c_int, P, P, P, P]
     lib.triattn_finalize_scores.restype = c_int

@@ -4,6 +4,7 @@
 
 #include <algorithm>
 #include <cstdint>
+#include <mutex>
 
 #include "../../include/triattn_b200.h"
 #include "common.cuh"
@@ -114,6 +115,46 @@ int triattn_prep_weights(const float* q_mean_real, const float* q_mean_imag, con
                                                                    scratch, num_layers, num_reqs, num_q_heads,
                                                                    num_freqs, num_offsets, agg_max, flags, weights_out);
   return check_launch();
+}
+
+// ------------------------------------------------------------------------- allocation-free prep
+// Trig-table scratch that lives in the library image, for callers that cannot allocate.  In host
+// code the name below is only a host-side stand-in for the device array, never a device address:
+// the pointer handed to kernels comes from cudaGetSymbolAddress, looked up once per device.
+static __device__ __align__(256) float g_noalloc_prep_scratch[TRIATTN_NOALLOC_PREP_SCRATCH_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_noalloc_mutex;
+float* g_noalloc_prep_ptr[kMaxDevices] = {};
+}  // namespace
+
+int triattn_prep_weights_noalloc(const float* q_mean_real, const float* q_mean_imag, const float* q_abs_mean,
+                                 const float* freq_scale_sq, const float* omega, const float* offsets,
+                                 const int32_t* round_start, int num_layers, int num_reqs, int num_q_heads,
+                                 int num_freqs, int num_offsets, int offset_agg, int flags, float* weights_out,
+                                 void* stream) {
+  if (num_layers <= 0 || num_reqs <= 0 || num_q_heads <= 0 || num_freqs <= 0 || num_offsets <= 0)
+    return TRIATTN_ERR_INVALID_ARGUMENT;
+  if (triattn_prep_scratch_floats(num_reqs, num_freqs, num_offsets, offset_agg) >
+      (size_t)TRIATTN_NOALLOC_PREP_SCRATCH_FLOATS)
+    return TRIATTN_ERR_LIMIT_EXCEEDED;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return TRIATTN_ERR_CUDA;
+  float* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (g_noalloc_prep_ptr[dev] == nullptr) {
+      // set-up, once per device, with that device current
+      void* p = nullptr;
+      if (cudaGetSymbolAddress(&p, g_noalloc_prep_scratch) != cudaSuccess || p == nullptr) return TRIATTN_ERR_CUDA;
+      g_noalloc_prep_ptr[dev] = static_cast<float*>(p);
+    }
+    scratch = g_noalloc_prep_ptr[dev];
+  }
+  return triattn_prep_weights(q_mean_real, q_mean_imag, q_abs_mean, freq_scale_sq, omega, offsets, round_start,
+                              num_layers, num_reqs, num_q_heads, num_freqs, num_offsets, offset_agg, flags, scratch,
+                              weights_out, stream);
 }
 
 int triattn_score_paged(const triattn_paged_layout* layout, const void* const* k_layer_ptrs,
