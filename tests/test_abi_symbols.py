@@ -31,7 +31,7 @@ def test_host_only_queries():
     lib = _native.load()
     assert lib.triattn_abi_version() == 1
     assert _native.status_string(0) == "ok"
-    assert [lib.triattn_padded_group(g) for g in (1, 2, 3, 4, 5, 7, 8, 9)] == [1, 2, 4, 4, 8, 8, 8, 0]
+    assert [lib.triattn_padded_group(g) for g in (1, 2, 3, 4, 5, 7, 8, 9, 16, 65)] == [1, 2, 4, 4, 8, 8, 8, 12, 16, 0]
     assert lib.triattn_weight_rows(_native.OFFSETS_MEAN, 17) == 3
     assert lib.triattn_weight_rows(_native.OFFSETS_MAX, 17) == 35
     assert lib.triattn_prep_scratch_floats(8, 64, 17, _native.OFFSETS_MEAN) == 8 * 2 * 64

@@ -260,12 +260,12 @@ def test_device_status_flags_bad_metadata():
 def test_abi_rejects_bad_arguments():
     lib = _native.load()
     assert lib.triattn_select_topk(None, 1, 1, None, None, 1, 1, None, 1, None, None) == 1
-    lay = _native.PagedLayout(num_layers=1, num_reqs=1, num_kv_heads=1, group_size=16, head_dim=128, block_size=16,
+    lay = _native.PagedLayout(num_layers=1, num_reqs=1, num_kv_heads=1, group_size=80, head_dim=128, block_size=16,
                               num_blocks=4, max_blocks_per_req=4, block_stride=2048, token_stride=128, head_stride=128)
     import ctypes
     x = torch.zeros(16, device="cuda")
     rc = lib.triattn_score_paged(ctypes.byref(lay), x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr(), 0, 17,
                                  x.data_ptr(), x.data_ptr(), None, None)
-    assert rc == 2  # group size 16 is not supported
+    assert rc == 2  # group size 80 is beyond the supported 64
     with pytest.raises(_native.NativeLibraryError):
         _native.check(rc, "score_paged")

@@ -7,13 +7,14 @@ marker (``TRIATTN_FATAL_TRITON_SCORING_REQUIRED``, runtime/constants.py:3) is ra
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import POINTER, Structure, c_char_p, c_int, c_int32, c_int64, c_size_t, c_uint32, c_void_p
 from pathlib import Path
 
 from .constants import TRITON_SCORING_REQUIRED_MARKER
 
 LIB_NAME = "libtriattn_b200.so"
-LIB_PATH = Path(__file__).resolve().parent / LIB_NAME
+LIB_PATH = Path(os.environ.get("TRIATTN_B200_LIB") or (Path(__file__).resolve().parent / LIB_NAME))
 
 OK = 0
 ERR_LIMIT_EXCEEDED = 6

@@ -4,6 +4,7 @@
 
 #include <algorithm>
 #include <cstdint>
+#include <cstdlib>
 #include <mutex>
 
 #include "../../include/triattn_b200.h"
@@ -20,6 +21,14 @@ namespace {
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// tuning knob read from the environment (unset or unparsable -> the built-in choice)
+int env_int(const char* name, int fallback, int lo, int hi) {
+  const char* v = std::getenv(name);
+  if (v == nullptr || *v == 0) return fallback;
+  const long x = std::strtol(v, nullptr, 10);
+  return (x < lo || x > hi) ? fallback : (int)x;
+}
 
 int check_launch() { return cudaGetLastError() == cudaSuccess ? TRIATTN_OK : TRIATTN_ERR_CUDA; }
 
@@ -49,14 +58,13 @@ int launch_score_fast(const ScoreParams& p, int gp, dim3 grid, size_t smem, cuda
     auto kern = score_paged_mean_kernel<D, GP, IL>;                                                           \
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)   \
       return TRIATTN_ERR_CUDA;                                                                                \
-    kern<<<grid, kScoreThreads, smem, st>>>(p);                                                               \
+    kern<<<grid, kScoreThreadsWS, smem, st>>>(p);                                                               \
     return check_launch();                                                                                    \
   }
   switch (gp) {
     case 1: TRIATTN_LAUNCH(1)
     case 2: TRIATTN_LAUNCH(2)
     case 4: TRIATTN_LAUNCH(4)
-    case 8: TRIATTN_LAUNCH(8)
     default: return TRIATTN_ERR_UNSUPPORTED_SHAPE;
   }
 #undef TRIATTN_LAUNCH
@@ -82,7 +90,8 @@ const char* triattn_status_string(int status) {
 }
 
 int triattn_padded_group(int g) {
-  if (g <= 0 || g > 8) return 0;
+  if (g <= 0 || g > 64) return 0;
+  if (g > 4) return (g + 3) / 4 * 4;
   int gp = 1;
   while (gp < g) gp <<= 1;
   return gp;
@@ -195,20 +204,28 @@ int triattn_score_paged(const triattn_paged_layout* layout, const void* const* k
   p.agg_max = offset_agg == TRIATTN_OFFSETS_MAX ? 1 : 0;
 
   const long long block_bytes = (long long)Y.block_size * Y.num_kv_heads * Y.head_dim * 2;
+  p.gp_total = gp;
+  const int gpv = std::min(gp, 4);            // query slots per virtual head
+  const int nsub = gp / gpv;                  // virtual heads per KV head
+  const int nt = kLPK / gpv;
   const bool fast = !p.agg_max && (Y.head_dim == 64 || Y.head_dim == 128) && block_is_dense(layout) &&
-                    block_bytes <= 64 * 1024 && (p.block_stride_bytes % 16) == 0;
+                    block_bytes <= 64 * 1024 && (p.block_stride_bytes % 16) == 0 && (Y.block_size % nt) == 0 &&
+                    (long long)Y.num_kv_heads * nsub * (Y.block_size / nt) <= kMaxScoreItems;
   if (fast) {
-    constexpr int kNG = kScoreThreads / kLPK;
+    constexpr int kNG = kScoreConsumerThreads / kLPK;
     // cache blocks per stage: enough (head, token-batch) items to occupy all 16 key groups, stage <= 32 KB
-    const int nt = kLPK / gp;
-    const int items_per_block = Y.num_kv_heads * ((Y.block_size + nt - 1) / nt);
+    const int items_per_block = Y.num_kv_heads * nsub * (Y.block_size / nt);
     int mb = 1;
     while (mb * items_per_block < 2 * kNG && (mb * 2) * block_bytes <= 32 * 1024) mb *= 2;
+    mb = env_int("TRIATTN_SCORE_MB", mb, 1, 64);
+    while (mb > 1 && ((long long)mb * items_per_block > kMaxScoreItems || (long long)mb * block_bytes > 96 * 1024)) mb /= 2;
     const long long stage_bytes = (long long)mb * block_bytes;
     // two CTAs per SM share ~200 KB of shared memory; 8x128 keeps one CTA per SM
-    const long long budget = (gp * Y.head_dim >= 8 * 128) ? 160 * 1024 : 96 * 1024;
+    const long long budget = 100 * 1024;
     int stages = (int)std::min<long long>(4, budget / stage_bytes);
+    stages = env_int("TRIATTN_SCORE_STAGES", stages, 1, kMaxStages);
     if (stages < 2) stages = 2;
+    while (stages > 2 && stages * stage_bytes > 200 * 1024) --stages;
     p.block_bytes = (int)block_bytes;
     p.mb = mb;
     p.stages = stages;
@@ -219,18 +236,19 @@ int triattn_score_paged(const triattn_paged_layout* layout, const void* const* k
     const int min_tpc = (int)std::max<long long>(1, (64 * 1024) / stage_bytes);
     const int max_tpc = (int)std::max<long long>(min_tpc, (2 * 1024 * 1024) / stage_bytes);
     int tpc = (int)std::min<long long>(max_tpc, std::max<long long>(min_tpc, total_tiles / target_ctas));
+    tpc = env_int("TRIATTN_SCORE_TILES_PER_CTA", tpc, 1, 1 << 20);
     p.tiles_per_cta = tpc;
     dim3 grid((unsigned)((max_tiles + tpc - 1) / tpc), (unsigned)Y.num_layers, (unsigned)Y.num_reqs);
     const size_t smem = (size_t)stages * stage_bytes;
     if (Y.head_dim == 128)
-      return Y.rope_interleaved ? launch_score_fast<128, true>(p, gp, grid, smem, st)
-                                : launch_score_fast<128, false>(p, gp, grid, smem, st);
-    return Y.rope_interleaved ? launch_score_fast<64, true>(p, gp, grid, smem, st)
-                              : launch_score_fast<64, false>(p, gp, grid, smem, st);
+      return Y.rope_interleaved ? launch_score_fast<128, true>(p, gpv, grid, smem, st)
+                                : launch_score_fast<128, false>(p, gpv, grid, smem, st);
+    return Y.rope_interleaved ? launch_score_fast<64, true>(p, gpv, grid, smem, st)
+                              : launch_score_fast<64, false>(p, gpv, grid, smem, st);
   }
   dim3 grid((unsigned)((p.t_pad + 127) / 128), (unsigned)Y.num_kv_heads, (unsigned)(Y.num_layers * Y.num_reqs));
   if ((long long)Y.num_layers * Y.num_reqs > 65535) return TRIATTN_ERR_UNSUPPORTED_SHAPE;
-  score_paged_generic_kernel<<<grid, 128, 0, st>>>(p, Y.head_dim, gp, Y.rope_interleaved);
+  score_paged_generic_kernel<<<grid, 128, 0, st>>>(p, Y.head_dim, Y.rope_interleaved);
   return check_launch();
 }
 
@@ -271,12 +289,8 @@ int triattn_finalize_scores(const triattn_paged_layout* layout, const float* raw
   p.layer_reduce = layer_reduce;
   const int Ho = head_reduce != TRIATTN_REDUCE_NONE ? 1 : Y.num_kv_heads;
   dim3 grid((unsigned)((t_pad + 255) / 256), (unsigned)Ho, (unsigned)Y.num_reqs);
-  switch (gp) {
-    case 1: finalize_scores_kernel<1><<<grid, 256, 0, st>>>(p); break;
-    case 2: finalize_scores_kernel<2><<<grid, 256, 0, st>>>(p); break;
-    case 4: finalize_scores_kernel<4><<<grid, 256, 0, st>>>(p); break;
-    default: finalize_scores_kernel<8><<<grid, 256, 0, st>>>(p); break;
-  }
+  p.gp = gp;
+  finalize_scores_kernel<<<grid, 256, 0, st>>>(p);
   return check_launch();
 }
 

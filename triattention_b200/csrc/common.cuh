@@ -34,7 +34,7 @@ __device__ __forceinline__ float sqrt_approx(float x) {
 }
 // two bf16 packed in a 32-bit word -> (low element, high element) as fp32 (exact)
 __device__ __forceinline__ float2 bf16x2_to_float2(uint32_t w) {
-  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+  return make_float2(__uint_as_float(__byte_perm(w, 0u, 0x1044u)), __uint_as_float(__byte_perm(w, 0u, 0x3244u)));
 }
 __device__ __forceinline__ float bf16_to_float(uint16_t h) { return __uint_as_float(((uint32_t)h) << 16); }
 
@@ -48,6 +48,11 @@ __device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// orders earlier generic-proxy accesses to shared memory before later async-proxy (bulk copy) writes
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(

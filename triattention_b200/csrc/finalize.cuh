@@ -26,22 +26,22 @@ __global__ void moments_to_mean_std_kernel(const double* __restrict__ moments, c
 }
 
 struct FinalizeParams {
-  const float* raw;        // [L, B, Hkv, t_pad, GP]
+  const float* raw;        // [L, B, Hkv, t_pad, gp]
   const float* mean_std;   // [L, B, Hq, 2]
   const int32_t* seq_lens;
   const int32_t* prefill_lens;  // may be null
   float* out;              // [Lo, B, Ho, t_pad]
-  int L, B, Hkv, g, t_pad;
+  int L, B, Hkv, g, gp, t_pad;
   int window, normalize, group_reduce, head_reduce, layer_reduce;
 };
 
-// one thread per (request, output head, token)
-template <int GP>
+// one thread per (request, output head, token); gp = query-head slots per KV head in the raw layout
 __global__ void __launch_bounds__(256) finalize_scores_kernel(const __grid_constant__ FinalizeParams p) {
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   const int ho = blockIdx.y, b = blockIdx.z;
   const int seq_len = min(p.seq_lens[b], p.t_pad);
   if (t >= seq_len) return;
+  const int gp = p.gp;
   const int Hq = p.Hkv * p.g;
   const int Ho = p.head_reduce != TRIATTN_REDUCE_NONE ? 1 : p.Hkv;
   const int recent = p.window > 0 ? min(p.window, seq_len) : 0;
@@ -49,6 +49,7 @@ __global__ void __launch_bounds__(256) finalize_scores_kernel(const __grid_const
   if (p.prefill_lens != nullptr && t < p.prefill_lens[b]) guarded = true;
   const int h_begin = p.head_reduce != TRIATTN_REDUCE_NONE ? 0 : ho;
   const int h_end = p.head_reduce != TRIATTN_REDUCE_NONE ? p.Hkv : ho + 1;
+  const bool vec4 = (gp & 3) == 0;
   float acc = 0.f;
   for (int l = 0; l < p.L; ++l) {
     float lv = -INFINITY;
@@ -57,32 +58,26 @@ __global__ void __launch_bounds__(256) finalize_scores_kernel(const __grid_const
       if (guarded) {
         gv = INFINITY;
       } else {
-        const float* r = p.raw + ((((size_t)l * p.B + b) * p.Hkv + kvh) * (size_t)p.t_pad + t) * GP;
-        float s[GP];
-        if constexpr (GP == 4) {
-          const float4 q = *reinterpret_cast<const float4*>(r);
-          s[0] = q.x; s[1] = q.y; s[2] = q.z; s[3] = q.w;
-        } else if constexpr (GP == 2) {
-          const float2 q = *reinterpret_cast<const float2*>(r);
-          s[0] = q.x; s[1] = q.y;
-        } else if constexpr (GP == 8) {
-          const float4 q0 = *reinterpret_cast<const float4*>(r);
-          const float4 q1 = *reinterpret_cast<const float4*>(r + 4);
-          s[0] = q0.x; s[1] = q0.y; s[2] = q0.z; s[3] = q0.w;
-          s[4] = q1.x; s[5] = q1.y; s[6] = q1.z; s[7] = q1.w;
-        } else {
-#pragma unroll
-          for (int j = 0; j < GP; ++j) s[j] = r[j];
-        }
+        const float* r = p.raw + ((((size_t)l * p.B + b) * p.Hkv + kvh) * (size_t)p.t_pad + t) * gp;
         const float* ms = p.mean_std + (((size_t)l * p.B + b) * Hq + (size_t)kvh * p.g) * 2;
         float mx = -INFINITY, sum = 0.f;
+        for (int j0 = 0; j0 < p.g; j0 += 4) {
+          float s[4];
+          if (vec4) {
+            const float4 q = *reinterpret_cast<const float4*>(r + j0);
+            s[0] = q.x; s[1] = q.y; s[2] = q.z; s[3] = q.w;
+          } else {
 #pragma unroll
-        for (int j = 0; j < GP; ++j) {
-          if (j < p.g) {
-            float z = s[j];
-            if (p.normalize) z = __fdiv_rn(__fsub_rn(z, __ldg(ms + 2 * j)), __ldg(ms + 2 * j + 1));
-            mx = fmaxf(mx, z);
-            sum = __fadd_rn(sum, z);
+            for (int j = 0; j < 4; ++j) s[j] = (j0 + j < gp) ? r[j0 + j] : 0.f;
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (j0 + j < p.g) {
+              float z = s[j];
+              if (p.normalize) z = __fdiv_rn(__fsub_rn(z, __ldg(ms + 2 * (j0 + j))), __ldg(ms + 2 * (j0 + j) + 1));
+              mx = fmaxf(mx, z);
+              sum = __fadd_rn(sum, z);
+            }
           }
         }
         gv = p.group_reduce == TRIATTN_REDUCE_MEAN ? __fdiv_rn(sum, (float)p.g) : mx;

@@ -15,6 +15,8 @@
 //     store 64 contiguous bytes.
 #pragma once
 
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace triattn {
@@ -34,6 +36,7 @@ struct ScoreParams {
   int mb;                         // cache blocks per pipeline stage
   int stages;
   int tiles_per_cta;
+  int gp_total;  // query-head slots per KV head in the raw layout
   int num_offsets;  // generic kernel only
   int agg_max;      // generic kernel only
 };
@@ -41,27 +44,40 @@ struct ScoreParams {
 constexpr int kScoreThreads = 256;
 constexpr int kLPK = 16;  // lanes per key
 
+// One (virtual head, token-batch) work item of a pipeline stage; the table is identical for every stage.
+// A KV head with g > 4 query heads is split into ceil(g/4) virtual heads of <= 4 query heads that read
+// the same K rows, so the register-resident weight set never exceeds 4 query heads.
+struct ScoreItem {
+  int smem_off;  // byte offset of (cache block, KV head, first token of the batch) inside the stage
+  int tok_rel;   // token index of the batch's first token relative to the stage's first token
+  int vhead;     // virtual head = kv_head * nsub + sub
+  int pad;
+};
+constexpr int kMaxScoreItems = 256;
+constexpr int kScoreConsumerWarps = 8;
+constexpr int kScoreConsumerThreads = kScoreConsumerWarps * 32;
+constexpr int kScoreThreadsWS = kScoreConsumerThreads;  // the last warp to release a stage refills it
+constexpr int kMaxStages = 8;
+
+// GP = query-head slots per virtual head (1, 2 or 4).  p.gp_total = slots per KV head in the raw layout.
 template <int D, int GP, bool INTERLEAVED>
-__global__ void __launch_bounds__(kScoreThreads, (GP * D >= 8 * 128) ? 1 : 2)
+__global__ void __launch_bounds__(kScoreThreadsWS, 2)
 score_paged_mean_kernel(const __grid_constant__ ScoreParams p) {
   constexpr int F = D / 2;
   constexpr int FPT = F / kLPK;  // frequencies per lane: 4 (D=128) or 2 (D=64)
   constexpr int P2 = FPT / 2;    // fp32x2 pairs per lane per component
   constexpr int NT = kLPK / GP;  // tokens per batch
-  constexpr int NG = kScoreThreads / kLPK;
+  constexpr int NG = kScoreConsumerThreads / kLPK;
   static_assert(FPT >= 2 && (FPT % 2) == 0, "head_dim must be 64 or 128");
   static_assert(NT >= 1 && NT * GP == kLPK, "GP must divide 16");
 
   extern __shared__ __align__(128) unsigned char smem_tiles[];
-  __shared__ __align__(8) uint64_t full_bar[8];
+  __shared__ __align__(16) ScoreItem s_items[kMaxScoreItems];
+  __shared__ __align__(8) uint64_t full_bar[kMaxStages];
+  __shared__ unsigned int s_released[kMaxStages];  // warps that released each stage so far (monotonic)
   __shared__ int s_err;
 
   const int tid = threadIdx.x;
-  const int lg = tid & (kLPK - 1);  // lane within the key group
-  const int gid = tid / kLPK;
-  const int lane_lo = lg % GP;      // permutes head slots
-  const int lane_hi = lg / GP;      // permutes token slots
-  const unsigned gmask = 0xffffu << (((tid & 31) / kLPK) * kLPK);
   const int l = blockIdx.y, b = blockIdx.z;
 
   int seq_len = p.seq_lens[b];
@@ -75,20 +91,39 @@ score_paged_mean_kernel(const __grid_constant__ ScoreParams p) {
   if (tile0 >= ntiles) return;
   const int my_tiles = min(p.tiles_per_cta, ntiles - tile0);
   const int stage_bytes = p.mb * p.block_bytes;
-  const unsigned char* kbase = reinterpret_cast<const unsigned char*>(p.k_ptrs[l]);
-  const int32_t* bt = p.block_table + (size_t)b * p.max_blocks;
+  const int stage_tokens = p.mb * p.bs;
   const int Hq = p.Hkv * p.g;
+  const int nsub = p.gp_total / GP;  // virtual heads per KV head (1 unless g > 4)
+  const int nvh = p.Hkv * nsub;
+  const int bph = p.bs / NT;  // token batches per cache block (the host guarantees bs % NT == 0)
+  const int n_items = p.mb * nvh * bph;
 
   if (tid == 0) {
-    for (int s = 0; s < p.stages; ++s) mbar_init(smem_u32(&full_bar[s]), 1);
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      s_released[s] = 0u;
+    }
     mbar_fence_init();
     s_err = 0;
   }
+  for (int i = tid; i < n_items; i += kScoreThreadsWS) {
+    const int vh = i % nvh;
+    const int q = i / nvh;
+    const int batch = q % bph;
+    const int mbi = q / bph;
+    ScoreItem it;
+    it.smem_off = mbi * p.block_bytes + ((vh / nsub) * p.head_stride + batch * NT * p.token_stride) * 2;
+    it.tok_rel = mbi * p.bs + batch * NT;
+    it.vhead = vh;
+    it.pad = 0;
+    s_items[i] = it;
+  }
   __syncthreads();
 
-  // producer (thread 0): fetch the cache blocks of stage-tile `it`
-  auto issue = [&](int it) {
-    const int stage = it % p.stages;
+  // fetch the cache blocks of stage-tile `it` (called by one lane)
+  const unsigned char* kbase = reinterpret_cast<const unsigned char*>(p.k_ptrs[l]);
+  const int32_t* bt = p.block_table + (size_t)b * p.max_blocks;
+  auto issue = [&](int it, int stage) {
     const uint32_t bar = smem_u32(&full_bar[stage]);
     const int blk0 = (tile0 + it) * p.mb;
     const int nb = min(p.mb, nblk - blk0);
@@ -105,36 +140,59 @@ score_paged_mean_kernel(const __grid_constant__ ScoreParams p) {
   };
   if (tid == 0) {
     const int pre = min(p.stages, my_tiles);
-    for (int it = 0; it < pre; ++it) issue(it);
+    for (int it = 0; it < pre; ++it) issue(it, it);
   }
 
-  // register-resident weights of the current KV head: [pair][head slot] for re / im / magnitude
+  // ---------------------------------------------------------------- consumers (all 8 warps)
+  // The two 16-lane key groups of a warp run in lockstep (same trip counts, warp-uniform branches), so
+  // every shuffle uses the full-warp mask; xor distances < 16 never cross the group boundary.
+  constexpr unsigned kFull = 0xffffffffu;
+  const int lane = tid & 31;
+  const int lg = tid & (kLPK - 1);  // lane within the key group
+  const int gid = tid / kLPK;
+  const int lane_lo = lg % GP;      // permutes head slots
+  const int lane_hi = lg / GP;      // permutes token slots
+
+  // register-resident weights of the current virtual head: [pair][head slot] for re / im / magnitude
   float2 wre[P2][GP], wim[P2][GP], wmg[P2][GP];
-  int cur_head = -1;
-  float s1 = 0.f, s2 = 0.f;  // running sum / sum of squares of this lane's (head, query slot)
+  int cur_vh = -1;
+  int cur_qbase = 0;           // first query head (within the layer) of the current virtual head
+  int cur_nq = 0;              // valid query slots of the current virtual head
+  float s1 = 0.f, s2 = 0.f;    // running sum / sum of squares of this lane's (virtual head, query slot)
+  float* raw_head = nullptr;   // raw-score rows of (l, b, kv head), pre-offset by sub*GP and this lane's slot
+
+  // 32-bit byte offsets into smem_tiles of this lane's slice of token slot tp (slot tp holds token tp ^ lane_hi)
+  const unsigned lane_byte = (unsigned)lg * (INTERLEAVED ? FPT * 4 : FPT * 2);
+  unsigned lane_off[NT];
+#pragma unroll
+  for (int tp = 0; tp < NT; ++tp) lane_off[tp] = (unsigned)((tp ^ lane_hi) * p.token_stride * 2) + lane_byte;
+  const int gp_total = p.gp_total;
 
   auto flush_moments = [&]() {
-    if (cur_head < 0) return;
+    if (cur_vh < 0) return;
     // lanes with equal lg % GP inside the 16-lane group hold the same query head
 #pragma unroll
     for (int s = GP; s < kLPK; s <<= 1) {
-      s1 += __shfl_xor_sync(gmask, s1, s);
-      s2 += __shfl_xor_sync(gmask, s2, s);
+      s1 += __shfl_xor_sync(kFull, s1, s);
+      s2 += __shfl_xor_sync(kFull, s2, s);
     }
-    if (lg < GP && lg < p.g) {
-      double* m = p.moments + (((size_t)l * p.B + b) * Hq + (size_t)cur_head * p.g + lg) * 2;
+    if (lg < GP && lg < cur_nq) {
+      double* m = p.moments + (((size_t)l * p.B + b) * Hq + (size_t)cur_qbase + lg) * 2;
       atomicAdd(m, (double)s1);
       atomicAdd(m + 1, (double)s2);
     }
     s1 = 0.f;
     s2 = 0.f;
   };
-  auto load_weights = [&](int head) {
+  auto load_weights = [&](int vh) {
+    const int kvh = vh / nsub, sub = vh - kvh * nsub;
+    cur_qbase = kvh * p.g + sub * GP;
+    cur_nq = min(GP, p.g - sub * GP);
 #pragma unroll
     for (int hp = 0; hp < GP; ++hp) {
       const int h = hp ^ lane_lo;
-      const bool on = h < p.g;
-      const float* w = p.weights + ((((size_t)l * p.B + b) * Hq + (size_t)head * p.g + (on ? h : 0)) * 3) * F + lg * FPT;
+      const bool on = h < cur_nq;
+      const float* w = p.weights + ((((size_t)l * p.B + b) * Hq + (size_t)cur_qbase + (on ? h : 0)) * 3) * F + lg * FPT;
 #pragma unroll
       for (int c = 0; c < P2; ++c) {
         const float2 z = make_float2(0.f, 0.f);
@@ -143,140 +201,158 @@ score_paged_mean_kernel(const __grid_constant__ ScoreParams p) {
         wmg[c][hp] = on ? __ldg(reinterpret_cast<const float2*>(w + 2 * F + 2 * c)) : z;
       }
     }
+    raw_head = p.raw + (((size_t)l * p.B + b) * p.Hkv + kvh) * (size_t)p.t_pad * gp_total + sub * GP +
+               lane_hi * gp_total + lane_lo;
   };
 
-  const int bph = (p.bs + NT - 1) / NT;        // token batches per cache block
-  const int items_per_block = p.Hkv * bph;
-  const int n_items = p.mb * items_per_block;
-
-  for (int it = 0; it < my_tiles; ++it) {
-    const int stage = it % p.stages;
-    const uint32_t parity = (uint32_t)((it / p.stages) & 1);
-    const bool ready = mbar_wait_bounded(smem_u32(&full_bar[stage]), parity);
-    if (!ready) {
-      s_err = 1;
-      flag_status(p.status, TRIATTN_DEV_WAIT_TIMEOUT);
+  // one (virtual head, batch of NT tokens) item; `checked` = the stage may hold tokens beyond seq_len.
+  // `live` is false only for the padding item of a group when n_items is not a multiple of the group count.
+  auto process_item = [&](unsigned tile_off, const ScoreItem it, int tile_tok0, bool live, auto checked) {
+    constexpr bool CHECK = decltype(checked)::value;
+    if (__any_sync(kFull, it.vhead != cur_vh)) {  // warp-uniform: both key groups switch together
+      flush_moments();
+      load_weights(it.vhead);
+      cur_vh = it.vhead;
     }
-    const unsigned char* tile = smem_tiles + (size_t)stage * stage_bytes;
-    const int blk0 = (tile0 + it) * p.mb;
+    const unsigned base = tile_off + (unsigned)it.smem_off;
+    const int gtok0 = tile_tok0 + it.tok_rel;
 
-    if (ready) {
-      for (int item = gid; item < n_items; item += NG) {
-        const int head = item % p.Hkv;
-        const int q = item / p.Hkv;
-        const int batch = q % bph;
-        const int mbi = q / bph;
-        if (head != cur_head) {
-          flush_moments();
-          load_weights(head);
-          cur_head = head;
+    float2 acc[NT][GP];
+#pragma unroll
+    for (int tp = 0; tp < NT; ++tp)
+#pragma unroll
+      for (int hp = 0; hp < GP; ++hp) acc[tp][hp] = make_float2(0.f, 0.f);
+
+#pragma unroll
+    for (int tp = 0; tp < NT; ++tp) {
+      bool valid = true;
+      if constexpr (CHECK) valid = gtok0 + (tp ^ lane_hi) < seq_len;
+      const unsigned char* row = smem_tiles + (base + (valid ? lane_off[tp] : lane_byte));  // invalid: token 0, zeroed
+      float2 kre[P2], kim[P2];
+      if constexpr (!INTERLEAVED) {
+        if constexpr (FPT == 4) {
+          const uint2 a = *reinterpret_cast<const uint2*>(row);
+          const uint2 c = *reinterpret_cast<const uint2*>(row + F * 2);
+          kre[0] = bf16x2_to_float2(a.x);
+          kre[1] = bf16x2_to_float2(a.y);
+          kim[0] = bf16x2_to_float2(c.x);
+          kim[1] = bf16x2_to_float2(c.y);
+        } else {
+          kre[0] = bf16x2_to_float2(*reinterpret_cast<const uint32_t*>(row));
+          kim[0] = bf16x2_to_float2(*reinterpret_cast<const uint32_t*>(row + F * 2));
         }
-        const int tok_base = batch * NT;
-        const int gtok_base = (blk0 + mbi) * p.bs;
-        const unsigned char* blkp = tile + (size_t)mbi * p.block_bytes + (size_t)head * p.head_stride * 2;
-
-        float2 acc[NT][GP];
+      } else {
+        if constexpr (FPT == 4) {
+          const uint4 a = *reinterpret_cast<const uint4*>(row);
+          const float2 p0 = bf16x2_to_float2(a.x), p1 = bf16x2_to_float2(a.y);
+          const float2 p2 = bf16x2_to_float2(a.z), p3 = bf16x2_to_float2(a.w);
+          kre[0] = make_float2(p0.x, p1.x);
+          kim[0] = make_float2(p0.y, p1.y);
+          kre[1] = make_float2(p2.x, p3.x);
+          kim[1] = make_float2(p2.y, p3.y);
+        } else {
+          const uint2 a = *reinterpret_cast<const uint2*>(row);
+          const float2 p0 = bf16x2_to_float2(a.x), p1 = bf16x2_to_float2(a.y);
+          kre[0] = make_float2(p0.x, p1.x);
+          kim[0] = make_float2(p0.y, p1.y);
+        }
+      }
 #pragma unroll
-        for (int tp = 0; tp < NT; ++tp)
-#pragma unroll
-          for (int hp = 0; hp < GP; ++hp) acc[tp][hp] = make_float2(0.f, 0.f);
-
-#pragma unroll
-        for (int tp = 0; tp < NT; ++tp) {
-          const int tok = tok_base + (tp ^ lane_hi);
-          const bool valid = (tok < p.bs) && (gtok_base + tok < seq_len);
-          const unsigned char* row = blkp + (size_t)(valid ? tok : 0) * p.token_stride * 2;
-          float2 kre[P2], kim[P2];
-          if constexpr (!INTERLEAVED) {
-            if constexpr (FPT == 4) {
-              const uint2 a = *reinterpret_cast<const uint2*>(row + lg * 8);
-              const uint2 c = *reinterpret_cast<const uint2*>(row + F * 2 + lg * 8);
-              kre[0] = bf16x2_to_float2(a.x);
-              kre[1] = bf16x2_to_float2(a.y);
-              kim[0] = bf16x2_to_float2(c.x);
-              kim[1] = bf16x2_to_float2(c.y);
-            } else {
-              kre[0] = bf16x2_to_float2(*reinterpret_cast<const uint32_t*>(row + lg * 4));
-              kim[0] = bf16x2_to_float2(*reinterpret_cast<const uint32_t*>(row + F * 2 + lg * 4));
-            }
-          } else {
-            if constexpr (FPT == 4) {
-              const uint4 a = *reinterpret_cast<const uint4*>(row + lg * 16);
-              const float2 p0 = bf16x2_to_float2(a.x), p1 = bf16x2_to_float2(a.y);
-              const float2 p2 = bf16x2_to_float2(a.z), p3 = bf16x2_to_float2(a.w);
-              kre[0] = make_float2(p0.x, p1.x);
-              kim[0] = make_float2(p0.y, p1.y);
-              kre[1] = make_float2(p2.x, p3.x);
-              kim[1] = make_float2(p2.y, p3.y);
-            } else {
-              const uint2 a = *reinterpret_cast<const uint2*>(row + lg * 8);
-              const float2 p0 = bf16x2_to_float2(a.x), p1 = bf16x2_to_float2(a.y);
-              kre[0] = make_float2(p0.x, p1.x);
-              kim[0] = make_float2(p0.y, p1.y);
-            }
-          }
-#pragma unroll
-          for (int c = 0; c < P2; ++c) {
-            if (!valid) {
-              kre[c] = make_float2(0.f, 0.f);
-              kim[c] = make_float2(0.f, 0.f);
-            }
-            float2 m2 = ffma2(kim[c], kim[c], fmul2(kre[c], kre[c]));
-            m2.x = sqrt_approx(m2.x);
-            m2.y = sqrt_approx(m2.y);
-#pragma unroll
-            for (int hp = 0; hp < GP; ++hp) {
-              float2 a2 = acc[tp][hp];
-              a2 = ffma2(kre[c], wre[c][hp], a2);
-              a2 = ffma2(kim[c], wim[c][hp], a2);
-              a2 = ffma2(m2, wmg[c][hp], a2);
-              acc[tp][hp] = a2;
-            }
+      for (int c = 0; c < P2; ++c) {
+        if constexpr (CHECK) {
+          if (!valid) {
+            kre[c] = make_float2(0.f, 0.f);
+            kim[c] = make_float2(0.f, 0.f);
           }
         }
-
-        // collapse the frequency pairs, then reduce-scatter across the 16 lanes
-        float v[kLPK];
+        float2 m2 = ffma2(kim[c], kim[c], fmul2(kre[c], kre[c]));
+        m2.x = sqrt_approx(m2.x);
+        m2.y = sqrt_approx(m2.y);
 #pragma unroll
-        for (int tp = 0; tp < NT; ++tp)
-#pragma unroll
-          for (int hp = 0; hp < GP; ++hp) v[tp * GP + hp] = acc[tp][hp].x + acc[tp][hp].y;
-#pragma unroll
-        for (int s = kLPK / 2; s >= 1; s >>= 1) {
-#pragma unroll
-          for (int i = 0; i < kLPK; ++i) {
-            if ((i & s) == 0 && i < 2 * s) v[i] += __shfl_xor_sync(gmask, v[i | s], s);
-          }
-        }
-        // lane lg now owns token tok_base + lg/GP, query slot lg%GP
-        const int tok = tok_base + lane_hi;
-        const int gtok = gtok_base + tok;
-        if (tok < p.bs && gtok < seq_len && lane_lo < p.g) {
-          const float sc = v[0];
-          p.raw[((((size_t)l * p.B + b) * p.Hkv + head) * (size_t)p.t_pad + gtok) * GP + lane_lo] = sc;
-          s1 += sc;
-          s2 = fmaf(sc, sc, s2);
+        for (int hp = 0; hp < GP; ++hp) {
+          float2 a2 = acc[tp][hp];
+          a2 = ffma2(kre[c], wre[c][hp], a2);
+          a2 = ffma2(kim[c], wim[c][hp], a2);
+          a2 = ffma2(m2, wmg[c][hp], a2);
+          acc[tp][hp] = a2;
         }
       }
     }
-    __syncthreads();  // every lane is done reading this stage
-    if (s_err) break;
-    if (tid == 0 && it + p.stages < my_tiles) issue(it + p.stages);
-  }
-  flush_moments();
 
-  if (s_err && tid == 0) {
-    // give copies that may still be in flight into this CTA's shared memory a bounded chance to land
-    for (int it = 0; it < my_tiles && it < p.stages; ++it) {
-      (void)mbar_wait_bounded(smem_u32(&full_bar[it % p.stages]), 0u);
+    // collapse the frequency pairs, then reduce-scatter across the 16 lanes
+    float v[kLPK];
+#pragma unroll
+    for (int tp = 0; tp < NT; ++tp)
+#pragma unroll
+      for (int hp = 0; hp < GP; ++hp) v[tp * GP + hp] = acc[tp][hp].x + acc[tp][hp].y;
+#pragma unroll
+    for (int s = kLPK / 2; s >= 1; s >>= 1) {
+#pragma unroll
+      for (int i = 0; i < kLPK; ++i) {
+        if ((i & s) == 0 && i < 2 * s) v[i] += __shfl_xor_sync(kFull, v[i | s], s);
+      }
+    }
+    // lane lg now owns token gtok0 + lg/GP, query slot lg%GP
+    bool store = live && (lane_lo < cur_nq);
+    if constexpr (CHECK) store = store && (gtok0 + lane_hi < seq_len);
+    if (store) {
+      const float sc = v[0];
+      raw_head[(size_t)gtok0 * gp_total] = sc;
+      s1 += sc;
+      s2 = fmaf(sc, sc, s2);
+    }
+  };
+
+  const int slots = (n_items + NG - 1) / NG;  // items per key group and stage (uniform over the CTA)
+  int stage = 0;
+  uint32_t parity = 0;
+  unsigned release_target = (unsigned)kScoreConsumerWarps;
+  for (int it = 0; it < my_tiles; ++it) {
+    // warp-uniform outcome, so that the shuffles below never see a split warp
+    const bool ready = __all_sync(kFull, mbar_wait_bounded(smem_u32(&full_bar[stage]), parity));
+    if (!ready) {
+      s_err = 1;
+      if (lane == 0) flag_status(p.status, TRIATTN_DEV_WAIT_TIMEOUT);
+      break;
+    }
+    const unsigned tile_off = (unsigned)(stage * stage_bytes);
+    const int tile_tok0 = (tile0 + it) * stage_tokens;
+    if (tile_tok0 + stage_tokens <= seq_len && slots * NG == n_items) {
+      for (int sl = 0; sl < slots; ++sl)
+        process_item(tile_off, s_items[gid + sl * NG], tile_tok0, true, std::false_type{});
+    } else {
+      for (int sl = 0; sl < slots; ++sl) {
+        const int item = gid + sl * NG;
+        const bool live = item < n_items;
+        process_item(tile_off, s_items[live ? item : 0], tile_tok0, live, std::true_type{});
+      }
+    }
+    // release the stage: all lanes of this warp have consumed their shared-memory reads.  The warp whose
+    // release is the last of the 8 refills the stage with the tile `stages` ahead - nobody waits for it.
+    __syncwarp();
+    if (lane == 0) {
+      __threadfence_block();
+      const unsigned int done = atomicAdd(&s_released[stage], 1u) + 1u;
+      if (done == release_target && it + p.stages < my_tiles) {
+        __threadfence_block();
+        fence_proxy_async();
+        issue(it + p.stages, stage);
+      }
+    }
+    if (++stage == p.stages) {
+      stage = 0;
+      parity ^= 1u;
+      release_target += (unsigned)kScoreConsumerWarps;
     }
   }
+  flush_moments();
 }
 
 // Generic scorer: any head_dim / group size / offset aggregation (mean or max).  One thread per
 // (token, KV head); K is read straight from global memory (cache resident between passes).
 // Weight rows: MEAN {w_re, w_im, w_mag}; MAX {w_re[o]..., w_im[o]..., w_mag}.
-__global__ void score_paged_generic_kernel(const __grid_constant__ ScoreParams p, int D, int GP, int interleaved) {
+__global__ void score_paged_generic_kernel(const __grid_constant__ ScoreParams p, int D, int interleaved) {
+  const int GP = p.gp_total;
   const int F = D / 2;
   const int l = blockIdx.z / p.B, b = blockIdx.z % p.B;
   const int head = blockIdx.y;
