@@ -347,12 +347,56 @@ def gen_real_stats_case(out: dict):
                               "source": "layers 0-1 of triattention/calibration/for_aime25_experiment/qwen3_8b.pt"}
 
 
+def gen_hook_cases(out: dict):
+    """The reference's runner hook (hook_impl.py) driven on CPU with a fake runner: result dicts, block tables, caches."""
+    import types
+    import triattention.vllm.runtime.config as ref_runtime_config
+    from triattention.vllm.runtime.hook_impl import make_runner_compression_hook
+    from triattention.vllm.runtime.signals import CompressionSignal
+
+    p = dict(seed=synth.seed_for(93, 0), num_layers=2, num_q_heads=8, num_kv_heads=2, head_dim=128, theta=1e6,
+             total_tokens=900, block_size=16, kv_axis=0, budget=256, window=32, round_start=900)
+    stats, caches, block_ids = build_paged_case(p)
+    arrays, results = {}, {}
+    with tempfile.TemporaryDirectory() as td:
+        sp = Path(td) / "hook.pt"
+        synth.save_stats_pt(stats, sp)
+        cfg = runtime_config(ref_runtime_config, sp, p)
+        T = p["total_tokens"]
+        runner = types.SimpleNamespace(
+            requests={"r0": types.SimpleNamespace(block_ids=(list(block_ids),), num_computed_tokens=T),
+                      "r1": types.SimpleNamespace(block_ids=(list(block_ids[:8]),), num_computed_tokens=100)},
+            kv_caches=caches, cache_config=types.SimpleNamespace(block_size=p["block_size"]))
+        hook = make_runner_compression_hook(runner, cfg)
+        so = types.SimpleNamespace(num_scheduled_tokens={"r0": 1, "r1": 1})
+
+        def sig(req, est, **kw):
+            base = dict(req_id=req, should_compress=True, reason="length_threshold", estimated_cache_len=est, step=1,
+                        kv_usage=None, protect_prefill=False, prefill_len=0, scheduled_tokens=1)
+            base.update(kw)
+            return CompressionSignal(**base)
+
+        results["under_budget"] = hook(req_id="r1", signal=sig("r1", 101), scheduler_output=so)
+        results["not_found"] = hook(req_id="zz", signal=sig("zz", 500), scheduler_output=so)
+        results["prefill_exceeds"] = hook(req_id="r0", signal=sig("r0", T + 1, protect_prefill=True, prefill_len=400),
+                                          scheduler_output=so)
+        results["compacted"] = hook(req_id="r0", signal=sig("r0", T + 1), scheduler_output=so)
+        results["block_ids_after"] = [list(g) for g in runner.requests["r0"].block_ids]
+        # the request grew by 40 tokens since: below budget + divide_length -> deferred
+        runner.requests["r0"].num_computed_tokens = T + 40
+        results["deferred"] = hook(req_id="r0", signal=sig("r0", 256 + 40 + 1), scheduler_output=so)
+    p["block_ids"] = block_ids
+    p["cache_out_sha256"] = [sha(c) for c in caches]
+    out["hook_cases"] = {"params": p, "results": results}
+
+
 def main():
     ref_scoring, ref_config = install_shims()
     out = {"torch": torch.__version__, "reference_root": str(REF)}
     gen_score_cases(ref_scoring, ref_config, out)
     gen_selector_cases(out)
     gen_real_stats_case(out)
+    gen_hook_cases(out)
     (HERE / "manifest.json").write_text(json.dumps(out, indent=1, sort_keys=True))
     print("wrote", [p.name for p in HERE.iterdir()])
 

@@ -1,0 +1,260 @@
+"""GPU parity of the Python mirror of the reference interface: selector modes, hook, batched engine, dense API."""
+from __future__ import annotations
+
+import types
+
+import pytest
+import torch
+
+import oracle
+from conftest import np_to_bf16, tensor_sha
+from golden_cases import build_paged_case, stats_by_layer
+from gpu_utils import device_stats, keep_sets_match_modulo_near_ties, score_tolerance_ok
+from triattention_b200 import _native, engine, hook as hook_mod, kv_compaction, ops, synth
+from triattention_b200.compressor import TriAttentionCompressor, compute_scores
+from triattention_b200.config import TriAttentionConfig, TriAttentionRuntimeConfig
+from triattention_b200.selector import build_triattention_selector
+from triattention_b200.signals import CompressionSignal
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _cfg(p, stats_path, **kw):
+    base = dict(
+        kv_budget=p["budget"], window_size=p["window"], sparse_stats_path=stats_path,
+        sparse_score_aggregation=p.get("aggregation", "mean"), sparse_normalize_scores=p.get("normalize", True),
+        pruning_mode=p.get("pruning_mode", "per_head"),
+        per_head_selection_semantics=p.get("semantics", "hf_aligned_global_per_head"),
+        layer_perhead_aggregation=p.get("layer_perhead_aggregation", "max"),
+        allow_per_layer_mode=p.get("pruning_mode", "per_head") == "per_layer",
+        protect_prefill=p.get("protect_prefill", False))
+    base.update(kw)
+    cfg = TriAttentionRuntimeConfig(**base)
+    cfg.validate()
+    return cfg
+
+
+def _register(caches, p):
+    for c in caches:
+        if int(c.shape[0]) == 2 and int(c.shape[1]) == 2:
+            kv_compaction.register_kv_layout_axis_hint(c, p["kv_axis"])
+
+
+@pytest.mark.parametrize("name", ["tiny_group", "chunked_group", "c0_like", "llama3_nonorm", "max_agg_prefill", "d64_g8"])
+def test_group_selector_matches_reference_keep(manifest, selector_cases, tmp_path, name):
+    p = manifest["selector_cases"]["cases"][name]
+    stats, caches, block_ids = build_paged_case(p)
+    sp = tmp_path / "s.pt"
+    synth.save_stats_pt(stats, sp)
+    _, sel_group, status = build_triattention_selector(_cfg(p, sp))
+    assert status == "enabled" and sel_group._supports_paged_group
+    dc = [c.to(DEV) for c in caches]
+    _register(dc, p)
+    T, bs = p["total_tokens"], p["block_size"]
+
+    def _iter():
+        for l, c in enumerate(dc):
+            yield l, c, block_ids, bs
+
+    res = sel_group(layer_inputs=None, layer_input_iter=None, layer_kv_iter=_iter, total_tokens=T,
+                    prefill_len=p.get("prefill_len", 0), protect_prefill=p.get("protect_prefill", False),
+                    round_start=p["round_start"], budget_total=min(p["budget"], T))
+    assert res["mode"] == "per_head" and res["semantic"] == "hf_aligned_global_per_head"
+    assert res["indices"].dtype == torch.int64 and res["debug_recent_count"] == min(p["window"], T)
+    ref_keep = torch.from_numpy(selector_cases[f"{name}/keep"]).long()
+    layers = [(l, c, block_ids, bs) for l, c in enumerate(caches)]
+    ref_final = oracle.final_scores_group_per_head(
+        layers, stats_by_layer(stats), stats.inv_freq, oracle.geometric_offsets(), T, p["round_start"],
+        window_size=p["window"], prefill_len=p.get("prefill_len", 0), protect_prefill=p.get("protect_prefill", False),
+        normalize=p.get("normalize", True), aggregation=p.get("aggregation", "mean"), kv_axis=p["kv_axis"])
+    ok, nd = keep_sets_match_modulo_near_ties(res["indices"].cpu(), ref_keep, ref_final)
+    assert ok, nd
+    # under budget: identity
+    ident = sel_group(layer_inputs=None, layer_input_iter=None, layer_kv_iter=_iter, total_tokens=T, prefill_len=0,
+                      protect_prefill=False, round_start=T, budget_total=T)
+    assert torch.equal(ident["indices"].cpu(), torch.arange(T).expand(p["num_kv_heads"], -1))
+
+
+@pytest.mark.parametrize("name,mode", [("legacy_layer_local", "per_head"), ("per_layer_shared", "shared"),
+                                       ("plph_mean", "per_head")])
+def test_layer_local_selector_modes(manifest, selector_cases, tmp_path, name, mode):
+    p = manifest["selector_cases"]["cases"][name]
+    stats, caches, block_ids = build_paged_case(p)
+    sp = tmp_path / "s.pt"
+    synth.save_stats_pt(stats, sp)
+    sel_layer, sel_group, _ = build_triattention_selector(_cfg(p, sp))
+    T, bs = p["total_tokens"], p["block_size"]
+    sl = stats_by_layer(stats)
+    for l, c in enumerate(caches):
+        dcache = c.to(DEV)
+        res = sel_layer(keys_dense=None, kv_cache=dcache, block_ids=torch.as_tensor(block_ids), block_size=bs,
+                        total_tokens=T, prefill_len=0, protect_prefill=False, layer_idx=l,
+                        round_start=p["round_start"], budget_total=p["budget"])
+        assert res["mode"] == mode
+        ref_keep = torch.from_numpy(selector_cases[f"{name}/keep_l{l}"]).long()
+        got = res["indices"].cpu()
+        same = set(got.flatten().tolist()) == set(ref_keep.flatten().tolist()) if mode == "shared" else None
+        if mode == "shared":
+            diff = set(got.tolist()) ^ set(ref_keep.tolist())
+            assert len(diff) <= 4, diff   # near-ties at the cut-off only
+        else:
+            for h in range(got.shape[0]):
+                diff = set(got[h].tolist()) ^ set(ref_keep[h].tolist())
+                assert len(diff) <= 4, (h, diff)
+        # compaction through the mirrored API, whole region equal to the checker with the same keep set
+        exp = c.clone()
+        if mode == "shared":
+            n = kv_compaction.compact_request_kv_in_place(dcache, block_ids, bs, res["indices"], T)
+            oracle.compact_shared(exp, block_ids, bs, got, T, preserve_dropped_tokens=True, kv_axis=0)
+        else:
+            n = kv_compaction.compact_request_kv_in_place_per_head(dcache, block_ids, bs, res["indices"], T)
+            oracle.compact_per_head(exp, block_ids, bs, got, T, preserve_dropped_tokens=True, kv_axis=0)
+        assert n == p["budget"]
+        assert torch.equal(dcache.cpu().view(torch.int16), exp.view(torch.int16))
+
+
+def test_compaction_api_errors():
+    g = torch.Generator().manual_seed(3)
+    cache = torch.randn((2, 8, 16, 2, 128), generator=g).to(torch.bfloat16).to(DEV)
+    ids = [3, 1, 5, 2]
+    with pytest.raises(IndexError):
+        kv_compaction.compact_request_kv_in_place_per_head(cache, ids, 16, torch.tensor([[0, 70], [1, 2]]), 64)
+    with pytest.raises(ValueError, match="duplicates"):
+        kv_compaction.compact_request_kv_in_place_per_head(cache, ids, 16, torch.tensor([[1, 1], [1, 2]]), 64)
+    with pytest.raises(ValueError, match="head count"):
+        kv_compaction.compact_request_kv_in_place_per_head(cache, ids, 16, torch.tensor([[1, 2]]), 64)
+    with pytest.raises(ValueError, match="2D"):
+        kv_compaction.compact_request_kv_in_place_per_head(cache, ids, 16, torch.tensor([1, 2]), 64)
+    with pytest.raises(IndexError):
+        kv_compaction.compact_request_kv_in_place(cache, ids, 16, [0, 5, 64], 64)
+    with pytest.raises(ValueError, match="duplicates"):
+        kv_compaction.compact_request_kv_in_place(cache, ids, 16, [0, 5, 5], 64)
+    with pytest.raises(IndexError):
+        kv_compaction.compact_request_kv_in_place(cache, ids, 16, [0, 5, 9], 100)   # needs 7 blocks, 4 given
+    assert kv_compaction.compact_request_kv_in_place(cache, ids, 16, [], 64) == 0
+    before = cache.clone()
+    assert kv_compaction.compact_request_kv_in_place(cache, ids, 16, list(range(10)), 64) == 10   # identity
+    assert torch.equal(cache, before)
+    amb = torch.zeros((2, 2, 16, 2, 128), dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(ValueError, match="Ambiguous"):
+        kv_compaction.compact_request_kv_in_place(amb, [0, 1], 16, [1, 2], 20)
+
+
+def test_hook_on_gpu_matches_reference_results(manifest, tmp_path):
+    hc = manifest["hook_cases"]
+    p, want = hc["params"], hc["results"]
+    stats, caches, block_ids = build_paged_case(p)
+    sp = tmp_path / "s.pt"
+    synth.save_stats_pt(stats, sp)
+    T = p["total_tokens"]
+    for preserve in (True, False):
+        dc = [c.to(DEV) for c in caches]
+        cfg = TriAttentionRuntimeConfig(kv_budget=p["budget"], window_size=p["window"], sparse_stats_path=sp,
+                                        preserve_dropped_tokens=preserve)
+        runner = types.SimpleNamespace(
+            requests={"r0": types.SimpleNamespace(block_ids=(list(block_ids),), num_computed_tokens=T),
+                      "r1": types.SimpleNamespace(block_ids=(list(block_ids[:8]),), num_computed_tokens=100)},
+            kv_caches=dc, cache_config=types.SimpleNamespace(block_size=p["block_size"]))
+        hook_mod.install_runner_compression_hook(runner, cfg)
+        hook = runner.triattention_apply_compression
+        so = types.SimpleNamespace(num_scheduled_tokens={"r0": 1, "r1": 1})
+
+        def sig(req, est, **kw):
+            base = dict(req_id=req, should_compress=True, reason="length_threshold", estimated_cache_len=est, step=1,
+                        kv_usage=None, protect_prefill=False, prefill_len=0, scheduled_tokens=1)
+            base.update(kw)
+            return CompressionSignal(**base)
+
+        assert hook(req_id="r1", signal=sig("r1", 101), scheduler_output=so) == want["under_budget"]
+        assert hook(req_id="zz", signal=sig("zz", 500), scheduler_output=so) == want["not_found"]
+        assert hook(req_id="r0", signal=sig("r0", T + 1, protect_prefill=True, prefill_len=400),
+                    scheduler_output=so) == want["prefill_exceeds"]
+        assert hook(req_id="r0", signal=sig("r0", T + 1), scheduler_output=so) == want["compacted"]
+        assert [list(g) for g in runner.requests["r0"].block_ids] == want["block_ids_after"]
+        if preserve:
+            # same keep set as the reference (no near-tie at the cut-off in this fixture): byte-identical caches
+            assert [tensor_sha(c) for c in dc] == p["cache_out_sha256"]
+        runner.requests["r0"].num_computed_tokens = T + 40
+        assert hook(req_id="r0", signal=sig("r0", 256 + 40 + 1), scheduler_output=so) == want["deferred"]
+
+
+def test_batched_engine_equals_per_request_calls():
+    """Ragged batch (different lengths, round starts, budgets) in one native call == one call per request."""
+    gen = torch.Generator().manual_seed(21)
+    L, Hq, Hkv, D, bs = 3, 8, 2, 128, 16
+    inv = synth.rope_inv_freq(D, 1e6)
+    stats = synth.make_stats(L, Hq, D, inv, gen)
+    lens, budgets, starts = [700, 37, 2500, 1024], [256, 64, 512, 1024], [700, 5000, 2500, 70000]
+    nblk = [(t + bs - 1) // bs for t in lens]
+    perm = synth.random_block_ids(sum(nblk), sum(nblk) + 9, gen)
+    ids, o = [], 0
+    for n in nblk:
+        ids.append(perm[o:o + n])
+        o += n
+    caches = []
+    for _ in range(L):
+        c = synth.make_paged_layer(sum(nblk) + 9, bs, Hkv, D, kv_axis=1)
+        for b, t in enumerate(lens):
+            synth.write_tokens_to_paged(c, 1, ids[b], bs, synth.make_rotated_keys(Hkv, t, D, inv, gen),
+                                        synth.make_values(Hkv, t, D, gen))
+        caches.append(c)
+    dstats = device_stats(stats, oracle.geometric_offsets())
+    batched = [c.to(DEV) for c in caches]
+    comp = engine.PagedCompressor(dstats, window=32)
+    res = comp.compress(ops.PagedCacheView.from_layers(batched, kv_axis=1), ids, lens, starts, budgets)
+    assert res.device_status == 0 and res.keep_counts == [256, 37, 512, 1024]
+    single = [c.to(DEV) for c in caches]
+    view1 = ops.PagedCacheView.from_layers(single, kv_axis=1)
+    for b in range(len(lens)):
+        r1 = engine.PagedCompressor(dstats, window=32).compress(view1, [ids[b]], [lens[b]], [starts[b]], [budgets[b]])
+        k = r1.keep_counts[0]
+        assert torch.equal(r1.keep[0, :, :k], res.keep[b, :, :k])
+        assert r1.kept_block_ids[0] == res.kept_block_ids[b] == ids[b][: (k + bs - 1) // bs]
+        assert r1.removed_block_ids[0] == res.removed_block_ids[b]
+    for a, c in zip(batched, single):
+        assert torch.equal(a, c)
+    # the request that fits its budget is untouched and keeps the identity set
+    assert torch.equal(res.keep[1, :, :37].cpu(), torch.arange(37, dtype=torch.int32).expand(Hkv, -1))
+    with pytest.raises(IndexError):
+        comp.compress(ops.PagedCacheView.from_layers(batched, kv_axis=1), [ids[0][:3]], [700], [700], [256])
+
+
+def test_dense_api(manifest, score_cases, tmp_path):
+    a = score_cases
+    v = manifest["score_cases"]["variants"][0]
+    keys = np_to_bf16(a["keys_0"]).to(DEV)
+    cfg = TriAttentionConfig(score_aggregation=v["aggregation"], rope_style=v["rope_style"])
+    hs = {"q_mean_complex": torch.stack([torch.from_numpy(a["q_mean_real"]), torch.from_numpy(a["q_mean_imag"])], -1).to(DEV),
+          "q_abs_mean": torch.from_numpy(a["q_abs_mean"]).to(DEV)}
+    got = compute_scores(keys, None, hs, torch.from_numpy(a["omega"]).to(DEV), torch.from_numpy(a["offsets"]).to(DEV),
+                         torch.from_numpy(a["freq_scale_sq"]).to(DEV), cfg, round_start=v["round_start"])
+    ok, worst = score_tolerance_ok(got.cpu(), torch.from_numpy(a["scores_0"]))
+    assert ok, worst
+    with pytest.raises(_native.NativeLibraryError):
+        compute_scores(keys.cpu(), None, hs, None, None, None, cfg, round_start=1)
+
+    # dense compress(): budget tokens per head, window kept, gathered K/V consistent with the indices
+    gen = torch.Generator().manual_seed(5)
+    H, T, D = 4, 600, 128
+    inv = synth.rope_inv_freq(D, 1e6)
+    st = synth.make_stats(1, H, D, inv, gen)
+    sp = tmp_path / "d.pt"
+    synth.save_stats_pt(st, sp)
+    comp = TriAttentionCompressor(TriAttentionConfig(kv_budget=128, divide_length=64, window_size=16, stats_path=sp,
+                                                     device=torch.device(DEV)))
+    k = synth.make_rotated_keys(H, T, D, inv, gen).permute(1, 0, 2).unsqueeze(0).to(DEV)
+    vv = synth.make_values(H, T, D, gen).permute(1, 0, 2).unsqueeze(0).to(DEV)
+    ck, cv, idx = comp.compress(k, vv, layer_idx=0)
+    assert ck.shape == (1, H, 128, D) and idx.shape == (1, H, 128)
+    assert bool((idx[0, :, -16:] == torch.arange(T - 16, T, device=DEV)).all())
+    assert torch.equal(ck[0, 2], k[0, 2, idx[0, 2]]) and torch.equal(cv[0, 1], vv[0, 1, idx[0, 1]])
+    raw = oracle.score_keys_reference(k.cpu(), st.q_mean_real[0], st.q_mean_imag[0], st.q_abs_mean[0],
+                                      torch.ones(H, D // 2), inv, oracle.geometric_offsets(), T)[0]
+    mean, std = oracle.streaming_moments(raw, chunk_tokens=T)
+    z = (raw - mean[:, None]) / std[:, None]
+    z[:, -16:] = float("inf")
+    ok, nd = keep_sets_match_modulo_near_ties(idx[0].cpu(), oracle.topk_lowest_index(z, 128), z)
+    assert ok, nd
+    small_k, _, small_idx = comp.compress(k[:, :, :100], vv[:, :, :100])
+    assert small_k.shape[2] == 100 and torch.equal(small_idx.cpu(), torch.arange(100))

@@ -58,10 +58,14 @@ constexpr int kScoreConsumerWarps = 8;
 constexpr int kScoreConsumerThreads = kScoreConsumerWarps * 32;
 constexpr int kScoreThreadsWS = kScoreConsumerThreads;  // the last warp to release a stage refills it
 constexpr int kMaxStages = 8;
+constexpr int kMaxPrefetchedBlocks = 1024;
+#ifndef TRIATTN_SCORE_MIN_CTAS
+#define TRIATTN_SCORE_MIN_CTAS 2
+#endif
 
 // GP = query-head slots per virtual head (1, 2 or 4).  p.gp_total = slots per KV head in the raw layout.
 template <int D, int GP, bool INTERLEAVED>
-__global__ void __launch_bounds__(kScoreThreadsWS, 2)
+__global__ void __launch_bounds__(kScoreThreadsWS, TRIATTN_SCORE_MIN_CTAS)
 score_paged_mean_kernel(const __grid_constant__ ScoreParams p) {
   constexpr int F = D / 2;
   constexpr int FPT = F / kLPK;  // frequencies per lane: 4 (D=128) or 2 (D=64)
@@ -75,6 +79,7 @@ score_paged_mean_kernel(const __grid_constant__ ScoreParams p) {
   __shared__ __align__(16) ScoreItem s_items[kMaxScoreItems];
   __shared__ __align__(8) uint64_t full_bar[kMaxStages];
   __shared__ unsigned int s_released[kMaxStages];  // warps that released each stage so far (monotonic)
+  __shared__ int s_bt[kMaxPrefetchedBlocks];  // this CTA's slice of the block table
   __shared__ int s_err;
 
   const int tid = threadIdx.x;
@@ -118,21 +123,39 @@ score_paged_mean_kernel(const __grid_constant__ ScoreParams p) {
     it.pad = 0;
     s_items[i] = it;
   }
+  // block ids of this CTA's tiles (bounds-checked once here), so the refill path never waits on global memory
+  const int32_t* bt = p.block_table + (size_t)b * p.max_blocks;
+  const int my_blocks = min(my_tiles * p.mb, nblk - tile0 * p.mb);
+  const bool bt_in_smem = my_blocks <= kMaxPrefetchedBlocks;
+  if (bt_in_smem) {
+    for (int i = tid; i < my_blocks; i += kScoreThreadsWS) {
+      int blk = bt[tile0 * p.mb + i];
+      if ((unsigned)blk >= (unsigned)p.num_blocks) {
+        flag_status(p.status, TRIATTN_DEV_BAD_BLOCK_ID);
+        blk = 0;
+      }
+      s_bt[i] = blk;
+    }
+  }
   __syncthreads();
 
   // fetch the cache blocks of stage-tile `it` (called by one lane)
   const unsigned char* kbase = reinterpret_cast<const unsigned char*>(p.k_ptrs[l]);
-  const int32_t* bt = p.block_table + (size_t)b * p.max_blocks;
   auto issue = [&](int it, int stage) {
     const uint32_t bar = smem_u32(&full_bar[stage]);
     const int blk0 = (tile0 + it) * p.mb;
     const int nb = min(p.mb, nblk - blk0);
     mbar_arrive_expect_tx(bar, (uint32_t)(nb * p.block_bytes));
     for (int j = 0; j < nb; ++j) {
-      int blk = bt[blk0 + j];
-      if ((unsigned)blk >= (unsigned)p.num_blocks) {
-        flag_status(p.status, TRIATTN_DEV_BAD_BLOCK_ID);
-        blk = 0;
+      int blk;
+      if (bt_in_smem) {
+        blk = s_bt[it * p.mb + j];
+      } else {
+        blk = bt[blk0 + j];
+        if ((unsigned)blk >= (unsigned)p.num_blocks) {
+          flag_status(p.status, TRIATTN_DEV_BAD_BLOCK_ID);
+          blk = 0;
+        }
       }
       bulk_copy_g2s(smem_u32(smem_tiles + (size_t)stage * stage_bytes + (size_t)j * p.block_bytes),
                     kbase + (long long)blk * p.block_stride_bytes, (uint32_t)p.block_bytes, bar);
@@ -207,15 +230,8 @@ score_paged_mean_kernel(const __grid_constant__ ScoreParams p) {
 
   // one (virtual head, batch of NT tokens) item; `checked` = the stage may hold tokens beyond seq_len.
   // `live` is false only for the padding item of a group when n_items is not a multiple of the group count.
-  auto process_item = [&](unsigned tile_off, const ScoreItem it, int tile_tok0, bool live, auto checked) {
+  auto compute_item = [&](const unsigned base, const int gtok0, bool live, auto checked) {
     constexpr bool CHECK = decltype(checked)::value;
-    if (__any_sync(kFull, it.vhead != cur_vh)) {  // warp-uniform: both key groups switch together
-      flush_moments();
-      load_weights(it.vhead);
-      cur_vh = it.vhead;
-    }
-    const unsigned base = tile_off + (unsigned)it.smem_off;
-    const int gtok0 = tile_tok0 + it.tok_rel;
 
     float2 acc[NT][GP];
 #pragma unroll
@@ -303,7 +319,33 @@ score_paged_mean_kernel(const __grid_constant__ ScoreParams p) {
     }
   };
 
+  // general path: the virtual head may change from item to item
+  auto process_item = [&](unsigned tile_off, const ScoreItem it, int tile_tok0, bool live, auto checked) {
+    if (__any_sync(kFull, it.vhead != cur_vh)) {  // warp-uniform: both key groups switch together
+      flush_moments();
+      load_weights(it.vhead);
+      cur_vh = it.vhead;
+    }
+    compute_item(tile_off + (unsigned)it.smem_off, tile_tok0 + it.tok_rel, live, checked);
+  };
+
   const int slots = (n_items + NG - 1) / NG;  // items per key group and stage (uniform over the CTA)
+  // common case: every key group keeps one virtual head for the whole CTA and has at most kMaxFixedSlots items
+  // per stage; its item descriptors and weights then live in registers for the whole kernel
+  constexpr int kMaxFixedSlots = 4;
+  const bool fixed = (NG % nvh) == 0 && slots <= kMaxFixedSlots && slots * NG == n_items;
+  unsigned f_off[kMaxFixedSlots];
+  int f_tok[kMaxFixedSlots];
+#pragma unroll
+  for (int sl = 0; sl < kMaxFixedSlots; ++sl) {
+    const ScoreItem d = s_items[min(gid + sl * NG, n_items - 1)];
+    f_off[sl] = (unsigned)d.smem_off;
+    f_tok[sl] = d.tok_rel;
+  }
+  if (fixed) {
+    cur_vh = gid % nvh;
+    load_weights(cur_vh);
+  }
   int stage = 0;
   uint32_t parity = 0;
   unsigned release_target = (unsigned)kScoreConsumerWarps;
@@ -317,7 +359,11 @@ score_paged_mean_kernel(const __grid_constant__ ScoreParams p) {
     }
     const unsigned tile_off = (unsigned)(stage * stage_bytes);
     const int tile_tok0 = (tile0 + it) * stage_tokens;
-    if (tile_tok0 + stage_tokens <= seq_len && slots * NG == n_items) {
+    if (fixed && tile_tok0 + stage_tokens <= seq_len) {
+#pragma unroll
+      for (int sl = 0; sl < kMaxFixedSlots; ++sl)
+        if (sl < slots) compute_item(tile_off + f_off[sl], tile_tok0 + f_tok[sl], true, std::false_type{});
+    } else if (tile_tok0 + stage_tokens <= seq_len && slots * NG == n_items) {
       for (int sl = 0; sl < slots; ++sl)
         process_item(tile_off, s_items[gid + sl * NG], tile_tok0, true, std::false_type{});
     } else {
