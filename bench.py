@@ -363,11 +363,14 @@ def run_ours(args, world, rank, local):
     status_bits = int(d_status.item())
 
     # end to end through the public batched API: host lists -> pinned -> H2D, kernels, D2H of the status word
+    import numpy as np
+    host_block_ids = [np.asarray(ids, dtype=np.int32) for ids in block_ids]  # host-side block tables, as an engine keeps them
+
     def e2e_once():
         saver.restore()
         torch.cuda.synchronize()
         t0 = time.perf_counter()
-        res = comp.compress(view, block_ids, seq_lens, round_starts, budgets)
+        res = comp.compress(view, host_block_ids, seq_lens, round_starts, budgets)
         torch.cuda.synchronize()
         return time.perf_counter() - t0, res
 

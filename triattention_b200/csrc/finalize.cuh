@@ -6,7 +6,7 @@
 
 namespace triattn {
 
-// mean_std[l][b][h] = (mean, std_safe) from (sum, sumsq): mean = S1/n, var = (S2 - n*mean^2)/(n-1)
+// mean_std[l][b][h] = (mean, 1/std_safe) from (sum, sumsq): mean = S1/n, var = (S2 - n*mean^2)/(n-1)
 // clamped at 0, std < 1e-8 -> 1 (streaming formula of the reference selector), evaluated in double.
 __global__ void moments_to_mean_std_kernel(const double* __restrict__ moments, const int32_t* __restrict__ seq_lens,
                                            int L, int B, int Hq, int t_pad, float* __restrict__ mean_std) {
@@ -22,12 +22,12 @@ __global__ void moments_to_mean_std_kernel(const double* __restrict__ moments, c
   float sd = (float)sqrt(var);
   if (sd < 1e-8f) sd = 1.0f;
   mean_std[2 * (size_t)i] = (float)mean;
-  mean_std[2 * (size_t)i + 1] = sd;
+  mean_std[2 * (size_t)i + 1] = 1.0f / sd;  // the finalize kernel multiplies by the reciprocal
 }
 
 struct FinalizeParams {
   const float* raw;        // [L, B, Hkv, t_pad, gp]
-  const float* mean_std;   // [L, B, Hq, 2]
+  const float* mean_std;   // [L, B, Hq, 2]: (mean, 1/std)
   const int32_t* seq_lens;
   const int32_t* prefill_lens;  // may be null
   float* out;              // [Lo, B, Ho, t_pad]
@@ -51,6 +51,7 @@ __global__ void __launch_bounds__(256) finalize_scores_kernel(const __grid_const
   const int h_end = p.head_reduce != TRIATTN_REDUCE_NONE ? p.Hkv : ho + 1;
   const bool vec4 = (gp & 3) == 0;
   float acc = 0.f;
+#pragma unroll 4
   for (int l = 0; l < p.L; ++l) {
     float lv = -INFINITY;
     for (int kvh = h_begin; kvh < h_end; ++kvh) {
@@ -74,7 +75,7 @@ __global__ void __launch_bounds__(256) finalize_scores_kernel(const __grid_const
           for (int j = 0; j < 4; ++j) {
             if (j0 + j < p.g) {
               float z = s[j];
-              if (p.normalize) z = __fdiv_rn(__fsub_rn(z, __ldg(ms + 2 * (j0 + j))), __ldg(ms + 2 * (j0 + j) + 1));
+              if (p.normalize) z = __fmul_rn(__fsub_rn(z, __ldg(ms + 2 * (j0 + j))), __ldg(ms + 2 * (j0 + j) + 1));
               mx = fmaxf(mx, z);
               sum = __fadd_rn(sum, z);
             }

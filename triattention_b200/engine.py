@@ -14,6 +14,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Optional, Sequence
 
+import numpy as np
 import torch
 
 from . import _native, ops
@@ -108,17 +109,18 @@ class PagedCompressor:
         n_ints = B * max_blocks + 4 * B + 4
         self._buffers(n_ints, ws_bytes + keep_bytes + 256, view.device)
         st = self._staging[:n_ints]
-        st.zero_()
-        bt_host = st[: B * max_blocks].view(B, max_blocks)
+        sn = st.numpy()  # the pinned staging buffer, filled through numpy (block ids may be lists or int arrays)
+        sn[:] = 0
+        bt_host = sn[: B * max_blocks].reshape(B, max_blocks)
         for b, ids in enumerate(block_ids):
             nb = num_required_blocks(int(seq_lens[b]), bs)
-            bt_host[b, :nb] = torch.as_tensor(list(ids[:nb]), dtype=torch.int32)
+            bt_host[b, :nb] = ids[:nb]
         off = B * max_blocks
-        st[off : off + B] = torch.as_tensor(list(seq_lens), dtype=torch.int32)
-        st[off + B : off + 2 * B] = torch.as_tensor(list(round_starts), dtype=torch.int32)
-        st[off + 2 * B : off + 3 * B] = torch.as_tensor(keep_counts, dtype=torch.int32)
+        sn[off : off + B] = seq_lens
+        sn[off + B : off + 2 * B] = round_starts
+        sn[off + 2 * B : off + 3 * B] = keep_counts
         if prefill_lens is not None:
-            st[off + 3 * B : off + 4 * B] = torch.as_tensor(list(prefill_lens), dtype=torch.int32)
+            sn[off + 3 * B : off + 4 * B] = prefill_lens
         dm = self._dev_meta[:n_ints]
         dm.copy_(st, non_blocking=True)
         bt = dm[: B * max_blocks].view(B, max_blocks)
@@ -138,8 +140,11 @@ class PagedCompressor:
         kept, removed = [], []
         for b, ids in enumerate(block_ids):
             req = num_required_blocks(keep_counts[b], bs)
-            ids = [int(x) for x in ids]
-            kept.append(ids[:req])
-            removed.append(ids[req:])
+            if isinstance(ids, np.ndarray):
+                kept.append(ids[:req].tolist())
+                removed.append(ids[req:].tolist())
+            else:
+                kept.append([int(x) for x in ids[:req]])
+                removed.append([int(x) for x in ids[req:]])
         return CompressResult(keep=keep, keep_counts=keep_counts, kept_block_ids=kept, removed_block_ids=removed,
                               device_status=status, h2d_bytes=n_ints * 4, d2h_bytes=4)
