@@ -1,0 +1,187 @@
+"""GPU checks at the sizes and shapes of the benchmark configurations.
+
+Small enough for the CPU checker: full parity.  Full-size shapes: size-independent properties (keep rows
+strictly ascending and in range, recent window kept, compacted prefix == gather of the original cache by the
+keep set, block tables truncated) evaluated with torch on the device.
+"""
+from __future__ import annotations
+
+import pytest
+import torch
+
+import oracle
+from gpu_utils import device_stats, keep_sets_match_modulo_near_ties
+from triattention_b200 import engine, ops, synth
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+BS = 16
+
+
+def _build(L, Hq, Hkv, D, lens, gen, theta=1e6, llama3=None, kv_axis=0, positions=None):
+    inv = synth.rope_inv_freq(D, theta, llama3)
+    stats = synth.make_stats(L, Hq, D, inv, gen)
+    nblk = [(t + BS - 1) // BS for t in lens]
+    total = sum(nblk) + 7
+    perm = synth.random_block_ids(sum(nblk), total, gen)
+    ids, o = [], 0
+    for n in nblk:
+        ids.append(perm[o:o + n])
+        o += n
+    caches = []
+    for _ in range(L):
+        c = synth.make_paged_layer(total, BS, Hkv, D, kv_axis=kv_axis)
+        for b, t in enumerate(lens):
+            synth.write_tokens_to_paged(c, kv_axis, ids[b], BS, synth.make_rotated_keys(Hkv, t, D, inv, gen),
+                                        synth.make_values(Hkv, t, D, gen))
+        caches.append(c)
+    return stats, caches, ids, inv
+
+
+def _stats_dict(stats):
+    return {l: {"q_mean_real": stats.q_mean_real[l], "q_mean_imag": stats.q_mean_imag[l],
+                "q_abs_mean": stats.q_abs_mean[l], "freq_scale_sq": torch.ones_like(stats.q_abs_mean[l])}
+            for l in range(stats.num_layers)}
+
+
+def test_config0_full_size_parity():
+    """BASELINE config 0: 1 layer, 32q/8kv heads, D 128, 4096 tokens at positions 0..4095, query position 4096,
+    budget 2048, window 128."""
+    gen = torch.Generator().manual_seed(synth.seed_for(0, 0))
+    T, budget, window = 4096, 2048, 128
+    stats, caches, ids, inv = _build(1, 32, 8, 128, [T], gen)
+    ref_final = oracle.final_scores_group_per_head([(0, caches[0], ids[0], BS)], _stats_dict(stats), inv,
+                                                   oracle.geometric_offsets(), T, T, window_size=window, kv_axis=0)
+    ref_keep = oracle.topk_lowest_index(ref_final, budget)
+    dc = [c.to(DEV) for c in caches]
+    comp = engine.PagedCompressor(device_stats(stats, oracle.geometric_offsets()), window=window)
+    res = comp.compress(ops.PagedCacheView.from_layers(dc, kv_axis=0), ids, [T], [T], [budget])
+    assert res.device_status == 0
+    keep = res.keep[0].cpu().long()
+    ok, nd = keep_sets_match_modulo_near_ties(keep, ref_keep, ref_final)
+    assert ok, nd
+    exp = caches[0].clone()
+    oracle.compact_per_head(exp, ids[0], BS, keep, T, preserve_dropped_tokens=False, kv_axis=0)
+    assert torch.equal(dc[0].cpu().view(torch.int16), exp.view(torch.int16))
+    assert res.kept_block_ids[0] == ids[0][:128] and res.removed_block_ids[0] == ids[0][128:]
+
+
+def test_group8_head_dim128_parity():
+    """Qwen3-32B head geometry under TP8: 1 local KV head, 8 query heads per KV head, D 128."""
+    gen = torch.Generator().manual_seed(synth.seed_for(2, 0))
+    T, budget, window = 1500, 512, 128
+    stats, caches, ids, inv = _build(2, 8, 1, 128, [T], gen)
+    layers = [(l, c, ids[0], BS) for l, c in enumerate(caches)]
+    ref_final = oracle.final_scores_group_per_head(layers, _stats_dict(stats), inv, oracle.geometric_offsets(), T, T,
+                                                   window_size=window, kv_axis=0)
+    dc = [c.to(DEV) for c in caches]
+    comp = engine.PagedCompressor(device_stats(stats, oracle.geometric_offsets()), window=window)
+    res = comp.compress(ops.PagedCacheView.from_layers(dc, kv_axis=0), ids, [T], [T], [budget])
+    assert res.device_status == 0
+    ok, nd = keep_sets_match_modulo_near_ties(res.keep[0].cpu().long(), oracle.topk_lowest_index(ref_final, budget), ref_final)
+    assert ok, nd
+
+
+def test_decode_interleaved_rounds_match_checker():
+    """Config-3 style: llama3-scaled RoPE, ragged requests, repeated compress -> append -> compress with
+    round_start = absolute tokens seen; the device cache and the CPU cache evolve in lockstep."""
+    gen = torch.Generator().manual_seed(synth.seed_for(3, 0))
+    llama3 = dict(factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0, original_max_position_embeddings=8192)
+    L, Hq, Hkv, D, budget, window, slack = 2, 8, 2, 128, 256, 32, 32
+    lens = [700, 1333, 300]
+    inv = synth.rope_inv_freq(D, 5e5, llama3)
+    stats = synth.make_stats(L, Hq, D, inv, gen)
+    cap = [(max(lens) + 3 * slack + BS) // BS for _ in lens]
+    total = sum(cap) + 3
+    perm = synth.random_block_ids(sum(cap), total, gen)
+    ids, o = [], 0
+    for n in cap:
+        ids.append(perm[o:o + n])
+        o += n
+    cpu = [synth.make_paged_layer(total, BS, Hkv, D, kv_axis=0) for _ in range(L)]
+    for c in cpu:
+        for b, t in enumerate(lens):
+            synth.write_tokens_to_paged(c, 0, ids[b], BS, synth.make_rotated_keys(Hkv, t, D, inv, gen),
+                                        synth.make_values(Hkv, t, D, gen))
+    dev = [c.to(DEV) for c in cpu]
+    view = ops.PagedCacheView.from_layers(dev, kv_axis=0)
+    comp = engine.PagedCompressor(device_stats(stats, oracle.geometric_offsets()), window=window)
+    sd = _stats_dict(stats)
+    cur = list(lens)          # tokens currently cached per request
+    seen = list(lens)         # absolute tokens computed so far (round_start)
+    for rnd in range(3):
+        act = [b for b in range(len(lens)) if cur[b] >= budget + slack]
+        assert act
+        res = comp.compress(view, [ids[b] for b in act], [cur[b] for b in act], [seen[b] for b in act],
+                            [budget] * len(act))
+        assert res.device_status == 0
+        for j, b in enumerate(act):
+            layers = [(l, c, ids[b], BS) for l, c in enumerate(cpu)]
+            fin = oracle.final_scores_group_per_head(layers, sd, inv, oracle.geometric_offsets(), cur[b], seen[b],
+                                                     window_size=window, kv_axis=0)
+            keep = res.keep[j].cpu().long()
+            ok, nd = keep_sets_match_modulo_near_ties(keep, oracle.topk_lowest_index(fin, budget), fin)
+            assert ok, (rnd, b, nd)
+            for c in cpu:   # the CPU cache follows the device's keep set so that later rounds stay comparable
+                oracle.compact_per_head(c, ids[b], BS, keep, cur[b], preserve_dropped_tokens=False, kv_axis=0)
+            cur[b] = budget
+        for l in range(L):
+            assert torch.equal(dev[l].cpu().view(torch.int16), cpu[l].view(torch.int16)), (rnd, l)
+        # decode: every request appends `slack` new tokens at its absolute positions
+        for b in range(len(lens)):
+            pos = torch.arange(seen[b], seen[b] + slack, dtype=torch.float32)
+            for l in range(L):
+                k_new = synth.make_rotated_keys(Hkv, slack, D, inv, gen, positions=pos)
+                v_new = synth.make_values(Hkv, slack, D, gen)
+                tok = torch.arange(cur[b], cur[b] + slack)
+                blk = torch.as_tensor(ids[b])[tok // BS]
+                cpu[l][0][blk, tok % BS] = k_new
+                cpu[l][1][blk, tok % BS] = v_new
+                dev[l][0][blk.to(DEV), (tok % BS).to(DEV)] = k_new.to(DEV)
+                dev[l][1][blk.to(DEV), (tok % BS).to(DEV)] = v_new.to(DEV)
+            cur[b] += slack
+            seen[b] += slack
+
+
+@pytest.mark.parametrize("hkv,g,batch", [(8, 4, 2), (1, 8, 4)])
+def test_full_length_properties(hkv, g, batch):
+    """32768-token requests (config 1 / config 2 per-GPU head geometry): properties that need no CPU checker."""
+    gen = torch.Generator(device=DEV).manual_seed(1234)
+    cgen = torch.Generator().manual_seed(1234)
+    L, D, T, budget, window = 2, 128, 32768, 2048, 128
+    inv = synth.rope_inv_freq(D, 1e6)
+    stats = synth.make_stats(L, hkv * g, D, inv, cgen)
+    nblk = T // BS
+    total = batch * nblk + 5
+    perm = torch.randperm(total - 1, generator=cgen)[: batch * nblk] + 1
+    ids = [perm[b * nblk:(b + 1) * nblk].tolist() for b in range(batch)]
+    caches = [(torch.randn((2, total, BS, hkv, D), generator=gen, device=DEV) * 2).to(torch.bfloat16) for _ in range(L)]
+    before = [c.clone() for c in caches]
+    comp = engine.PagedCompressor(device_stats(stats, oracle.geometric_offsets()), window=window)
+    res = comp.compress(ops.PagedCacheView.from_layers(caches, kv_axis=0), ids, [T] * batch, [T] * batch, [budget] * batch)
+    assert res.device_status == 0
+    keep = res.keep.long()                                  # [B, Hkv, k]
+    assert keep.shape == (batch, hkv, budget)
+    assert bool((keep[..., 1:] > keep[..., :-1]).all()) and int(keep.min()) >= 0 and int(keep.max()) < T
+    assert bool((keep[..., -window:] == torch.arange(T - window, T, device=DEV)).all())
+    hidx = torch.arange(hkv, device=DEV).view(hkv, 1)
+    for b in range(batch):
+        bt = torch.as_tensor(ids[b], device=DEV)
+        src_blk, src_off = bt[keep[b] // BS], keep[b] % BS             # [Hkv, k]
+        dst = torch.arange(budget, device=DEV)
+        dst_blk, dst_off = bt[dst // BS], dst % BS
+        for l in range(L):
+            for kv in (0, 1):
+                want = before[l][kv][src_blk, src_off, hidx]            # [Hkv, k, D]
+                got = caches[l][kv][dst_blk, dst_off].permute(1, 0, 2)  # [Hkv, k, D]
+                assert torch.equal(got, want), (b, l, kv)
+            # nothing outside the kept prefix of this request changed
+            tail = bt[budget // BS:]
+            assert torch.equal(caches[l][:, tail], before[l][:, tail])
+        assert res.kept_block_ids[b] == ids[b][: budget // BS]
+    # idempotence: compressing the compacted prefix with budget == length is the identity
+    snap = [c.clone() for c in caches]
+    res2 = comp.compress(ops.PagedCacheView.from_layers(caches, kv_axis=0), [i[: budget // BS] for i in ids],
+                         [budget] * batch, [T] * batch, [budget] * batch)
+    assert bool((res2.keep.long() == torch.arange(budget, device=DEV)).all())
+    assert all(torch.equal(a, c) for a, c in zip(snap, caches))

@@ -11,8 +11,14 @@
 
 namespace triattn {
 
-constexpr int kCompactThreads = 256;
-constexpr int kCompactUnroll = 4;
+#ifndef TRIATTN_COMPACT_THREADS
+#define TRIATTN_COMPACT_THREADS 256
+#endif
+constexpr int kCompactThreads = TRIATTN_COMPACT_THREADS;
+#ifndef TRIATTN_COMPACT_UNROLL
+#define TRIATTN_COMPACT_UNROLL 2
+#endif
+constexpr int kCompactUnroll = TRIATTN_COMPACT_UNROLL;
 
 struct CompactParams {
   void* const* k_ptrs;  // [L]
