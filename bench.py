@@ -62,6 +62,12 @@ def measured_peaks():
     return 6650.0, "fallback"
 
 
+# DRAM traffic of the score kernel per key from the ncu capture summarised in
+# profiles/score_paged_mean_kernel_c1_2layers.md (dram__bytes_read + dram__bytes_write = 1.0743 GB + 64.7 MB for
+# 4 194 304 keys); traffic grows in proportion to the keys scored, so a full launch is this figure x its keys.
+SCORE_DRAM_BYTES_PER_KEY_NCU = (1.074314e9 + 64.68e6) / 4194304.0
+
+
 def algorithmic_bytes_per_key(T: int, k: int) -> float:
     """K read once (256 B) + K and V of the kept tokens read and written (4 x 256 B x k/T)."""
     return 256.0 + 1024.0 * k / T
@@ -425,7 +431,10 @@ def run_ours(args, world, rank, local):
         "step_hbm_gbs": bytes_step / (step_ms * 1e-3) / 1e9, "step_hbm_frac": bytes_step / (step_ms * 1e-3) / 1e9 / peak,
         "stage_ms": stage,
         "roofline": {"kernel": "score_paged_mean_kernel", "bound": "hbm", "achieved": achieved, "peak": peak,
-                     "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None},
+                     "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
+                     "traffic": (keys_per_gpu * SCORE_DRAM_BYTES_PER_KEY_NCU
+                                 if (c["D"], c["g"], c["Hkv_local"]) == (128, 4, 8) else None),
+                     "traffic_note": "bytes per launch, scaled by keys from a 2-layer ncu capture of the same shape"},
         "e2e": {"value": keys_per_gpu * world / e2e_s, "unit": UNIT, "h2d_bytes_per_step": res.h2d_bytes,
                 "d2h_bytes_per_step": res.d2h_bytes, "ms_per_step": e2e_s * 1e3},
         "gpu_launches": 7 * args.steps,

@@ -141,12 +141,16 @@ score_paged_mean_kernel(const __grid_constant__ ScoreParams p) {
 
   // fetch the cache blocks of stage-tile `it` (called by one lane)
   const unsigned char* kbase = reinterpret_cast<const unsigned char*>(p.k_ptrs[l]);
-  auto issue = [&](int it, int stage) {
+  // Fetch the cache blocks of stage-tile `it`.  Called by a whole (converged) warp: lane 0 arms the barrier
+  // with the byte count, then lane j issues the copy of block j, so a stage made of several small cache
+  // blocks costs one issue slot per lane instead of a serial loop.
+  auto issue = [&](int it, int stage, int lane_id) {
     const uint32_t bar = smem_u32(&full_bar[stage]);
     const int blk0 = (tile0 + it) * p.mb;
     const int nb = min(p.mb, nblk - blk0);
-    mbar_arrive_expect_tx(bar, (uint32_t)(nb * p.block_bytes));
-    for (int j = 0; j < nb; ++j) {
+    if (lane_id == 0) mbar_arrive_expect_tx(bar, (uint32_t)(nb * p.block_bytes));
+    __syncwarp();
+    for (int j = lane_id; j < nb; j += 32) {
       int blk;
       if (bt_in_smem) {
         blk = s_bt[it * p.mb + j];
@@ -161,9 +165,9 @@ score_paged_mean_kernel(const __grid_constant__ ScoreParams p) {
                     kbase + (long long)blk * p.block_stride_bytes, (uint32_t)p.block_bytes, bar);
     }
   };
-  if (tid == 0) {
+  if (tid < 32) {
     const int pre = min(p.stages, my_tiles);
-    for (int it = 0; it < pre; ++it) issue(it, it);
+    for (int it = 0; it < pre; ++it) issue(it, it, tid);
   }
 
   // ---------------------------------------------------------------- consumers (all 8 warps)
@@ -376,15 +380,17 @@ score_paged_mean_kernel(const __grid_constant__ ScoreParams p) {
     // release the stage: all lanes of this warp have consumed their shared-memory reads.  The warp whose
     // release is the last of the 8 refills the stage with the tile `stages` ahead - nobody waits for it.
     __syncwarp();
+    unsigned refill = 0u;
     if (lane == 0) {
-      __threadfence_block();
+      // No memory fence: every shared-memory value this warp read from the stage has already been consumed by
+      // arithmetic (a fence here would also wait for the warp's outstanding global stores of raw scores).
       const unsigned int done = atomicAdd(&s_released[stage], 1u) + 1u;
       if (done == release_target && it + p.stages < my_tiles) {
-        __threadfence_block();
-        fence_proxy_async();
-        issue(it + p.stages, stage);
+        fence_proxy_async();  // generic-proxy reads of the stage before the async-proxy refill
+        refill = 1u;
       }
     }
+    if (__shfl_sync(kFull, refill, 0)) issue(it + p.stages, stage, lane);
     if (++stage == p.stages) {
       stage = 0;
       parity ^= 1u;
