@@ -1,0 +1,115 @@
+"""Multi-GPU parity (needs >= 2 CUDA devices; skipped otherwise): tensor-parallel sharding by KV head.
+
+Two NCCL ranks each hold half of the KV heads.  Per-head mode: every rank's keep rows equal the rows the
+single-GPU run produces for those heads (no communication).  Layer-shared mode: one all-reduce(MAX) of the
+score rows and both ranks produce the keep set of the single-GPU run.  NVLS is disabled for the test.
+"""
+from __future__ import annotations
+
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _build(seed=77):
+    from triattention_b200 import synth
+    gen = torch.Generator().manual_seed(seed)
+    L, Hq, Hkv, D, bs = 2, 16, 4, 128, 16
+    lens = [900, 1500]
+    inv = synth.rope_inv_freq(D, 1e6)
+    stats = synth.make_stats(L, Hq, D, inv, gen)
+    nblk = [(t + bs - 1) // bs for t in lens]
+    perm = synth.random_block_ids(sum(nblk), sum(nblk) + 5, gen)
+    ids, o = [], 0
+    for n in nblk:
+        ids.append(perm[o:o + n])
+        o += n
+    caches = []
+    for _ in range(L):
+        c = synth.make_paged_layer(sum(nblk) + 5, bs, Hkv, D, kv_axis=0)
+        for b, t in enumerate(lens):
+            synth.write_tokens_to_paged(c, 0, ids[b], bs, synth.make_rotated_keys(Hkv, t, D, inv, gen),
+                                        synth.make_values(Hkv, t, D, gen))
+        caches.append(c)
+    return stats, caches, ids, lens, inv
+
+
+def _dstats(stats, dev):
+    from triattention_b200 import ops
+    offsets = torch.tensor([float(2 ** i) for i in range(17)])
+    return ops.DeviceStats(stats.q_mean_real.to(dev), stats.q_mean_imag.to(dev), stats.q_abs_mean.to(dev),
+                           torch.ones_like(stats.q_abs_mean).to(dev), stats.inv_freq.to(dev), offsets.to(dev))
+
+
+def _worker(rank: int, world: int, port: int, q):
+    import torch.distributed as dist
+    from triattention_b200 import engine, ops, tp
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        stats, caches, ids, lens, _ = _build()
+        budgets, starts = [256, 512], list(lens)
+        lo, hi = tp.head_range(4, rank, world)
+        local = [c[:, :, :, lo:hi].contiguous().to(dev) for c in caches]     # this rank's KV heads
+        full = _dstats(stats, dev)
+        shard = tp.shard_stats(full, rank, world)
+        view = ops.PagedCacheView.from_layers(local, kv_axis=0)
+        res = engine.PagedCompressor(shard, window=32).compress(view, ids, lens, starts, budgets)
+        per_head = res.keep.cpu()
+        local2 = [c[:, :, :, lo:hi].contiguous().to(dev) for c in caches]
+        view2 = ops.PagedCacheView.from_layers(local2, kv_axis=0)
+        res2 = engine.compress_layer_shared(view2, shard, ids, lens, starts, budgets, window=32)
+        q.put((rank, per_head, res2.keep.cpu(), res.device_status | res2.device_status,
+               [c.cpu() for c in local2]))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_tp2_matches_single_gpu():
+    import torch.multiprocessing as mp
+    from triattention_b200 import engine, ops
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    out = {}
+    for _ in procs:
+        rank, per_head, shared, status, caches = q.get(timeout=300)
+        out[rank] = (per_head.clone(), shared.clone(), status, [c.clone() for c in caches])
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    # single-GPU reference run with all heads
+    stats, caches, ids, lens, _ = _build()
+    budgets, starts = [256, 512], list(lens)
+    dev = torch.device("cuda", 0)
+    full = _dstats(stats, dev)
+    one = [c.to(dev) for c in caches]
+    res = engine.PagedCompressor(full, window=32).compress(ops.PagedCacheView.from_layers(one, kv_axis=0), ids, lens,
+                                                           starts, budgets)
+    one2 = [c.to(dev) for c in caches]
+    res2 = engine.compress_layer_shared(ops.PagedCacheView.from_layers(one2, kv_axis=0), full, ids, lens, starts, budgets,
+                                        window=32)
+    for rank in (0, 1):
+        per_head, shared, status, shard_caches = out[rank]
+        assert status == 0
+        assert torch.equal(per_head, res.keep.cpu()[:, 2 * rank: 2 * rank + 2])       # heads of this rank, no collective
+        assert torch.equal(shared, res2.keep.cpu())                                   # identical on every rank
+        for l in range(len(caches)):
+            assert torch.equal(shard_caches[l], one2[l][:, :, :, 2 * rank: 2 * rank + 2].cpu())

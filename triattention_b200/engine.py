@@ -148,3 +148,77 @@ class PagedCompressor:
                 removed.append([int(x) for x in ids[req:]])
         return CompressResult(keep=keep, keep_counts=keep_counts, kept_block_ids=kept, removed_block_ids=removed,
                               device_status=status, h2d_bytes=n_ints * 4, d2h_bytes=4)
+
+
+def compress_layer_shared(
+    view: ops.PagedCacheView,
+    stats: ops.DeviceStats,
+    block_ids: Sequence[Sequence[int]],
+    seq_lens: Sequence[int],
+    round_starts: Sequence[int],
+    budgets: Sequence[int],
+    window: int = 128,
+    normalize: bool = True,
+    offset_agg: int = _native.OFFSETS_MEAN,
+    flags: int = 0,
+    prefill_lens: Optional[Sequence[int]] = None,
+    process_group=None,
+    reduce_stats_to_kv_heads: bool = True,
+) -> CompressResult:
+    """Layer-shared selection: every layer keeps ONE token set for all its heads (top-k of the max over heads).
+
+    Follows the reference's opt-in ``per_layer`` mode (selector_hf.py:636-667 with the statistics of each GQA
+    group averaged down to its KV head, :147-203) for a batch of requests.  Under tensor parallelism the heads
+    of a layer live on different ranks: each rank reduces its local heads, one all-reduce(MAX) over
+    ``process_group`` of the fp32 rows ``[L, B, t_pad]`` makes them global, and the deterministic top-k then
+    yields the same keep set on every rank.  ``stats`` must already be the rank's shard (``tp.shard_stats``).
+    Returns keep ``[L, B, keep_pitch]`` (as ``CompressResult.keep``).
+    """
+    from . import tp as _tp
+
+    B = len(block_ids)
+    bs = view.block_size
+    dev = view.device
+    if reduce_stats_to_kv_heads and stats.num_heads != view.num_kv_heads:
+        g0, rem = divmod(stats.num_heads, view.num_kv_heads)
+        if rem:
+            raise RuntimeError(f"incompatible_head_mapping:source={stats.num_heads},target={view.num_kv_heads}")
+
+        def _avg(x):
+            return x.reshape(x.shape[0], view.num_kv_heads, g0, x.shape[-1]).mean(dim=2).contiguous()
+
+        stats = ops.DeviceStats(_avg(stats.q_mean_real), _avg(stats.q_mean_imag), _avg(stats.q_abs_mean),
+                                _avg(stats.freq_scale_sq), stats.omega, stats.offsets, stats.rope_interleaved)
+    g = stats.num_heads // view.num_kv_heads
+    max_blocks = max(num_required_blocks(int(n), bs) for n in seq_lens)
+    keep_counts = [min(int(k), int(n)) for k, n in zip(budgets, seq_lens)]
+    keep_pitch = max(max(keep_counts), 1)
+    bt_host = np.zeros((B, max_blocks), dtype=np.int32)
+    for b, ids in enumerate(block_ids):
+        nb = num_required_blocks(int(seq_lens[b]), bs)
+        if nb > len(ids):
+            raise IndexError(f"token indices require block_idx={nb - 1}, but only {len(ids)} blocks exist")
+        bt_host[b, :nb] = ids[:nb]
+    bt = torch.from_numpy(bt_host).to(dev)
+    meta = torch.tensor([list(seq_lens), list(round_starts), keep_counts,
+                         list(prefill_lens) if prefill_lens is not None else [0] * B], dtype=torch.int32, device=dev)
+    d_seq, d_rs, d_kc, d_pre = meta[0], meta[1], meta[2], meta[3]
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    layout = view.layout(B, g, max_blocks, rope_interleaved=stats.rope_interleaved)
+    w = ops.prep_weights(stats, d_rs, offset_agg, flags)
+    raw, mom = ops.score_paged(view, layout, bt, d_seq, w, offset_agg, int(stats.offsets.numel()), status)
+    fin = ops.finalize_scores(layout, raw, mom, d_seq, d_pre if prefill_lens is not None else None, window, normalize,
+                              _native.REDUCE_MAX, _native.REDUCE_MAX, _native.REDUCE_NONE)   # [L, B, 1, t_pad]
+    _tp.allreduce_shared_scores(fin, process_group)
+    L = view.num_layers
+    keep = ops.select_topk(fin.view(L * B, fin.shape[-1]), d_seq, d_kc, B, 1, keep_pitch, status)  # rows (l, b)
+    ops.compact_paged(view, layout, bt, d_seq, keep, (B * keep_pitch, keep_pitch, 0), d_kc, status)
+    bits = int(status.item())
+    kept, removed = [], []
+    for b, ids in enumerate(block_ids):
+        req = num_required_blocks(keep_counts[b], bs)
+        kept.append([int(x) for x in ids[:req]])
+        removed.append([int(x) for x in ids[req:]])
+    return CompressResult(keep=keep.view(L, B, keep_pitch), keep_counts=keep_counts, kept_block_ids=kept,
+                          removed_block_ids=removed, device_status=bits, h2d_bytes=bt_host.nbytes + meta.numel() * 4,
+                          d2h_bytes=4)
