@@ -206,11 +206,11 @@ def dist_setup(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world > 1:
+    if world > 1 and args.impl == "ours":
+        # the reference arm runs on rank 0's host cores only: it needs no process group
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        backend = "nccl" if args.impl == "ours" else "gloo"
-        dist.init_process_group(backend=backend, device_id=torch.device("cuda", local) if backend == "nccl" else None)
+        dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local))
     return world, rank, local
 
 
@@ -460,7 +460,7 @@ def main():
         else:
             run_ours(args, world, rank, local)
     finally:
-        if world > 1:
+        if world > 1 and args.impl == "ours":
             import torch.distributed as dist
             if dist.is_initialized():
                 dist.destroy_process_group()
