@@ -1,8 +1,8 @@
 #!/usr/bin/env python
 """Generate the golden fixtures in this directory from the reference itself.
 
-Run in a container that has the reference checkout (default
-``/root/reference``, override with ``TRIATTN_REFERENCE_ROOT``)::
+Run where a checkout of the reference is available (default: a directory
+``reference`` next to this repository, override with ``TRIATTN_REFERENCE_ROOT``)::
 
     python tests/golden/make_golden.py
 
@@ -33,7 +33,7 @@ import torch
 
 HERE = Path(__file__).resolve().parent
 REPO = HERE.parent.parent
-REF = Path(os.environ.get("TRIATTN_REFERENCE_ROOT", "/root/reference"))
+REF = Path(os.environ.get("TRIATTN_REFERENCE_ROOT", str(REPO.parent / "reference")))
 sys.dont_write_bytecode = True
 sys.path.insert(0, str(REPO))
 sys.path.insert(0, str(REF))
@@ -392,7 +392,7 @@ def gen_hook_cases(out: dict):
 
 def main():
     ref_scoring, ref_config = install_shims()
-    out = {"torch": torch.__version__, "reference_root": str(REF)}
+    out = {"torch": torch.__version__}
     gen_score_cases(ref_scoring, ref_config, out)
     gen_selector_cases(out)
     gen_real_stats_case(out)
