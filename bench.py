@@ -48,6 +48,7 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (smaller captures)")
     ap.add_argument("--batch", type=int, default=0, help="override the request count")
     ap.add_argument("--tokens", type=int, default=0, help="override the cached length")
+    ap.add_argument("--budget", type=int, default=0, help="override the KV budget")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
 
@@ -127,6 +128,8 @@ def resolve_config(args, world: int):
         c["B"] = args.batch
     if args.tokens:
         c["T"] = args.tokens
+    if getattr(args, "budget", 0):
+        c["budget"] = args.budget
     if c["Hkv"] % world:
         raise SystemExit(f"--gpus {world} does not divide {c['Hkv']} KV heads")
     c["g"] = c["Hq"] // c["Hkv"]

@@ -1,6 +1,7 @@
 // Per-row top-k by radix select on order-preserving keys, with deterministic lowest-index
-// tie-break and ascending index output (stable compaction by ballot/popc prefix sums).
-// One CTA per row: rows are few (requests x KV heads) and each row fits in L2.
+// tie-break and ascending index output (stable compaction by prefix sums in index order).
+// One CTA per row: rows are few (requests x KV heads) and each row stays in L2 across passes.
+// Every thread handles 4 consecutive scores per step (one 16-byte load when the row is aligned).
 #pragma once
 
 #include "common.cuh"
@@ -8,6 +9,9 @@
 namespace triattn {
 
 constexpr int kSelectThreads = 1024;
+constexpr int kSelectVec = 4;
+constexpr int kSelectChunk = kSelectThreads * kSelectVec;
+constexpr int kSelectSubHists = 8;  // histogram copies, indexed by warp, to spread shared-memory atomics
 
 struct SelectParams {
   const float* scores;  // [rows, row_stride]
@@ -20,19 +24,62 @@ struct SelectParams {
   uint32_t* status;
 };
 
+// 4 consecutive keys starting at i (keys of positions >= n come back as 0 with valid=false)
+__device__ __forceinline__ void load_keys4(const float* __restrict__ x, int i, int n, bool aligned, unsigned (&key)[4],
+                                           bool (&valid)[4]) {
+  if (aligned && i + 3 < n) {
+    const float4 v = *reinterpret_cast<const float4*>(x + i);
+    key[0] = float_to_ordered(v.x);
+    key[1] = float_to_ordered(v.y);
+    key[2] = float_to_ordered(v.z);
+    key[3] = float_to_ordered(v.w);
+    valid[0] = valid[1] = valid[2] = valid[3] = true;
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      valid[j] = i + j < n;
+      key[j] = valid[j] ? float_to_ordered(x[i + j]) : 0u;
+    }
+  }
+}
+
+// exclusive prefix of `v` over the whole CTA (threads in index order) and the CTA total; 2 barriers
+__device__ __forceinline__ unsigned block_exclusive_scan(unsigned v, unsigned* warp_tot, unsigned& total) {
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  unsigned incl = v;
+#pragma unroll
+  for (int s = 1; s < 32; s <<= 1) {
+    const unsigned u = __shfl_up_sync(0xffffffffu, incl, s);
+    if (lane >= s) incl += u;
+  }
+  if (lane == 31) warp_tot[wid] = incl;
+  __syncthreads();
+  unsigned wv = warp_tot[lane];  // 32 warps: one value per lane
+  unsigned winc = wv;
+#pragma unroll
+  for (int s = 1; s < 32; s <<= 1) {
+    const unsigned u = __shfl_up_sync(0xffffffffu, winc, s);
+    if (lane >= s) winc += u;
+  }
+  total = __shfl_sync(0xffffffffu, winc, 31);
+  const unsigned warp_excl = __shfl_sync(0xffffffffu, winc - wv, wid);
+  __syncthreads();  // warp_tot may be reused by the caller
+  return warp_excl + incl - v;
+}
+
 __global__ void __launch_bounds__(kSelectThreads) select_topk_kernel(const __grid_constant__ SelectParams p) {
-  __shared__ unsigned int hist[256];
+  __shared__ unsigned int hist[kSelectSubHists][256];
   __shared__ unsigned int s_prefix, s_remaining;
-  __shared__ unsigned int warp_tot[2][32];
-  __shared__ unsigned int s_base_eq, s_base_out;
+  __shared__ unsigned int warp_tot[32];
 
   const int row = blockIdx.x;
   const int b = (row / p.rows_inner) % p.num_reqs;
   const int n = p.seq_lens[b];
-  int k = min(p.keep_counts[b], min(n, p.keep_pitch));
+  const int k = min(p.keep_counts[b], min(n, p.keep_pitch));
   const float* x = p.scores + (size_t)row * p.row_stride;
   int32_t* out = p.keep_out + (size_t)row * p.keep_pitch;
   const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(x) & 15u) == 0);
 
   if (k <= 0 || n <= 0) {
     for (int i = tid; i < p.keep_pitch; i += kSelectThreads) out[i] = -1;
@@ -44,42 +91,42 @@ __global__ void __launch_bounds__(kSelectThreads) select_topk_kernel(const __gri
     return;
   }
 
-  // ---- radix select: find the key value of the k-th largest element, 8 bits per pass
+  // ---- radix select: key value of the k-th largest element, 8 bits per pass from the top
   if (tid == 0) {
     s_prefix = 0u;
     s_remaining = (unsigned)k;
   }
+  unsigned int* my_hist = hist[wid & (kSelectSubHists - 1)];
   for (int pass = 0; pass < 4; ++pass) {
     const int shift = 24 - 8 * pass;
     const unsigned himask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
-    if (tid < 256) hist[tid] = 0u;
+    for (int i = tid; i < kSelectSubHists * 256; i += kSelectThreads) (&hist[0][0])[i] = 0u;
     __syncthreads();
     const unsigned prefix = s_prefix;
-    for (int i0 = 0; i0 < n; i0 += kSelectThreads) {
-      const int i = i0 + tid;
-      bool on = false;
-      unsigned bin = 0;
-      if (i < n) {
-        const unsigned key = float_to_ordered(x[i]);
-        on = ((key ^ prefix) & himask) == 0u;
-        bin = (key >> shift) & 0xffu;
-      }
-      // warp-aggregated histogram update: one atomic per distinct bin per warp
-      const unsigned active = __ballot_sync(0xffffffffu, on);
-      if (on) {
-        const unsigned peers = __match_any_sync(active, bin);
-        if (lane == __ffs(peers) - 1) atomicAdd(&hist[bin], (unsigned)__popc(peers));
+    for (int i0 = 0; i0 < n; i0 += kSelectChunk) {
+      unsigned key[4];
+      bool valid[4];
+      load_keys4(x, i0 + tid * kSelectVec, n, aligned, key, valid);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (valid[j] && ((key[j] ^ prefix) & himask) == 0u) atomicAdd(&my_hist[(key[j] >> shift) & 0xffu], 1u);
       }
     }
     __syncthreads();
-    // thread 0..255: suffix count above my bin; the bin where the running count crosses `remaining` wins
+    if (tid < 256) {
+      unsigned s = 0;
+#pragma unroll
+      for (int h = 0; h < kSelectSubHists; ++h) s += hist[h][tid];
+      hist[0][tid] = s;
+    }
+    __syncthreads();
     if (wid == 0) {
-      // each lane owns 8 consecutive bins, descending order
+      // lane owns 8 consecutive bins in descending order; find the bin where the count from the top crosses
       unsigned local[8];
       unsigned tot = 0;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        local[j] = hist[255 - (lane * 8 + j)];
+        local[j] = hist[0][255 - (lane * 8 + j)];
         tot += local[j];
       }
       unsigned incl = tot;
@@ -88,8 +135,9 @@ __global__ void __launch_bounds__(kSelectThreads) select_topk_kernel(const __gri
         const unsigned v = __shfl_up_sync(0xffffffffu, incl, s);
         if (lane >= s) incl += v;
       }
-      unsigned above = incl - tot;  // elements in bins strictly greater than my first bin
+      unsigned above = incl - tot;  // elements in bins above this lane's first bin
       const unsigned remaining = s_remaining;
+      __syncwarp();
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         if (above < remaining && above + local[j] >= remaining) {
@@ -102,51 +150,46 @@ __global__ void __launch_bounds__(kSelectThreads) select_topk_kernel(const __gri
     }
     __syncthreads();
   }
-  const unsigned kth = s_prefix;        // key of the k-th largest element
-  const unsigned need_eq = s_remaining;  // how many elements equal to kth are kept (lowest indices first)
-  if (tid == 0) {
-    s_base_eq = 0u;
-    s_base_out = 0u;
-  }
+  const unsigned kth = s_prefix;         // key of the k-th largest element
+  const unsigned need_eq = s_remaining;  // elements equal to kth that are kept (lowest indices first)
   __syncthreads();
 
-  // ---- stable compaction in index order
-  for (int i0 = 0; i0 < n; i0 += kSelectThreads) {
-    const int i = i0 + tid;
-    bool gt = false, eq = false;
-    if (i < n) {
-      const unsigned key = float_to_ordered(x[i]);
-      gt = key > kth;
-      eq = key == kth;
+  // ---- stable compaction in index order: keys > kth, plus the first need_eq keys == kth
+  unsigned base_eq = 0u, base_out = 0u;
+  for (int i0 = 0; i0 < n; i0 += kSelectChunk) {
+    const int i = i0 + tid * kSelectVec;
+    unsigned key[4];
+    bool valid[4];
+    load_keys4(x, i, n, aligned, key, valid);
+    bool gt[4], eq[4];
+    unsigned ce = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      gt[j] = valid[j] && key[j] > kth;
+      eq[j] = valid[j] && key[j] == kth;
+      ce += eq[j] ? 1u : 0u;
     }
-    const unsigned beq = __ballot_sync(0xffffffffu, eq);
-    const unsigned lt_mask = (1u << lane) - 1u;
-    if (lane == 0) warp_tot[0][wid] = (unsigned)__popc(beq);
-    __syncthreads();
-    unsigned eq_before = s_base_eq;
-    for (int w = 0; w < wid; ++w) eq_before += warp_tot[0][w];
-    const unsigned eq_rank = eq_before + (unsigned)__popc(beq & lt_mask);
-    const bool sel = gt || (eq && eq_rank < need_eq);
-    const unsigned bsel = __ballot_sync(0xffffffffu, sel);
-    if (lane == 0) warp_tot[1][wid] = (unsigned)__popc(bsel);
-    __syncthreads();
-    unsigned out_before = s_base_out;
-    for (int w = 0; w < wid; ++w) out_before += warp_tot[1][w];
-    if (sel) {
-      const unsigned pos = out_before + (unsigned)__popc(bsel & lt_mask);
-      if (pos < (unsigned)k) out[pos] = i;
+    unsigned tot_eq;
+    unsigned eq_rank = base_eq + block_exclusive_scan(ce, warp_tot, tot_eq);
+    bool sel[4];
+    unsigned cs = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      sel[j] = gt[j] || (eq[j] && eq_rank < need_eq);
+      eq_rank += eq[j] ? 1u : 0u;
+      cs += sel[j] ? 1u : 0u;
     }
-    __syncthreads();
-    if (tid == 0) {
-      unsigned te = 0, to = 0;
-      for (int w = 0; w < 32; ++w) {
-        te += warp_tot[0][w];
-        to += warp_tot[1][w];
+    unsigned tot_sel;
+    unsigned pos = base_out + block_exclusive_scan(cs, warp_tot, tot_sel);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (sel[j]) {
+        if (pos < (unsigned)k) out[pos] = i + j;
+        ++pos;
       }
-      s_base_eq += te;
-      s_base_out += to;
     }
-    __syncthreads();
+    base_eq += tot_eq;
+    base_out += tot_sel;
   }
 }
 

@@ -26,8 +26,9 @@ class CompressResult:
 
     keep: torch.Tensor                     # [B, Hkv, keep_pitch] int32 on device, ascending per row
     keep_counts: list[int]                 # per request: tokens kept (cache_len_after)
-    kept_block_ids: list[list[int]]        # block table after tail truncation
-    removed_block_ids: list[list[int]]     # blocks handed back to the allocator
+    kept_block_ids: list                   # per request: block table after tail truncation
+    removed_block_ids: list                # per request: blocks handed back to the allocator
+                                           # (lists of int, or int32 array views when arrays were passed in)
     device_status: int                     # 0 or TRIATTN_DEV_* bits
     h2d_bytes: int = 0
     d2h_bytes: int = 0
@@ -141,8 +142,8 @@ class PagedCompressor:
         for b, ids in enumerate(block_ids):
             req = num_required_blocks(keep_counts[b], bs)
             if isinstance(ids, np.ndarray):
-                kept.append(ids[:req].tolist())
-                removed.append(ids[req:].tolist())
+                kept.append(ids[:req])
+                removed.append(ids[req:])
             else:
                 kept.append([int(x) for x in ids[:req]])
                 removed.append([int(x) for x in ids[req:]])
