@@ -25,6 +25,11 @@ __global__ void moments_to_mean_std_kernel(const double* __restrict__ moments, c
   mean_std[2 * (size_t)i + 1] = 1.0f / sd;  // the finalize kernel multiplies by the reciprocal
 }
 
+#ifndef TRIATTN_FIN_UNROLL
+#define TRIATTN_FIN_UNROLL 4
+#endif
+constexpr int kFinalizeUnroll = TRIATTN_FIN_UNROLL;
+
 struct FinalizeParams {
   const float* raw;        // [L, B, Hkv, t_pad, gp]
   const float* mean_std;   // [L, B, Hq, 2]: (mean, 1/std)
@@ -51,7 +56,7 @@ __global__ void __launch_bounds__(256) finalize_scores_kernel(const __grid_const
   const int h_end = p.head_reduce != TRIATTN_REDUCE_NONE ? p.Hkv : ho + 1;
   const bool vec4 = (gp & 3) == 0;
   float acc = 0.f;
-#pragma unroll 4
+#pragma unroll(kFinalizeUnroll)
   for (int l = 0; l < p.L; ++l) {
     float lv = -INFINITY;
     for (int kvh = h_begin; kvh < h_end; ++kvh) {
