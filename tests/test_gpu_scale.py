@@ -185,3 +185,35 @@ def test_full_length_properties(hkv, g, batch):
                          [budget] * batch, [T] * batch, [budget] * batch)
     assert bool((res2.keep.long() == torch.arange(budget, device=DEV)).all())
     assert all(torch.equal(a, c) for a, c in zip(snap, caches))
+
+
+def test_token_pool_layout_block_size_one():
+    """A token-granular slot pool (one token per 'block', as a flat KV pool stores it) goes through the same
+    entry points: the block table is the request's slot list."""
+    gen = torch.Generator().manual_seed(4242)
+    L, Hq, Hkv, D, T, budget, window = 2, 4, 2, 128, 333, 100, 16
+    inv = synth.rope_inv_freq(D, 1e6)
+    stats = synth.make_stats(L, Hq, D, inv, gen)
+    pool = T + 40
+    slots = synth.random_block_ids(T, pool, gen)
+    caches = []
+    for _ in range(L):
+        c = torch.zeros((2, pool, 1, Hkv, D), dtype=torch.bfloat16)
+        synth.write_tokens_to_paged(c, 0, slots, 1, synth.make_rotated_keys(Hkv, T, D, inv, gen),
+                                    synth.make_values(Hkv, T, D, gen))
+        caches.append(c)
+    layers = [(l, c, slots, 1) for l, c in enumerate(caches)]
+    ref_final = oracle.final_scores_group_per_head(layers, _stats_dict(stats), inv, oracle.geometric_offsets(), T, 5000,
+                                                   window_size=window, kv_axis=0)
+    dc = [c.to(DEV) for c in caches]
+    comp = engine.PagedCompressor(device_stats(stats, oracle.geometric_offsets()), window=window)
+    res = comp.compress(ops.PagedCacheView.from_layers(dc, kv_axis=0), [slots], [T], [5000], [budget])
+    assert res.device_status == 0
+    keep = res.keep[0].cpu().long()
+    ok, nd = keep_sets_match_modulo_near_ties(keep, oracle.topk_lowest_index(ref_final, budget), ref_final)
+    assert ok, nd
+    for l, c in enumerate(caches):
+        exp = c.clone()
+        oracle.compact_per_head(exp, slots, 1, keep, T, preserve_dropped_tokens=False, kv_axis=0)
+        assert torch.equal(dc[l].cpu().view(torch.int16), exp.view(torch.int16))
+    assert res.kept_block_ids[0] == slots[:budget] and res.removed_block_ids[0] == slots[budget:]

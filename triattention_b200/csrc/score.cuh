@@ -10,8 +10,8 @@
 //     adjacent frequencies, so the inner loop is fma.rn.f32x2 on naturally paired bf16 data);
 //   * a batch of NT = 16/GP tokens gives 16 partial sums per lane, combined across the 16 lanes
 //     with a select-free reduce-scatter: lane j accumulates logical value (token, head) in
-//     register slot (idx ^ j), so every lane sends slots with bit s set and keeps the others;
-//     after 4 steps lane j holds the finished score of token j/GP, head j%GP and the 16 lanes
+//     register slot (idx ^ j), so every lane sends the slots with the exchanged bits set and keeps the
+//     others (no selects); after two radix-4 steps (15 shuffles) lane j holds the finished score of token j/GP, head j%GP and the 16 lanes
 //     store 64 contiguous bytes.
 #pragma once
 
@@ -305,12 +305,20 @@ score_paged_mean_kernel(const __grid_constant__ ScoreParams p) {
     for (int tp = 0; tp < NT; ++tp)
 #pragma unroll
       for (int hp = 0; hp < GP; ++hp) v[tp * GP + hp] = acc[tp][hp].x + acc[tp][hp].y;
+    // radix-4 reduce-scatter: two latency levels instead of four, still 15 shuffles.  Slot p holds logical value
+    // p ^ lg, so for every xor distance d a lane keeps the slots with the d-bits clear and sends slot p | d.
 #pragma unroll
-    for (int s = kLPK / 2; s >= 1; s >>= 1) {
-#pragma unroll
-      for (int i = 0; i < kLPK; ++i) {
-        if ((i & s) == 0 && i < 2 * s) v[i] += __shfl_xor_sync(kFull, v[i | s], s);
-      }
+    for (int q = 0; q < 4; ++q) {
+      const float t1 = __shfl_xor_sync(kFull, v[q | 4], 4);
+      const float t2 = __shfl_xor_sync(kFull, v[q | 8], 8);
+      const float t3 = __shfl_xor_sync(kFull, v[q | 12], 12);
+      v[q] = (v[q] + t1) + (t2 + t3);
+    }
+    {
+      const float t1 = __shfl_xor_sync(kFull, v[1], 1);
+      const float t2 = __shfl_xor_sync(kFull, v[2], 2);
+      const float t3 = __shfl_xor_sync(kFull, v[3], 3);
+      v[0] = (v[0] + t1) + (t2 + t3);
     }
     // lane lg now owns token gtok0 + lg/GP, query slot lg%GP
     bool store = live && (lane_lo < cur_nq);
