@@ -208,19 +208,28 @@ int triattn_score_paged(const triattn_paged_layout* layout, const void* const* k
   const int gpv = std::min(gp, 4);            // query slots per virtual head
   const int nsub = gp / gpv;                  // virtual heads per KV head
   const int nt = kLPK / gpv;
-  const bool fast = !p.agg_max && (Y.head_dim == 64 || Y.head_dim == 128) && block_is_dense(layout) &&
-                    block_bytes <= 64 * 1024 && (p.block_stride_bytes % 16) == 0 && (Y.block_size % nt) == 0 &&
-                    (long long)Y.num_kv_heads * nsub * (Y.block_size / nt) <= kMaxScoreItems;
-  if (fast) {
+  const bool nhd = Y.head_stride == Y.head_dim && Y.token_stride == (int64_t)Y.num_kv_heads * Y.head_dim;
+  p.nhd = nhd ? 1 : 0;
+  // cache blocks per stage: a power of two filling ~32 KB, so that all 16 key groups get (head, batch) items
+  int mb = 1;
+  while ((mb * 2) * block_bytes <= 32 * 1024) mb *= 2;
+  {
     constexpr int kNG = kScoreConsumerThreads / kLPK;
-    // cache blocks per stage: enough (head, token-batch) items to occupy all 16 key groups, stage <= 32 KB
-    const int items_per_block = Y.num_kv_heads * nsub * (Y.block_size / nt);
-    int mb = 1;
-    while (mb * items_per_block < 2 * kNG && (mb * 2) * block_bytes <= 32 * 1024) mb *= 2;
-    mb = env_int("TRIATTN_SCORE_MB", mb, 1, 64);
-    while (mb > 1 && ((long long)mb * items_per_block > kMaxScoreItems || (long long)mb * block_bytes > 96 * 1024)) mb /= 2;
+    const int items_per_block = Y.num_kv_heads * nsub * std::max(1, Y.block_size / nt);
+    while (mb > 1 && (mb / 2) * items_per_block >= 2 * kNG && (long long)(mb / 2) * block_bytes >= 16 * 1024) mb /= 2;
+  }
+  mb = env_int("TRIATTN_SCORE_MB", mb, 1, 64);
+  while (mb > 1 && (long long)mb * block_bytes > 96 * 1024) mb /= 2;
+  const long long stage_tok = (long long)mb * Y.block_size;
+  const long long n_items = nhd ? (long long)Y.num_kv_heads * nsub * (stage_tok / nt)
+                                : (long long)mb * Y.num_kv_heads * nsub * (Y.block_size / nt);
+  const bool fast = !p.agg_max && (Y.head_dim == 64 || Y.head_dim == 128) && block_is_dense(layout) &&
+                    block_bytes <= 64 * 1024 && (block_bytes % 16) == 0 && (p.block_stride_bytes % 16) == 0 &&
+                    (nhd ? (stage_tok % nt) == 0 : (Y.block_size % nt) == 0) && n_items > 0 &&
+                    n_items <= kMaxScoreItems;
+  if (fast) {
     const long long stage_bytes = (long long)mb * block_bytes;
-    // two CTAs per SM share ~200 KB of shared memory; 8x128 keeps one CTA per SM
+    // two CTAs per SM share ~200 KB of shared memory
     const long long budget = 100 * 1024;
     int stages = (int)std::min<long long>(4, budget / stage_bytes);
     stages = env_int("TRIATTN_SCORE_STAGES", stages, 1, kMaxStages);
@@ -234,8 +243,9 @@ int triattn_score_paged(const triattn_paged_layout* layout, const void* const* k
     const long long target_ctas = (long long)kSMs * 2 * 8;
     // at least ~64 KB and at most ~2 MB of keys per CTA
     const int min_tpc = (int)std::max<long long>(1, (64 * 1024) / stage_bytes);
-    const int max_tpc = (int)std::max<long long>(min_tpc, (2 * 1024 * 1024) / stage_bytes);
-    int tpc = (int)std::min<long long>(max_tpc, std::max<long long>(min_tpc, total_tiles / target_ctas));
+    int max_tpc = (int)std::max<long long>(min_tpc, (2 * 1024 * 1024) / stage_bytes);
+    max_tpc = std::max(1, std::min(max_tpc, kMaxPrefetchedBlocks / mb));  // the CTA's block ids fit its smem table
+    int tpc = (int)std::min<long long>(max_tpc, std::max<long long>(std::min(min_tpc, max_tpc), total_tiles / target_ctas));
     tpc = env_int("TRIATTN_SCORE_TILES_PER_CTA", tpc, 1, 1 << 20);
     p.tiles_per_cta = tpc;
     dim3 grid((unsigned)((max_tiles + tpc - 1) / tpc), (unsigned)Y.num_layers, (unsigned)Y.num_reqs);

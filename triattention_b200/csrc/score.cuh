@@ -37,6 +37,7 @@ struct ScoreParams {
   int stages;
   int tiles_per_cta;
   int gp_total;  // query-head slots per KV head in the raw layout
+  int nhd;       // 1: token-major blocks (head_stride == D, token_stride == Hkv*D)
   int num_offsets;  // generic kernel only
   int agg_max;      // generic kernel only
 };
@@ -100,8 +101,12 @@ score_paged_mean_kernel(const __grid_constant__ ScoreParams p) {
   const int Hq = p.Hkv * p.g;
   const int nsub = p.gp_total / GP;  // virtual heads per KV head (1 unless g > 4)
   const int nvh = p.Hkv * nsub;
-  const int bph = p.bs / NT;  // token batches per cache block (the host guarantees bs % NT == 0)
-  const int n_items = p.mb * nvh * bph;
+  // Token batches of a stage.  In NHD order the blocks of a stage sit back to back with one uniform token
+  // stride, so the stage is a dense [mb*bs tokens, heads, D] array and batches may span cache blocks (this
+  // covers blocks smaller than a batch, down to token-granular pools with block_size 1).  Otherwise batches
+  // stay inside a block (the host guarantees block_size % NT == 0 then).
+  const int bph = p.nhd ? stage_tokens / NT : p.bs / NT;
+  const int n_items = (p.nhd ? 1 : p.mb) * nvh * bph;
 
   if (tid == 0) {
     for (int s = 0; s < p.stages; ++s) {
@@ -115,7 +120,7 @@ score_paged_mean_kernel(const __grid_constant__ ScoreParams p) {
     const int vh = i % nvh;
     const int q = i / nvh;
     const int batch = q % bph;
-    const int mbi = q / bph;
+    const int mbi = q / bph;  // always 0 in NHD order
     ScoreItem it;
     it.smem_off = mbi * p.block_bytes + ((vh / nsub) * p.head_stride + batch * NT * p.token_stride) * 2;
     it.tok_rel = mbi * p.bs + batch * NT;
