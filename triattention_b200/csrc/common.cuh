@@ -64,11 +64,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after kWaitLimit polls and reports failure instead of spinning forever.
-constexpr uint32_t kWaitLimit = 1u << 22;
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t suspend_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(suspend_ns)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: each poll may suspend the thread in hardware for up to kWaitSuspendNs (so a wait that is
+// satisfied within that time costs one instruction); after kWaitLimit polls it gives up and reports failure
+// instead of spinning forever (worst case about kWaitLimit * kWaitSuspendNs = 1 s).
+constexpr uint32_t kWaitSuspendNs = 1u << 14;
+constexpr uint32_t kWaitLimit = 1u << 16;
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kWaitLimit; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
+  if (mbar_try_wait_hint(bar, parity, kWaitSuspendNs)) return true;
+  for (uint32_t i = 1; i < kWaitLimit; ++i) {
+    if (mbar_try_wait_hint(bar, parity, kWaitSuspendNs)) return true;
   }
   return false;
 }
