@@ -13,6 +13,7 @@
 #include "finalize.cuh"
 #include "prep.cuh"
 #include "score.cuh"
+#include "score_mma.cuh"
 #include "select.cuh"
 
 using namespace triattn;
@@ -67,6 +68,21 @@ int launch_score_fast(const ScoreParams& p, int gp, dim3 grid, size_t smem, cuda
     case 4: TRIATTN_LAUNCH(4)
     default: return TRIATTN_ERR_UNSUPPORTED_SHAPE;
   }
+#undef TRIATTN_LAUNCH
+}
+
+template <int D, bool IL>
+int launch_score_mma(const ScoreParams& p, dim3 grid, size_t smem, cudaStream_t st) {
+#define TRIATTN_LAUNCH(NT)                                                                                  \
+  {                                                                                                         \
+    auto kern = score_paged_mma_kernel<D, IL, NT>;                                                          \
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
+      return TRIATTN_ERR_CUDA;                                                                              \
+    kern<<<grid, kScoreThreadsWS, smem, st>>>(p);                                                           \
+    return check_launch();                                                                                  \
+  }
+  if (p.gp_total <= 4) TRIATTN_LAUNCH(1)
+  TRIATTN_LAUNCH(2)
 #undef TRIATTN_LAUNCH
 }
 
@@ -223,10 +239,11 @@ int triattn_score_paged(const triattn_paged_layout* layout, const void* const* k
   const long long stage_tok = (long long)mb * Y.block_size;
   const long long n_items = nhd ? (long long)Y.num_kv_heads * nsub * (stage_tok / nt)
                                 : (long long)mb * Y.num_kv_heads * nsub * (Y.block_size / nt);
-  const bool fast = !p.agg_max && (Y.head_dim == 64 || Y.head_dim == 128) && block_is_dense(layout) &&
-                    block_bytes <= 64 * 1024 && (block_bytes % 16) == 0 && (p.block_stride_bytes % 16) == 0 &&
-                    (nhd ? (stage_tok % nt) == 0 : (Y.block_size % nt) == 0) && n_items > 0 &&
-                    n_items <= kMaxScoreItems;
+  const bool streamable = !p.agg_max && (Y.head_dim == 64 || Y.head_dim == 128) && block_is_dense(layout) &&
+                          block_bytes <= 64 * 1024 && (block_bytes % 16) == 0 && (p.block_stride_bytes % 16) == 0;
+  const bool use_mma = streamable && env_int("TRIATTN_SCORE_MMA", 1, 0, 1) == 1;
+  const bool fast = streamable && (use_mma || ((nhd ? (stage_tok % nt) == 0 : (Y.block_size % nt) == 0) &&
+                                               n_items > 0 && n_items <= kMaxScoreItems));
   if (fast) {
     const long long stage_bytes = (long long)mb * block_bytes;
     // two CTAs per SM share ~200 KB of shared memory
@@ -250,6 +267,13 @@ int triattn_score_paged(const triattn_paged_layout* layout, const void* const* k
     p.tiles_per_cta = tpc;
     dim3 grid((unsigned)((max_tiles + tpc - 1) / tpc), (unsigned)Y.num_layers, (unsigned)Y.num_reqs);
     const size_t smem = (size_t)stages * stage_bytes;
+    if (use_mma) {
+      if (Y.head_dim == 128)
+        return Y.rope_interleaved ? launch_score_mma<128, true>(p, grid, smem, st)
+                                  : launch_score_mma<128, false>(p, grid, smem, st);
+      return Y.rope_interleaved ? launch_score_mma<64, true>(p, grid, smem, st)
+                                : launch_score_mma<64, false>(p, grid, smem, st);
+    }
     if (Y.head_dim == 128)
       return Y.rope_interleaved ? launch_score_fast<128, true>(p, gpv, grid, smem, st)
                                 : launch_score_fast<128, false>(p, gpv, grid, smem, st);

@@ -1,0 +1,412 @@
+// Key scorer on the warp-level tensor-core path (mma.sync m16n8k16 bf16), offset aggregation = mean.
+//
+// With the offsets folded into per-frequency weights the score of a key for the query heads of its KV head is
+// a small matrix product: [16 keys x 3F] x [3F x heads], where the 3F entries are re(k), im(k) and |k|.
+//   * Keys are the A operand (M = 16 keys per MMA), weights the B operand: the 8 output columns of an MMA are
+//     4 query heads x {high, low} part of the fp32 weight (column n = 2*head + part; bf16 high part and bf16 of
+//     the remainder, accurate to ~2^-17).  A KV head with 5..8 query heads uses two such column tiles.
+//   * re / im are the cached bf16 values themselves, so they go from shared memory into the MMA unchanged.
+//   * |k| = sqrt(re^2 + im^2) is computed in fp32 on the CUDA cores and split into a bf16 high part (by
+//     truncation) and the bf16 of the exact remainder; both parts extend the K dimension of the magnitude MMAs.
+//   * The K dimension of a dot product may be visited in any order, so every thread reads whole 16-byte chunks
+//     of "its" two keys (rows lane/4 and lane/4+8 of the tile, chunks lane%4 + 4q) and the weight fragments are
+//     permuted once per CTA to match: no ldmatrix and no cross-lane reduction; a thread ends up with the two
+//     parts of query head lane%4 for its two keys, and their sum is the finished score.
+// The copy pipeline (whole cache blocks by bulk async copies on an mbarrier ring, the last warp to release a
+// stage refills it) is the one of the CUDA-core kernel.
+#pragma once
+
+#include "score.cuh"
+
+namespace triattn {
+
+#ifndef TRIATTN_SCORE_MMA_MIN_CTAS
+#define TRIATTN_SCORE_MMA_MIN_CTAS 2
+#endif
+
+constexpr int kMmaKeys = 16;  // keys per MMA tile and work item
+
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// bf16 (round to nearest even) of x, as the upper 16 bits of an fp32 pattern
+__device__ __forceinline__ uint32_t bf16_bits_rn(float x) {
+  const uint32_t u = __float_as_uint(x);
+  return (u + 0x7fffu + ((u >> 16) & 1u)) & 0xffff0000u;
+}
+// x = hi + lo with hi = bf16(x), lo = bf16(x - hi); both returned in the low 16 bits
+__device__ __forceinline__ void bf16_split(float x, uint32_t& hi16, uint32_t& lo16) {
+  const uint32_t hi = bf16_bits_rn(x);
+  hi16 = hi >> 16;
+  lo16 = bf16_bits_rn(x - __uint_as_float(hi)) >> 16;
+}
+// two fp32 -> bf16x2 (round to nearest even), `lo` in the low half
+__device__ __forceinline__ uint32_t pack_bf16x2_rn(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+
+
+// NT = column tiles of 4 query heads per virtual head (1: g <= 4, 2: g <= 8; larger groups are split into
+// virtual heads of 8 that read the same K rows).
+template <int D, bool INTERLEAVED, int NT>
+__global__ void __launch_bounds__(kScoreThreadsWS, TRIATTN_SCORE_MMA_MIN_CTAS)
+score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
+  constexpr int F = D / 2;
+  constexpr int NQ = D / 32;  // 16-byte chunks per key and thread: chunk index lane%4 + 4q
+  constexpr int GP = 4 * NT;  // query-head slots per virtual head
+  static_assert(D == 64 || D == 128, "head_dim must be 64 or 128");
+
+  extern __shared__ __align__(128) unsigned char smem_tiles[];
+  __shared__ __align__(8) uint64_t full_bar[kMaxStages];
+  __shared__ unsigned int s_released[kMaxStages];
+  __shared__ int s_bt[kMaxPrefetchedBlocks];
+  __shared__ int s_err;
+
+  const int tid = threadIdx.x;
+  const int l = blockIdx.y, b = blockIdx.z;
+
+  int seq_len = p.seq_lens[b];
+  if (seq_len > p.t_pad) {
+    if (tid == 0) flag_status(p.status, TRIATTN_DEV_BAD_LENGTH);
+    seq_len = p.t_pad;
+  }
+  const int nblk = (seq_len + p.bs - 1) / p.bs;
+  const int ntiles = (nblk + p.mb - 1) / p.mb;
+  const int tile0 = blockIdx.x * p.tiles_per_cta;
+  if (tile0 >= ntiles) return;
+  const int my_tiles = min(p.tiles_per_cta, ntiles - tile0);
+  const int stage_bytes = p.mb * p.block_bytes;
+  const int stage_tokens = p.mb * p.bs;
+  const int Hq = p.Hkv * p.g;
+  const int nsub = (p.gp_total + GP - 1) / GP;  // virtual heads per KV head
+  const int nvh = p.Hkv * nsub;
+  const int ntt = (stage_tokens + kMmaKeys - 1) / kMmaKeys;  // 16-key items per stage and virtual head
+  const int n_items = ntt * nvh;
+
+  if (tid == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      s_released[s] = 0u;
+    }
+    mbar_fence_init();
+    s_err = 0;
+  }
+  const int32_t* bt = p.block_table + (size_t)b * p.max_blocks;
+  const int my_blocks = min(my_tiles * p.mb, nblk - tile0 * p.mb);
+  const bool bt_in_smem = my_blocks <= kMaxPrefetchedBlocks;
+  if (bt_in_smem) {
+    for (int i = tid; i < my_blocks; i += kScoreThreadsWS) {
+      int blk = bt[tile0 * p.mb + i];
+      if ((unsigned)blk >= (unsigned)p.num_blocks) {
+        flag_status(p.status, TRIATTN_DEV_BAD_BLOCK_ID);
+        blk = 0;
+      }
+      s_bt[i] = blk;
+    }
+  }
+  __syncthreads();
+
+  const unsigned char* kbase = reinterpret_cast<const unsigned char*>(p.k_ptrs[l]);
+  // Fetch the cache blocks of stage-tile `it`: lane 0 arms the barrier, lane j copies block j.
+  auto issue = [&](int it, int stage, int lane_id) {
+    const uint32_t bar = smem_u32(&full_bar[stage]);
+    const int blk0 = (tile0 + it) * p.mb;
+    const int nb = min(p.mb, nblk - blk0);
+    if (lane_id == 0) mbar_arrive_expect_tx(bar, (uint32_t)(nb * p.block_bytes));
+    __syncwarp();
+    for (int j = lane_id; j < nb; j += 32) {
+      int blk;
+      if (bt_in_smem) {
+        blk = s_bt[it * p.mb + j];
+      } else {
+        blk = bt[blk0 + j];
+        if ((unsigned)blk >= (unsigned)p.num_blocks) {
+          flag_status(p.status, TRIATTN_DEV_BAD_BLOCK_ID);
+          blk = 0;
+        }
+      }
+      bulk_copy_g2s(smem_u32(smem_tiles + (size_t)stage * stage_bytes + (size_t)j * p.block_bytes),
+                    kbase + (long long)blk * p.block_stride_bytes, (uint32_t)p.block_bytes, bar);
+    }
+  };
+  if (tid < 32) {
+    const int pre = min(p.stages, my_tiles);
+    for (int it = 0; it < pre; ++it) issue(it, it, tid);
+  }
+
+  constexpr unsigned kFull = 0xffffffffu;
+  const int lane = tid & 31, wid = tid >> 5;
+  const int rg = lane >> 2;  // this thread owns keys (rows) rg and rg + 8 of a tile; in B: output column rg
+  const int rt = lane & 3;   // chunk selector; in the result: query-head slot rt of each column tile
+  const int b_head = rg >> 1, b_part = rg & 1;  // column rg of a weight fragment = (head within the tile, part)
+
+  // weight fragments (B operands) of the current virtual head, permuted to the chunk order of the loads
+  uint32_t bri[NT][NQ][2][2];  // re/im: [column tile][chunk][half of the chunk][b0, b1]
+  uint32_t bmg[NT][NQ][2];     // magnitude: [column tile][4 consecutive frequencies][b0, b1]
+  int cur_vh = -1, cur_qbase = 0, cur_nq = 0;
+  float s1[NT], s2[NT];  // running sum / sum of squares of query slot 4*nt + rt over this thread's keys
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) s1[nt] = s2[nt] = 0.f;
+  float* raw_head = nullptr;
+  const uint32_t smem_base = smem_u32(smem_tiles);
+  const int gp_total = p.gp_total;
+
+  auto flush_moments = [&]() {
+    if (cur_vh < 0) return;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+      for (int s = 4; s < 32; s <<= 1) {
+        s1[nt] += __shfl_xor_sync(kFull, s1[nt], s);
+        s2[nt] += __shfl_xor_sync(kFull, s2[nt], s);
+      }
+      if (lane < 4 && 4 * nt + lane < cur_nq) {
+        double* m = p.moments + (((size_t)l * p.B + b) * Hq + (size_t)cur_qbase + 4 * nt + lane) * 2;
+        atomicAdd(m, (double)s1[nt]);
+        atomicAdd(m + 1, (double)s2[nt]);
+      }
+      s1[nt] = 0.f;
+      s2[nt] = 0.f;
+    }
+  };
+  // 4 consecutive weights starting at w -> this thread's column part, packed as (b0, b1)
+  auto pack_part = [&](const float (&x)[4], bool on, uint32_t& b0, uint32_t& b1) {
+    uint32_t v[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      uint32_t hi, lo;
+      bf16_split(on ? x[e] : 0.f, hi, lo);
+      v[e] = b_part ? lo : hi;
+    }
+    b0 = v[0] | (v[1] << 16);
+    b1 = v[2] | (v[3] << 16);
+  };
+  auto load_weights = [&](int vh) {
+    const int kvh = vh / nsub, sub = vh - kvh * nsub;
+    cur_qbase = kvh * p.g + sub * GP;
+    cur_nq = min(GP, p.g - sub * GP);
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int head = 4 * nt + b_head;
+      const bool on = head < cur_nq;
+      const float* w = p.weights + ((((size_t)l * p.B + b) * Hq + (size_t)cur_qbase + (on ? head : 0)) * 3) * F;
+#pragma unroll
+      for (int c = 0; c < NQ; ++c) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int d0 = 8 * (rt + 4 * c) + 4 * h;  // the thread's 4 consecutive dims of this MMA
+          float x[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int d = d0 + e;
+            // half layout: rows re | im of the weight record are contiguous, so dim d is element d
+            x[e] = INTERLEAVED ? __ldg(w + (d & 1) * F + (d >> 1)) : __ldg(w + d);
+          }
+          pack_part(x, on, bri[nt][c][h][0], bri[nt][c][h][1]);
+        }
+      }
+      const float* wm = w + 2 * F;
+#pragma unroll
+      for (int j = 0; j < NQ; ++j) {
+        // 4 consecutive frequencies per magnitude MMA, in the order compute_item produces |k|
+        const int f0 = INTERLEAVED ? 4 * (rt + 4 * j) : 8 * (rt + 4 * (j >> 1)) + 4 * (j & 1);
+        float x[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) x[e] = __ldg(wm + f0 + e);
+        pack_part(x, on, bmg[nt][j][0], bmg[nt][j][1]);
+      }
+    }
+    raw_head = p.raw + (((size_t)l * p.B + b) * p.Hkv + kvh) * (size_t)p.t_pad * gp_total + sub * GP + rt;
+  };
+
+  // shared-memory byte offset (inside a stage) of token `tk` of the stage for KV head `kvh`
+  auto row_offset = [&](int tk, int kvh) -> uint32_t {
+    if (p.nhd) return (uint32_t)((tk * p.token_stride + kvh * p.head_stride) * 2);
+    const int j = tk / p.bs, in = tk - j * p.bs;
+    return (uint32_t)(j * p.block_bytes + (kvh * p.head_stride + in * p.token_stride) * 2);
+  };
+
+  // One work item: keys tt*16 .. tt*16+15 of the stage for the current virtual head.
+  // `full` = all 16 keys exist (inside the stage and below seq_len), so stores need no per-key test.
+  auto compute_item = [&](uint32_t stage_addr, int tt, int kvh, int stage_tok0, bool full) {
+    const int tkA = tt * kMmaKeys + rg, tkB = tkA + 8;
+    const uint32_t rowA = stage_addr + row_offset(min(tkA, stage_tokens - 1), kvh) + 16u * rt;
+    const uint32_t rowB = stage_addr + row_offset(min(tkB, stage_tokens - 1), kvh) + 16u * rt;
+    float acc[NT][2][4];  // two accumulator chains per column tile
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int ch = 0; ch < 2; ++ch)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[nt][ch][e] = 0.f;
+
+    // (hi, lo) bf16x2 pairs of two adjacent |k| values; lo is the bf16 of the exact remainder
+    auto split_pair = [&](float m0, float m1, uint32_t& hi, uint32_t& lo) {
+      const uint32_t u0 = __float_as_uint(m0), u1 = __float_as_uint(m1);
+      hi = __byte_perm(u0, u1, 0x7632);
+      lo = pack_bf16x2_rn(m0 - __uint_as_float(u0 & 0xffff0000u), m1 - __uint_as_float(u1 & 0xffff0000u));
+    };
+
+    if constexpr (!INTERLEAVED) {
+#pragma unroll
+      for (int q = 0; q < NQ / 2; ++q) {
+        constexpr int QI = NQ / 2;
+        const uint4 reA = lds128(rowA + 64u * q), reB = lds128(rowB + 64u * q);
+        const uint4 imA = lds128(rowA + 64u * q + D), imB = lds128(rowB + 64u * q + D);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          mma_bf16_16816(acc[nt][0], reA.x, reB.x, reA.y, reB.y, bri[nt][q][0][0], bri[nt][q][0][1]);
+          mma_bf16_16816(acc[nt][1], reA.z, reB.z, reA.w, reB.w, bri[nt][q][1][0], bri[nt][q][1][1]);
+          mma_bf16_16816(acc[nt][0], imA.x, imB.x, imA.y, imB.y, bri[nt][q + QI][0][0], bri[nt][q + QI][0][1]);
+          mma_bf16_16816(acc[nt][1], imA.z, imB.z, imA.w, imB.w, bri[nt][q + QI][1][0], bri[nt][q + QI][1][1]);
+        }
+        const uint32_t rA[4] = {reA.x, reA.y, reA.z, reA.w}, rB[4] = {reB.x, reB.y, reB.z, reB.w};
+        const uint32_t iA[4] = {imA.x, imA.y, imA.z, imA.w}, iB[4] = {imB.x, imB.y, imB.z, imB.w};
+        uint32_t hA[4], lA[4], hB[4], lB[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 ra = bf16x2_to_float2(rA[i]), ia = bf16x2_to_float2(iA[i]);
+          const float2 rb = bf16x2_to_float2(rB[i]), ib = bf16x2_to_float2(iB[i]);
+          const float2 ma = ffma2(ia, ia, fmul2(ra, ra));
+          const float2 mb = ffma2(ib, ib, fmul2(rb, rb));
+          split_pair(sqrt_approx(ma.x), sqrt_approx(ma.y), hA[i], lA[i]);
+          split_pair(sqrt_approx(mb.x), sqrt_approx(mb.y), hB[i], lB[i]);
+        }
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            const int j = 2 * q + hh;
+            mma_bf16_16816(acc[nt][hh], hA[2 * hh], hB[2 * hh], hA[2 * hh + 1], hB[2 * hh + 1], bmg[nt][j][0],
+                           bmg[nt][j][1]);
+            mma_bf16_16816(acc[nt][hh ^ 1], lA[2 * hh], lB[2 * hh], lA[2 * hh + 1], lB[2 * hh + 1], bmg[nt][j][0],
+                           bmg[nt][j][1]);
+          }
+      }
+    } else {
+#pragma unroll
+      for (int c = 0; c < NQ; ++c) {
+        const uint4 xA = lds128(rowA + 64u * c), xB = lds128(rowB + 64u * c);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          mma_bf16_16816(acc[nt][0], xA.x, xB.x, xA.y, xB.y, bri[nt][c][0][0], bri[nt][c][0][1]);
+          mma_bf16_16816(acc[nt][1], xA.z, xB.z, xA.w, xB.w, bri[nt][c][1][0], bri[nt][c][1][1]);
+        }
+        const uint32_t wA[4] = {xA.x, xA.y, xA.z, xA.w}, wB[4] = {xB.x, xB.y, xB.z, xB.w};
+        float mA[4], mB[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 va = bf16x2_to_float2(wA[i]), vb = bf16x2_to_float2(wB[i]);
+          const float2 pa = fmul2(va, va), pb = fmul2(vb, vb);
+          mA[i] = sqrt_approx(pa.x + pa.y);
+          mB[i] = sqrt_approx(pb.x + pb.y);
+        }
+        uint32_t hA[2], lA[2], hB[2], lB[2];
+        split_pair(mA[0], mA[1], hA[0], lA[0]);
+        split_pair(mA[2], mA[3], hA[1], lA[1]);
+        split_pair(mB[0], mB[1], hB[0], lB[0]);
+        split_pair(mB[2], mB[3], hB[1], lB[1]);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          mma_bf16_16816(acc[nt][0], hA[0], hB[0], hA[1], hB[1], bmg[nt][c][0], bmg[nt][c][1]);
+          mma_bf16_16816(acc[nt][1], lA[0], lB[0], lA[1], lB[1], bmg[nt][c][0], bmg[nt][c][1]);
+        }
+      }
+    }
+    // columns 2*rt and 2*rt+1 of a column tile are the two weight parts of query slot 4*nt + rt
+    const int gA = stage_tok0 + tkA;
+    const bool okA = full || (tkA < stage_tokens && gA < seq_len);
+    const bool okB = full || (tkB < stage_tokens && gA + 8 < seq_len);
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const float scA = (acc[nt][0][0] + acc[nt][1][0]) + (acc[nt][0][1] + acc[nt][1][1]);
+      const float scB = (acc[nt][0][2] + acc[nt][1][2]) + (acc[nt][0][3] + acc[nt][1][3]);
+      if (4 * nt + rt < cur_nq) {
+        float* out = raw_head + (size_t)gA * gp_total + 4 * nt;
+        if (okA) {
+          out[0] = scA;
+          s1[nt] += scA;
+          s2[nt] = fmaf(scA, scA, s2[nt]);
+        }
+        if (okB) {
+          out[(size_t)8 * gp_total] = scB;
+          s1[nt] += scB;
+          s2[nt] = fmaf(scB, scB, s2[nt]);
+        }
+      }
+    }
+  };
+
+  const int slots = (n_items + kScoreConsumerWarps - 1) / kScoreConsumerWarps;
+  // common case: every warp keeps one virtual head for the whole CTA
+  const bool fixed = (kScoreConsumerWarps % nvh) == 0;
+  const int tt_first = fixed ? wid / nvh : 0, tt_step = fixed ? kScoreConsumerWarps / nvh : 1;
+  if (fixed) {
+    cur_vh = wid % nvh;
+    load_weights(cur_vh);
+  }
+  const int fixed_kvh = cur_vh >= 0 ? cur_vh / nsub : 0;
+  int stage = 0;
+  uint32_t parity = 0;
+  unsigned release_target = (unsigned)kScoreConsumerWarps;
+  for (int it = 0; it < my_tiles; ++it) {
+    const bool ready = __all_sync(kFull, mbar_wait_bounded(smem_u32(&full_bar[stage]), parity));
+    if (!ready) {
+      s_err = 1;
+      if (lane == 0) flag_status(p.status, TRIATTN_DEV_WAIT_TIMEOUT);
+      break;
+    }
+    const uint32_t stage_addr = smem_base + (uint32_t)(stage * stage_bytes);
+    const int stage_tok0 = (tile0 + it) * stage_tokens;
+    const int tok_end = min(seq_len - stage_tok0, stage_tokens);  // keys of this stage that exist
+    if (fixed) {
+      for (int tt = tt_first; tt * kMmaKeys < tok_end; tt += tt_step)
+        compute_item(stage_addr, tt, fixed_kvh, stage_tok0, (tt + 1) * kMmaKeys <= tok_end);
+    } else {
+      for (int sl = 0; sl < slots; ++sl) {
+        const int item = wid + sl * kScoreConsumerWarps;  // warp-uniform
+        if (item >= n_items) break;
+        const int vh = item % nvh, tt = item / nvh;
+        if (tt * kMmaKeys >= tok_end) break;  // items are ordered by token
+        if (vh != cur_vh) {
+          flush_moments();
+          load_weights(vh);
+          cur_vh = vh;
+        }
+        compute_item(stage_addr, tt, vh / nsub, stage_tok0, (tt + 1) * kMmaKeys <= tok_end);
+      }
+    }
+    // release the stage; the warp whose release is the last of the 8 refills it with the tile `stages` ahead
+    __syncwarp();
+    unsigned refill = 0u;
+    if (lane == 0) {
+      const unsigned int done = atomicAdd(&s_released[stage], 1u) + 1u;
+      if (done == release_target && it + p.stages < my_tiles) {
+        fence_proxy_async();
+        refill = 1u;
+      }
+    }
+    if (__shfl_sync(kFull, refill, 0)) issue(it + p.stages, stage, lane);
+    if (++stage == p.stages) {
+      stage = 0;
+      parity ^= 1u;
+      release_target += (unsigned)kScoreConsumerWarps;
+    }
+  }
+  flush_moments();
+}
+
+}  // namespace triattn
