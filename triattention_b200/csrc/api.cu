@@ -53,25 +53,6 @@ bool block_is_dense(const triattn_paged_layout* L) {
 }
 
 template <int D, bool IL>
-int launch_score_fast(const ScoreParams& p, int gp, dim3 grid, size_t smem, cudaStream_t st) {
-#define TRIATTN_LAUNCH(GP)                                                                                    \
-  {                                                                                                           \
-    auto kern = score_paged_mean_kernel<D, GP, IL>;                                                           \
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)   \
-      return TRIATTN_ERR_CUDA;                                                                                \
-    kern<<<grid, kScoreThreadsWS, smem, st>>>(p);                                                               \
-    return check_launch();                                                                                    \
-  }
-  switch (gp) {
-    case 1: TRIATTN_LAUNCH(1)
-    case 2: TRIATTN_LAUNCH(2)
-    case 4: TRIATTN_LAUNCH(4)
-    default: return TRIATTN_ERR_UNSUPPORTED_SHAPE;
-  }
-#undef TRIATTN_LAUNCH
-}
-
-template <int D, bool IL>
 int launch_score_mma(const ScoreParams& p, dim3 grid, size_t smem, cudaStream_t st) {
 #define TRIATTN_LAUNCH(NT)                                                                                  \
   {                                                                                                         \
@@ -221,30 +202,17 @@ int triattn_score_paged(const triattn_paged_layout* layout, const void* const* k
 
   const long long block_bytes = (long long)Y.block_size * Y.num_kv_heads * Y.head_dim * 2;
   p.gp_total = gp;
-  const int gpv = std::min(gp, 4);            // query slots per virtual head
-  const int nsub = gp / gpv;                  // virtual heads per KV head
-  const int nt = kLPK / gpv;
   const bool nhd = Y.head_stride == Y.head_dim && Y.token_stride == (int64_t)Y.num_kv_heads * Y.head_dim;
   p.nhd = nhd ? 1 : 0;
-  // cache blocks per stage: a power of two filling ~32 KB, so that all 16 key groups get (head, batch) items
-  int mb = 1;
-  while ((mb * 2) * block_bytes <= 32 * 1024) mb *= 2;
-  {
-    constexpr int kNG = kScoreConsumerThreads / kLPK;
-    const int items_per_block = Y.num_kv_heads * nsub * std::max(1, Y.block_size / nt);
-    while (mb > 1 && (mb / 2) * items_per_block >= 2 * kNG && (long long)(mb / 2) * block_bytes >= 16 * 1024) mb /= 2;
-  }
-  mb = env_int("TRIATTN_SCORE_MB", mb, 1, 64);
-  while (mb > 1 && (long long)mb * block_bytes > 96 * 1024) mb /= 2;
-  const long long stage_tok = (long long)mb * Y.block_size;
-  const long long n_items = nhd ? (long long)Y.num_kv_heads * nsub * (stage_tok / nt)
-                                : (long long)mb * Y.num_kv_heads * nsub * (Y.block_size / nt);
+  // Streaming tensor-core kernel: mean aggregation, head_dim 64/128, K region of a block one dense run.
   const bool streamable = !p.agg_max && (Y.head_dim == 64 || Y.head_dim == 128) && block_is_dense(layout) &&
                           block_bytes <= 64 * 1024 && (block_bytes % 16) == 0 && (p.block_stride_bytes % 16) == 0;
-  const bool use_mma = streamable && env_int("TRIATTN_SCORE_MMA", 1, 0, 1) == 1;
-  const bool fast = streamable && (use_mma || ((nhd ? (stage_tok % nt) == 0 : (Y.block_size % nt) == 0) &&
-                                               n_items > 0 && n_items <= kMaxScoreItems));
-  if (fast) {
+  if (streamable) {
+    // cache blocks per pipeline stage: a power of two filling ~32 KB (8 work items of 16 keys for 8 KV heads)
+    int mb = 1;
+    while ((mb * 2) * block_bytes <= 32 * 1024) mb *= 2;
+    mb = env_int("TRIATTN_SCORE_MB", mb, 1, 64);
+    while (mb > 1 && (long long)mb * block_bytes > 96 * 1024) mb /= 2;
     const long long stage_bytes = (long long)mb * block_bytes;
     // two CTAs per SM share ~200 KB of shared memory
     const long long budget = 100 * 1024;
@@ -267,18 +235,11 @@ int triattn_score_paged(const triattn_paged_layout* layout, const void* const* k
     p.tiles_per_cta = tpc;
     dim3 grid((unsigned)((max_tiles + tpc - 1) / tpc), (unsigned)Y.num_layers, (unsigned)Y.num_reqs);
     const size_t smem = (size_t)stages * stage_bytes;
-    if (use_mma) {
-      if (Y.head_dim == 128)
-        return Y.rope_interleaved ? launch_score_mma<128, true>(p, grid, smem, st)
-                                  : launch_score_mma<128, false>(p, grid, smem, st);
-      return Y.rope_interleaved ? launch_score_mma<64, true>(p, grid, smem, st)
-                                : launch_score_mma<64, false>(p, grid, smem, st);
-    }
     if (Y.head_dim == 128)
-      return Y.rope_interleaved ? launch_score_fast<128, true>(p, gpv, grid, smem, st)
-                                : launch_score_fast<128, false>(p, gpv, grid, smem, st);
-    return Y.rope_interleaved ? launch_score_fast<64, true>(p, gpv, grid, smem, st)
-                              : launch_score_fast<64, false>(p, gpv, grid, smem, st);
+      return Y.rope_interleaved ? launch_score_mma<128, true>(p, grid, smem, st)
+                                : launch_score_mma<128, false>(p, grid, smem, st);
+    return Y.rope_interleaved ? launch_score_mma<64, true>(p, grid, smem, st)
+                              : launch_score_mma<64, false>(p, grid, smem, st);
   }
   dim3 grid((unsigned)((p.t_pad + 127) / 128), (unsigned)Y.num_kv_heads, (unsigned)(Y.num_layers * Y.num_reqs));
   if ((long long)Y.num_layers * Y.num_reqs > 65535) return TRIATTN_ERR_UNSUPPORTED_SHAPE;

@@ -12,8 +12,12 @@
 //     of "its" two keys (rows lane/4 and lane/4+8 of the tile, chunks lane%4 + 4q) and the weight fragments are
 //     permuted once per CTA to match: no ldmatrix and no cross-lane reduction; a thread ends up with the two
 //     parts of query head lane%4 for its two keys, and their sum is the finished score.
-// The copy pipeline (whole cache blocks by bulk async copies on an mbarrier ring, the last warp to release a
-// stage refills it) is the one of the CUDA-core kernel.
+// Data movement: a CTA owns a run of consecutive cache blocks of one (layer, request); each pipeline stage holds
+// `mb` whole cache blocks (all KV heads) fetched by 1-D bulk async copies (TMA) that complete on an mbarrier
+// (bounded waits).  There is no CTA-wide barrier in the loop: a warp that finishes a stage bumps a shared
+// counter and the last of the 8 warps to do so refills the stage with the tile `stages` ahead.  In token-major
+// (NHD) order the blocks of a stage form one dense token array, so 16-key tiles may span cache blocks (block
+// sizes down to 1).
 #pragma once
 
 #include "score.cuh"
