@@ -64,7 +64,7 @@ def measured_peaks():
 
 
 # DRAM traffic of the score kernel per key from the ncu capture summarised in
-# profiles/score_paged_mean_kernel_c1_2layers.md (dram__bytes_read + dram__bytes_write = 1.0743 GB + 64.7 MB for
+# profiles/score_paged_mma_kernel_c1_2layers.md (dram__bytes_read + dram__bytes_write = 1.0743 GB + 64.7 MB for
 # 4 194 304 keys); traffic grows in proportion to the keys scored, so a full launch is this figure x its keys.
 SCORE_DRAM_BYTES_PER_KEY_NCU = (1.074314e9 + 64.68e6) / 4194304.0
 
@@ -433,7 +433,7 @@ def run_ours(args, world, rank, local):
         "keys_per_s_per_gpu": value / world,
         "step_hbm_gbs": bytes_step / (step_ms * 1e-3) / 1e9, "step_hbm_frac": bytes_step / (step_ms * 1e-3) / 1e9 / peak,
         "stage_ms": stage,
-        "roofline": {"kernel": "score_paged_mean_kernel", "bound": "hbm", "achieved": achieved, "peak": peak,
+        "roofline": {"kernel": "score_paged_mma_kernel", "bound": "hbm", "achieved": achieved, "peak": peak,
                      "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
                      "traffic": (keys_per_gpu * SCORE_DRAM_BYTES_PER_KEY_NCU
                                  if (c["D"], c["g"], c["Hkv_local"]) == (128, 4, 8) else None),

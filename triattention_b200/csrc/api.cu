@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <cmath>
 #include <cstdint>
 #include <cstdlib>
 #include <mutex>
@@ -225,12 +226,16 @@ int triattn_score_paged(const triattn_paged_layout* layout, const void* const* k
     p.stages = stages;
     const int max_tiles = (Y.max_blocks_per_req + mb - 1) / mb;
     const long long total_tiles = (long long)max_tiles * Y.num_layers * Y.num_reqs;
-    const long long target_ctas = (long long)kSMs * 2 * 8;
-    // at least ~64 KB and at most ~2 MB of keys per CTA
+    // Tiles per CTA: every CTA pays a fixed start-up (weight fragments, first copies: about two tiles' worth),
+    // while few CTAs per SM leave a ragged last wave; tpc ~ sqrt(total_tiles / (SMs/2)) balances the two.
+    // At least ~64 KB and at most ~2 MB of keys per CTA, and the CTA's block ids must fit its shared-memory table.
     const int min_tpc = (int)std::max<long long>(1, (64 * 1024) / stage_bytes);
     int max_tpc = (int)std::max<long long>(min_tpc, (2 * 1024 * 1024) / stage_bytes);
-    max_tpc = std::max(1, std::min(max_tpc, kMaxPrefetchedBlocks / mb));  // the CTA's block ids fit its smem table
-    int tpc = (int)std::min<long long>(max_tpc, std::max<long long>(std::min(min_tpc, max_tpc), total_tiles / target_ctas));
+    max_tpc = std::max(1, std::min(max_tpc, kMaxPrefetchedBlocks / mb));
+    int tpc = (int)std::lround(std::sqrt((double)total_tiles / (kSMs / 2.0)));
+    tpc = std::max(std::min(min_tpc, max_tpc), std::min(tpc, max_tpc));
+    // equal shares for the CTAs of one (layer, request)
+    tpc = (max_tiles + (max_tiles + tpc - 1) / tpc - 1) / ((max_tiles + tpc - 1) / tpc);
     tpc = env_int("TRIATTN_SCORE_TILES_PER_CTA", tpc, 1, 1 << 20);
     p.tiles_per_cta = tpc;
     dim3 grid((unsigned)((max_tiles + tpc - 1) / tpc), (unsigned)Y.num_layers, (unsigned)Y.num_reqs);
@@ -320,9 +325,13 @@ static int compact_common(const triattn_paged_layout* layout, void* const* k_lay
     return TRIATTN_ERR_INVALID_ARGUMENT;
   const triattn_paged_layout& Y = *layout;
   const int row_bytes = Y.head_dim * 2;
-  if (row_bytes % 16 != 0 || kCompactThreads % (row_bytes / 16) != 0 || row_bytes / 16 > kCompactThreads)
-    return TRIATTN_ERR_UNSUPPORTED_SHAPE;
+  if (row_bytes % 16 != 0) return TRIATTN_ERR_UNSUPPORTED_SHAPE;
+  const int ppr = row_bytes / 16, nsub = (ppr + 31) / 32;
+  if (ppr % nsub != 0) return TRIATTN_ERR_UNSUPPORTED_SHAPE;
+  // row offsets inside a layer's pool are kept as 32-bit counts of 16 bytes: pools up to 64 GB per layer
+  if (((long long)Y.num_blocks * Y.block_stride >> 3) >= (1ll << 32) - (1ll << 20)) return TRIATTN_ERR_UNSUPPORTED_SHAPE;
   CompactParams p{};
+  p.nsub = nsub;
   p.k_ptrs = k_layer_ptrs;
   p.v_ptrs = v_layer_ptrs;
   p.block_table = block_table;
