@@ -290,7 +290,24 @@ int triattn_finalize_scores(const triattn_paged_layout* layout, const float* raw
   const int Ho = head_reduce != TRIATTN_REDUCE_NONE ? 1 : Y.num_kv_heads;
   dim3 grid((unsigned)((t_pad + 255) / 256), (unsigned)Ho, (unsigned)Y.num_reqs);
   p.gp = gp;
-  finalize_scores_kernel<<<grid, 256, 0, st>>>(p);
+  if (head_reduce == TRIATTN_REDUCE_NONE && Y.group_size <= 8 && (gp == 4 || gp == 8)) {
+#define TRIATTN_FIN(G)                                                                                \
+  case G:                                                                                             \
+    if (layer_reduce == TRIATTN_REDUCE_NONE)                                                          \
+      finalize_scores_fast_kernel<G, TRIATTN_REDUCE_NONE><<<grid, 256, 0, st>>>(p);                   \
+    else if (layer_reduce == TRIATTN_REDUCE_MAX)                                                      \
+      finalize_scores_fast_kernel<G, TRIATTN_REDUCE_MAX><<<grid, 256, 0, st>>>(p);                    \
+    else                                                                                              \
+      finalize_scores_fast_kernel<G, TRIATTN_REDUCE_MEAN><<<grid, 256, 0, st>>>(p);                   \
+    break;
+    switch (Y.group_size) {
+      TRIATTN_FIN(3) TRIATTN_FIN(4) TRIATTN_FIN(5) TRIATTN_FIN(6) TRIATTN_FIN(7) TRIATTN_FIN(8)
+      default: finalize_scores_kernel<<<grid, 256, 0, st>>>(p);
+    }
+#undef TRIATTN_FIN
+  } else {
+    finalize_scores_kernel<<<grid, 256, 0, st>>>(p);
+  }
   return check_launch();
 }
 

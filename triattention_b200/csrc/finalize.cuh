@@ -102,4 +102,83 @@ __global__ void __launch_bounds__(256) finalize_scores_kernel(const __grid_const
   if (p.layer_reduce != TRIATTN_REDUCE_NONE) p.out[((size_t)b * Ho + ho) * (size_t)p.t_pad + t] = acc;
 }
 
+// Fast path for one KV head per output row (head_reduce == NONE): group size G and the layer reduction are
+// compile-time, the per-layer arithmetic is branch-free, and the raw rows of kFinalizePrefetch layers are
+// requested before any of them is used, so a thread keeps that many 16-byte loads in flight.  The arithmetic
+// per layer and the order over layers are those of the kernel above.
+constexpr int kFinalizePrefetch = 6;
+
+template <int G, int LR>
+__global__ void __launch_bounds__(256) finalize_scores_fast_kernel(const __grid_constant__ FinalizeParams p) {
+  constexpr int NQ = (G + 3) / 4;  // float4 loads per layer; the raw layout has 4*NQ slots per KV head
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  const int kvh = blockIdx.y, b = blockIdx.z;
+  const int seq_len = min(p.seq_lens[b], p.t_pad);
+  if (t >= seq_len) return;
+  const int Hq = p.Hkv * G;
+  const int recent = p.window > 0 ? min(p.window, seq_len) : 0;
+  bool guarded = recent > 0 && t >= seq_len - recent;
+  if (p.prefill_lens != nullptr && t < p.prefill_lens[b]) guarded = true;
+  float* out = p.out + ((size_t)b * p.Hkv + kvh) * (size_t)p.t_pad + t;
+  const size_t out_layer_stride = (size_t)p.B * p.Hkv * (size_t)p.t_pad;
+  if (guarded) {
+    // +inf survives max and sum over layers and the division of the mean
+    if (LR == TRIATTN_REDUCE_NONE) {
+      for (int l = 0; l < p.L; ++l) out[(size_t)l * out_layer_stride] = INFINITY;
+    } else {
+      *out = INFINITY;
+    }
+    return;
+  }
+  const size_t raw_layer_stride = (size_t)p.B * p.Hkv * (size_t)p.t_pad * NQ;  // in float4
+  const float4* r = reinterpret_cast<const float4*>(p.raw) + (((size_t)b * p.Hkv + kvh) * (size_t)p.t_pad + t) * NQ;
+  const float2* ms = reinterpret_cast<const float2*>(p.mean_std) + ((size_t)b * Hq + (size_t)kvh * G);
+  const size_t ms_layer_stride = (size_t)p.B * Hq;  // in float2
+  const bool normalize = p.normalize != 0, group_mean = p.group_reduce == TRIATTN_REDUCE_MEAN;
+  float acc = 0.f;
+
+  // z-normalise, reduce over the G query heads; then fold layer l into the accumulator / the output
+  auto layer = [&](const float4 (&q)[NQ], int l) {
+    const float2* msl = ms + (size_t)l * ms_layer_stride;
+    float mx = -INFINITY, sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < G; ++j) {
+      const float4 v = q[j >> 2];
+      const float sj = (j & 3) == 0 ? v.x : (j & 3) == 1 ? v.y : (j & 3) == 2 ? v.z : v.w;
+      float2 m = __ldg(msl + j);
+      if (!normalize) m = make_float2(0.f, 1.f);  // (s - 0) * 1 == s exactly
+      const float z = __fmul_rn(__fsub_rn(sj, m.x), m.y);
+      mx = fmaxf(mx, z);
+      sum = __fadd_rn(sum, z);
+    }
+    const float lv = group_mean ? __fdiv_rn(sum, (float)G) : mx;
+    if (LR == TRIATTN_REDUCE_NONE) {
+      out[(size_t)l * out_layer_stride] = lv;
+    } else if (LR == TRIATTN_REDUCE_MAX) {
+      acc = l == 0 ? lv : fmaxf(acc, lv);
+    } else {
+      acc = l == 0 ? lv : __fadd_rn(acc, lv);
+    }
+  };
+
+  int l0 = 0;
+  for (; l0 + kFinalizePrefetch <= p.L; l0 += kFinalizePrefetch) {
+    float4 q[kFinalizePrefetch][NQ];
+#pragma unroll
+    for (int i = 0; i < kFinalizePrefetch; ++i)
+#pragma unroll
+      for (int n = 0; n < NQ; ++n) q[i][n] = r[(size_t)(l0 + i) * raw_layer_stride + n];
+#pragma unroll
+    for (int i = 0; i < kFinalizePrefetch; ++i) layer(q[i], l0 + i);
+  }
+  for (; l0 < p.L; ++l0) {
+    float4 q[NQ];
+#pragma unroll
+    for (int n = 0; n < NQ; ++n) q[n] = r[(size_t)l0 * raw_layer_stride + n];
+    layer(q, l0);
+  }
+  if (LR == TRIATTN_REDUCE_MEAN) acc = __fdiv_rn(acc, (float)p.L);
+  if (LR != TRIATTN_REDUCE_NONE) *out = acc;
+}
+
 }  // namespace triattn
