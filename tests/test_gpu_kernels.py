@@ -58,8 +58,11 @@ def _run_stages(p, stats, caches, block_ids):
                 status=status, g=g, dstats=dstats, rs=rs, pre=pre)
 
 
+@pytest.mark.parametrize("score_path", ["mma", "fma"])
 @pytest.mark.parametrize("name", GROUP_CASES)
-def test_score_finalize_select_compact_vs_checker(manifest, selector_cases, name):
+def test_score_finalize_select_compact_vs_checker(manifest, selector_cases, name, score_path, monkeypatch):
+    # both streaming scorers (tensor-core default, CUDA-core variant) against the same checker and fixtures
+    monkeypatch.setenv("TRIATTN_SCORE_PATH", score_path)
     p = manifest["selector_cases"]["cases"][name]
     stats, caches, block_ids = build_paged_case(p)
     assert tensor_sha(stats.q_mean_real, stats.q_mean_imag, stats.q_abs_mean, *caches) == p["input_sha256"]

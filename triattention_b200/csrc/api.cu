@@ -14,6 +14,7 @@
 #include "finalize.cuh"
 #include "prep.cuh"
 #include "score.cuh"
+#include "score_fma.cuh"
 #include "score_mma.cuh"
 #include "select.cuh"
 
@@ -51,6 +52,31 @@ bool block_is_dense(const triattn_paged_layout* L) {
   const bool nhd = L->head_stride == D && L->token_stride == H * D;
   const bool hnd = L->token_stride == D && L->head_stride == bs * D;
   return nhd || hnd || (H == 1 && L->token_stride == D) || (bs == 1 && L->head_stride == D);
+}
+
+template <int D, bool IL>
+int launch_score_fma(const ScoreParams& p, int gp, dim3 grid, size_t smem, cudaStream_t st) {
+#define TRIATTN_LAUNCH(GP)                                                                                  \
+  {                                                                                                         \
+    auto kern = score_paged_mean_kernel<D, GP, IL>;                                                         \
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
+      return TRIATTN_ERR_CUDA;                                                                              \
+    kern<<<grid, kScoreThreadsWS, smem, st>>>(p);                                                           \
+    return check_launch();                                                                                  \
+  }
+  switch (gp) {
+    case 1: TRIATTN_LAUNCH(1)
+    case 2: TRIATTN_LAUNCH(2)
+    case 4: TRIATTN_LAUNCH(4)
+    default: return TRIATTN_ERR_UNSUPPORTED_SHAPE;
+  }
+#undef TRIATTN_LAUNCH
+}
+
+// TRIATTN_SCORE_PATH=fma selects the CUDA-core streaming kernel (no tensor cores); anything else the default.
+bool score_path_is_fma() {
+  const char* v = std::getenv("TRIATTN_SCORE_PATH");
+  return v != nullptr && v[0] == 'f' && v[1] == 'm' && v[2] == 'a' && v[3] == 0;
 }
 
 template <int D, bool IL>
@@ -240,6 +266,21 @@ int triattn_score_paged(const triattn_paged_layout* layout, const void* const* k
     p.tiles_per_cta = tpc;
     dim3 grid((unsigned)((max_tiles + tpc - 1) / tpc), (unsigned)Y.num_layers, (unsigned)Y.num_reqs);
     const size_t smem = (size_t)stages * stage_bytes;
+    if (score_path_is_fma()) {
+      // the CUDA-core kernel works on batches of 16/gpv tokens and keeps a table of work items per stage
+      const int gpv = std::min(gp, 4), nsub = gp / gpv, nt = kLPK / gpv;
+      const long long stage_tok = (long long)mb * Y.block_size;
+      const long long n_items = nhd ? (long long)Y.num_kv_heads * nsub * (stage_tok / nt)
+                                    : (long long)mb * Y.num_kv_heads * nsub * (Y.block_size / nt);
+      const bool ok = (nhd ? (stage_tok % nt) == 0 : (Y.block_size % nt) == 0) && n_items > 0 && n_items <= kMaxScoreItems;
+      if (ok) {
+        if (Y.head_dim == 128)
+          return Y.rope_interleaved ? launch_score_fma<128, true>(p, gpv, grid, smem, st)
+                                    : launch_score_fma<128, false>(p, gpv, grid, smem, st);
+        return Y.rope_interleaved ? launch_score_fma<64, true>(p, gpv, grid, smem, st)
+                                  : launch_score_fma<64, false>(p, gpv, grid, smem, st);
+      }
+    }
     if (Y.head_dim == 128)
       return Y.rope_interleaved ? launch_score_mma<128, true>(p, grid, smem, st)
                                 : launch_score_mma<128, false>(p, grid, smem, st);
