@@ -217,3 +217,75 @@ def test_token_pool_layout_block_size_one():
         oracle.compact_per_head(exp, slots, 1, keep, T, preserve_dropped_tokens=False, kv_axis=0)
         assert torch.equal(dc[l].cpu().view(torch.int16), exp.view(torch.int16))
     assert res.kept_block_ids[0] == slots[:budget] and res.removed_block_ids[0] == slots[budget:]
+
+
+@pytest.mark.parametrize("score_path", ["mma", "fma"])
+@pytest.mark.parametrize("hkv,g,D,bs,hnd,rope_style", [
+    (8, 4, 128, 16, False, "half"),        # the benchmark geometry
+    (8, 4, 128, 16, True, "half"),         # head-major blocks
+    (2, 3, 128, 16, False, "half"),        # odd group size, padded to 4 slots
+    (4, 1, 64, 16, False, "half"),         # no grouping, head_dim 64
+    (2, 2, 64, 32, True, "interleaved"),   # interleaved RoPE pairs, 32-token head-major blocks
+    (1, 6, 128, 16, False, "interleaved"), # 6 query heads per KV head: two column tiles
+    (2, 8, 128, 8, False, "half"),         # blocks smaller than a 16-key tile
+    (1, 12, 128, 16, False, "half"),       # more than 8 query heads: virtual heads
+    (3, 4, 128, 16, False, "half"),        # KV-head count that does not divide the warp count
+])
+def test_scorer_shape_sweep(hkv, g, D, bs, hnd, rope_style, score_path, monkeypatch):
+    """Raw scores of both streaming scorers against the checker over head/group/block geometries, ragged lengths."""
+    monkeypatch.setenv("TRIATTN_SCORE_PATH", score_path)
+    gen = torch.Generator().manual_seed(synth.seed_for(7, hkv * 100 + g * 10 + (1 if hnd else 0)))
+    L, lens = 2, [333, 150, 16]
+    Hq = hkv * g
+    inv = synth.rope_inv_freq(D, 1e6)
+    stats = synth.make_stats(L, Hq, D, inv, gen, rope_style=rope_style)
+    nblk = [(t + bs - 1) // bs for t in lens]
+    total = sum(nblk) + 5
+    perm = synth.random_block_ids(sum(nblk), total, gen)
+    ids, o = [], 0
+    for n in nblk:
+        ids.append(perm[o:o + n])
+        o += n
+    caches = []
+    for _ in range(L):
+        if hnd:
+            c = torch.zeros((2, total, hkv, bs, D), dtype=torch.bfloat16).permute(0, 1, 3, 2, 4)
+        else:
+            c = synth.make_paged_layer(total, bs, hkv, D, kv_axis=0)
+        for b, t in enumerate(lens):
+            synth.write_tokens_to_paged(c, 0, ids[b], bs, synth.make_rotated_keys(hkv, t, D, inv, gen, rope_style=rope_style),
+                                        synth.make_values(hkv, t, D, gen))
+        caches.append(c)
+    dc = [c.to(DEV) for c in caches]
+    if hnd:
+        dc = [torch.zeros((2, total, hkv, bs, D), dtype=torch.bfloat16, device=DEV).permute(0, 1, 3, 2, 4) for _ in caches]
+        for d, c in zip(dc, caches):
+            d.copy_(c)
+    view = ops.PagedCacheView.from_layers(dc, kv_axis=0)
+    width = max(nblk)
+    bt = torch.zeros((len(lens), width), dtype=torch.int32)
+    for b, row in enumerate(ids):
+        bt[b, :len(row)] = torch.tensor(row, dtype=torch.int32)
+    bt = bt.to(DEV)
+    layout = view.layout(len(lens), g, width, rope_interleaved=rope_style == "interleaved")
+    dstats = device_stats(stats, oracle.geometric_offsets())
+    seq = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    rs = torch.tensor([t + 5 for t in lens], dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    w = ops.prep_weights(dstats, rs)
+    raw, mom = ops.score_paged(view, layout, bt, seq, w, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    for b, t in enumerate(lens):
+        layers = [(l, c, ids[b], bs) for l, c in enumerate(caches)]
+        _, ref_raws = oracle.final_scores_group_per_head(layers, _stats_dict(stats), inv, oracle.geometric_offsets(), t,
+                                                         t + 5, window_size=0, return_raw=True, kv_axis=0,
+                                                         rope_style=rope_style)
+        got = raw[:, b, :, :t, :g].permute(0, 1, 3, 2).reshape(L, Hq, t).cpu()
+        ref = torch.stack(ref_raws)
+        sigma = ref.std(dim=-1, keepdim=True)
+        worst = float(((got - ref).abs() / torch.maximum(ref.abs(), sigma).clamp_min(1e-6)).max())
+        assert worst <= 1e-3, f"request {b}: raw score error {worst}"  # tolerance of the scores: 1e-3 relative
+        m = mom[:, b].cpu()
+        assert torch.allclose(m[..., 0], got.double().sum(-1), rtol=1e-6, atol=1e-4)
+        assert torch.allclose(m[..., 1], (got.double() ** 2).sum(-1), rtol=1e-6, atol=1e-4)
