@@ -221,6 +221,22 @@ int triattn_compact_paged_preserve(const triattn_paged_layout* layout /* host */
                                    const int32_t* keep_counts, int max_dropped_rows, void* scratch,
                                    size_t scratch_bytes, uint32_t* device_status, void* stream);
 
+/*
+ * Block-table rewrite after compaction, on the device and for all requests of a step at once:
+ * request b keeps the first ceil(lens_after[b] / block_size) entries of its block_table row
+ * (blocks_after[b], never more than blocks_before[b]); the removed tail entries are appended to
+ * freed_ids in request order, then row order, and overwritten with fill_value.  *freed_count
+ * receives the number of removed blocks; if it exceeds freed_capacity the list is truncated and
+ * TRIATTN_DEV_BAD_LENGTH is raised in *device_status.
+ * Replaces truncate_tail_reclaim_group (triattention/vllm/runtime/layout_engine.py:209-227) and the
+ * num_blocks_per_row shrink of apply_worker_block_reclaim_events
+ * (triattention/vllm/runtime/worker_reclaim_sync.py:95-112) for engines that keep block tables on the device.
+ */
+int triattn_rewrite_block_tables(int32_t* block_table, int num_reqs, int max_blocks_per_req, int block_size,
+                                 const int32_t* blocks_before, const int32_t* lens_after, int32_t* blocks_after,
+                                 int32_t* freed_ids, int freed_capacity, int32_t* freed_count, int32_t fill_value,
+                                 uint32_t* device_status, void* stream);
+
 /* Bytes of workspace triattn_compress_paged needs for this geometry. */
 size_t triattn_compress_workspace_bytes(const triattn_paged_layout* layout /* host */, int num_offsets,
                                         int offset_agg, int keep_pitch);

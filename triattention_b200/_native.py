@@ -41,6 +41,7 @@ EXPORTED_SYMBOLS = (
     "triattn_compact_paged_preserve",
     "triattn_compress_workspace_bytes",
     "triattn_compress_paged",
+    "triattn_rewrite_block_tables",
 )
 
 
@@ -106,6 +107,8 @@ def _declare(lib) -> None:
     lib.triattn_compress_paged.restype = c_int
     lib.triattn_compress_paged.argtypes = [LP, P, P, P, P, P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int,
                                            c_int, c_int, P, c_size_t, P, c_int, P, P]
+    lib.triattn_rewrite_block_tables.restype = c_int
+    lib.triattn_rewrite_block_tables.argtypes = [P, c_int, c_int, c_int, P, P, P, P, c_int, P, c_int, P, P]
 
 
 def load():

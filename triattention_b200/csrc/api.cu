@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cmath>
 #include <cstdint>
 #include <cstdlib>
@@ -13,6 +14,7 @@
 #include "compact.cuh"
 #include "finalize.cuh"
 #include "prep.cuh"
+#include "reclaim.cuh"
 #include "score.cuh"
 #include "score_fma.cuh"
 #include "score_mma.cuh"
@@ -34,6 +36,20 @@ int env_int(const char* name, int fallback, int lo, int hi) {
 }
 
 int check_launch() { return cudaGetLastError() == cudaSuccess ? TRIATTN_OK : TRIATTN_ERR_CUDA; }
+
+// Opt a kernel in to `smem` bytes of dynamic shared memory; the attribute call is made only when a device has
+// not yet been raised to that size for this kernel.
+constexpr int kMaxDevicesSmem = 64;
+template <auto Kern>
+bool ensure_dynamic_smem(size_t smem) {
+  static std::atomic<size_t> raised[kMaxDevicesSmem];
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevicesSmem) return false;
+  if (raised[dev].load(std::memory_order_relaxed) >= smem) return true;
+  if (cudaFuncSetAttribute(Kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return false;
+  raised[dev].store(smem, std::memory_order_relaxed);
+  return true;
+}
 
 int validate_layout(const triattn_paged_layout* L) {
   if (L == nullptr) return TRIATTN_ERR_INVALID_ARGUMENT;
@@ -58,10 +74,8 @@ template <int D, bool IL>
 int launch_score_fma(const ScoreParams& p, int gp, dim3 grid, size_t smem, cudaStream_t st) {
 #define TRIATTN_LAUNCH(GP)                                                                                  \
   {                                                                                                         \
-    auto kern = score_paged_mean_kernel<D, GP, IL>;                                                         \
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
-      return TRIATTN_ERR_CUDA;                                                                              \
-    kern<<<grid, kScoreThreadsWS, smem, st>>>(p);                                                           \
+    if (!ensure_dynamic_smem<score_paged_mean_kernel<D, GP, IL>>(smem)) return TRIATTN_ERR_CUDA;             \
+    score_paged_mean_kernel<D, GP, IL><<<grid, kScoreThreadsWS, smem, st>>>(p);                             \
     return check_launch();                                                                                  \
   }
   switch (gp) {
@@ -83,10 +97,8 @@ template <int D, bool IL>
 int launch_score_mma(const ScoreParams& p, dim3 grid, size_t smem, cudaStream_t st) {
 #define TRIATTN_LAUNCH(NT)                                                                                  \
   {                                                                                                         \
-    auto kern = score_paged_mma_kernel<D, IL, NT>;                                                          \
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
-      return TRIATTN_ERR_CUDA;                                                                              \
-    kern<<<grid, kScoreThreadsWS, smem, st>>>(p);                                                           \
+    if (!ensure_dynamic_smem<score_paged_mma_kernel<D, IL, NT>>(smem)) return TRIATTN_ERR_CUDA;              \
+    score_paged_mma_kernel<D, IL, NT><<<grid, kScoreThreadsWS, smem, st>>>(p);                              \
     return check_launch();                                                                                  \
   }
   if (p.gp_total <= 4) TRIATTN_LAUNCH(1)
@@ -450,6 +462,30 @@ int triattn_compact_paged_preserve(const triattn_paged_layout* layout, void* con
   return compact_common(layout, k_layer_ptrs, v_layer_ptrs, block_table, seq_lens, keep, keep_layer_stride,
                         keep_req_stride, keep_head_stride, keep_counts, scratch, (long long)per_stream,
                         max_dropped_rows, true, device_status, stream);
+}
+
+int triattn_rewrite_block_tables(int32_t* block_table, int num_reqs, int max_blocks_per_req, int block_size,
+                                 const int32_t* blocks_before, const int32_t* lens_after, int32_t* blocks_after,
+                                 int32_t* freed_ids, int freed_capacity, int32_t* freed_count, int32_t fill_value,
+                                 uint32_t* device_status, void* stream) {
+  if (!block_table || !blocks_before || !lens_after || !blocks_after || !freed_count) return TRIATTN_ERR_INVALID_ARGUMENT;
+  if (num_reqs <= 0 || max_blocks_per_req <= 0 || block_size <= 0 || freed_capacity < 0) return TRIATTN_ERR_INVALID_ARGUMENT;
+  if (freed_capacity > 0 && !freed_ids) return TRIATTN_ERR_INVALID_ARGUMENT;
+  ReclaimParams p{};
+  p.block_table = block_table;
+  p.blocks_before = blocks_before;
+  p.lens_after = lens_after;
+  p.blocks_after = blocks_after;
+  p.freed_ids = freed_ids;
+  p.freed_count = freed_count;
+  p.status = device_status;
+  p.B = num_reqs;
+  p.max_blocks = max_blocks_per_req;
+  p.block_size = block_size;
+  p.freed_capacity = freed_capacity;
+  p.fill_value = fill_value;
+  rewrite_block_tables_kernel<<<1, kReclaimThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return check_launch();
 }
 
 // ------------------------------------------------------------------------- fused step

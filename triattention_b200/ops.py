@@ -290,3 +290,29 @@ def compress_paged(view: PagedCacheView, layout: PagedLayout, stats: DeviceStats
         flags, int(window), 1 if normalize else 0, layer_reduce, _ptr(workspace), workspace.numel(),
         _ptr(keep_out), int(keep_pitch), _ptr(status), _stream()), "compress_paged")
     return keep_out
+
+
+def rewrite_block_tables(block_table: torch.Tensor, blocks_before: torch.Tensor, lens_after: torch.Tensor,
+                         block_size: int, freed_capacity: Optional[int] = None, fill_value: int = 0,
+                         status: Optional[torch.Tensor] = None):
+    """Shrink every row of a device block table to ``ceil(lens_after / block_size)`` entries in place
+    (``triattn_rewrite_block_tables``).
+
+    Returns ``(blocks_after [B] int32, freed_ids [capacity] int32, freed_count [1] int32)``, all on the device;
+    the freed ids are ordered by request, then by position in the row, like the concatenation of the
+    ``removed_block_ids`` lists of layout_engine.truncate_tail_reclaim_group.
+    """
+    lib = _native.load()
+    _require_cuda(block_table, "block_table")
+    if block_table.dtype != torch.int32 or block_table.dim() != 2 or not block_table.is_contiguous():
+        raise ValueError("block_table must be a contiguous int32 [B, max_blocks] tensor")
+    B, width = int(block_table.shape[0]), int(block_table.shape[1])
+    dev = block_table.device
+    cap = B * width if freed_capacity is None else int(freed_capacity)
+    blocks_after = torch.empty(B, dtype=torch.int32, device=dev)
+    freed = torch.empty(max(cap, 1), dtype=torch.int32, device=dev)
+    count = torch.zeros(1, dtype=torch.int32, device=dev)
+    _native.check(lib.triattn_rewrite_block_tables(
+        _ptr(block_table), B, width, int(block_size), _ptr(blocks_before), _ptr(lens_after), _ptr(blocks_after),
+        _ptr(freed), cap, _ptr(count), int(fill_value), _ptr(status), _stream()), "rewrite_block_tables")
+    return blocks_after, freed, count
