@@ -237,6 +237,24 @@ int triattn_rewrite_block_tables(int32_t* block_table, int num_reqs, int max_blo
                                  int32_t* freed_ids, int freed_capacity, int32_t* freed_count, int32_t fill_value,
                                  uint32_t* device_status, void* stream);
 
+/*
+ * Effective-length overrides for the step after a compaction, one launch for the whole batch:
+ *   seq_lens[r]      = effective_base[idx_mapping[r]] + (query_start_loc[r+1] - query_start_loc[r])
+ *                      for every batch entry r whose row has effective_base >= 0 (others untouched);
+ *   positions_out[i] = positions[i] + pos_delta[idx_mapping[r]] for the tokens i of entry r
+ *                      (tokens outside every segment are copied).
+ * effective_base / pos_delta are dense int32 arrays over request-state rows (null = absent);
+ * seq_lens or positions may be null.  counters[4] (device, zeroed by the call) receives: rows with a
+ * base override, rows with a non-zero delta, 1 if query_start_loc decreases somewhere, 1 if a
+ * segment leaves [0, num_tokens].  apply = 0 only fills the counters.
+ * Replaces overwrite_seq_lens_from_effective_lengths / overwrite_seq_lens_from_effective_base_map /
+ * shift_positions_from_sparse_deltas (triattention/vllm/runtime/input_patch_ops.py:66-215).
+ */
+int triattn_apply_effective_overrides(const int32_t* idx_mapping, const int32_t* query_start_loc, int num_reqs,
+                                      const int32_t* effective_base, const int32_t* pos_delta, int num_rows,
+                                      int32_t* seq_lens, const int64_t* positions, int64_t* positions_out,
+                                      int num_tokens, int32_t* counters, int apply, void* stream);
+
 /* Bytes of workspace triattn_compress_paged needs for this geometry. */
 size_t triattn_compress_workspace_bytes(const triattn_paged_layout* layout /* host */, int num_offsets,
                                         int offset_agg, int keep_pitch);

@@ -33,3 +33,4 @@ from .compaction import (  # noqa: F401
     truncate_tail_blocks,
     fallback_keep_indices,
 )
+from . import input_patch  # noqa: F401,E402

@@ -4,7 +4,8 @@
 Run where a checkout of the reference is available (default: a directory
 ``reference`` next to this repository, override with ``TRIATTN_REFERENCE_ROOT``)::
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py                       # everything
+    python tests/golden/make_golden.py --only input_patch    # only input_patch_cases.npz
 
 The reference is imported unmodified, on CPU, with three test-side shims:
 
@@ -390,13 +391,77 @@ def gen_hook_cases(out: dict):
     out["hook_cases"] = {"params": p, "results": results}
 
 
+def gen_input_patch_cases(out: dict):
+    """Outputs of the reference's effective-length override helpers (runtime/input_patch_ops.py:66-215) on CPU tensors."""
+    from triattention.vllm.runtime import input_patch_ops as ref
+
+    gen = torch.Generator().manual_seed(20269001)
+    arrays, cases = {}, {}
+
+    def batch(num_reqs, num_rows, max_q, start=0, pad=0):
+        rows = torch.randperm(num_rows, generator=gen)[:num_reqs].to(torch.int32)
+        q_lens = torch.randint(0 if max_q > 1 else 1, max_q + 1, (num_reqs,), generator=gen)
+        qsl = torch.zeros(num_reqs + 1, dtype=torch.int32)
+        qsl[1:] = torch.cumsum(q_lens, 0).to(torch.int32)
+        qsl += start
+        total = int(qsl[-1]) + pad
+        positions = torch.randint(0, 200000, (total,), generator=gen, dtype=torch.int64)
+        seq_lens = torch.randint(1, 200000, (num_reqs + 3,), generator=gen, dtype=torch.int32)
+        return rows, qsl, positions, seq_lens
+
+    specs = {
+        "decode_all_rows": dict(num_reqs=7, num_rows=16, max_q=1, frac=1.0),
+        "mixed_prefill_sparse": dict(num_reqs=12, num_rows=40, max_q=9, frac=0.4),
+        "single_request": dict(num_reqs=1, num_rows=4, max_q=5, frac=1.0),
+        "offset_segments_padded": dict(num_reqs=6, num_rows=9, max_q=4, frac=0.5, start=3, pad=5),
+        "missing_row": dict(num_reqs=5, num_rows=12, max_q=3, frac=0.6, extra_key=True),
+        "zero_deltas_only": dict(num_reqs=4, num_rows=8, max_q=2, frac=0.5, zero_delta=True),
+    }
+    for name, sp in specs.items():
+        rows, qsl, positions, seq_lens = batch(sp["num_reqs"], sp["num_rows"], sp["max_q"], sp.get("start", 0), sp.get("pad", 0))
+        n_sel = max(1, int(round(sp["frac"] * sp["num_reqs"])))
+        chosen = rows[torch.randperm(sp["num_reqs"], generator=gen)[:n_sel]].tolist()
+        base_map = {int(r): int(torch.randint(1, 5000, (1,), generator=gen)) for r in chosen}
+        delta_map = {int(r): (0 if sp.get("zero_delta") else -int(torch.randint(1, 3000, (1,), generator=gen))) for r in chosen}
+        if sp.get("extra_key"):
+            absent = [r for r in range(sp["num_rows"]) if r not in set(rows.tolist())][0]
+            base_map[absent] = 77
+            delta_map[absent] = -5
+        dense = torch.randint(0, 9000, (sp["num_rows"],), generator=gen, dtype=torch.int32)
+        s1 = seq_lens.clone()
+        ref.overwrite_seq_lens_from_effective_lengths(idx_mapping=rows, query_start_loc=qsl,
+                                                      effective_num_computed_tokens=dense, seq_lens=s1)
+        s2 = seq_lens.clone()
+        ok = ref.overwrite_seq_lens_from_effective_base_map(idx_mapping=rows, query_start_loc=qsl,
+                                                            effective_base_by_req_idx=dict(base_map), seq_lens=s2)
+        shifted = ref.shift_positions_from_sparse_deltas(idx_mapping=rows, query_start_loc=qsl, positions=positions,
+                                                         pos_delta_by_req_idx=dict(delta_map))
+        for k, v in dict(idx_mapping=rows, query_start_loc=qsl, positions=positions, seq_lens=seq_lens, dense_base=dense,
+                         base_keys=torch.tensor(list(base_map.keys()), dtype=torch.int32),
+                         base_vals=torch.tensor(list(base_map.values()), dtype=torch.int32),
+                         delta_vals=torch.tensor([delta_map[k2] for k2 in base_map.keys()], dtype=torch.int32),
+                         seq_lens_dense_out=s1, seq_lens_sparse_out=s2).items():
+            arrays[f"{name}/{k}"] = v.numpy()
+        if shifted is not None:
+            arrays[f"{name}/positions_out"] = shifted.numpy()
+        cases[name] = dict(sparse_applied=bool(ok), shifted=shifted is not None, num_rows=sp["num_rows"])
+    np.savez_compressed(HERE / "input_patch_cases.npz", **arrays)
+    out["input_patch_cases"] = {"file": "input_patch_cases.npz", "cases": cases}
+
+
 def main():
+    if len(sys.argv) > 2 and sys.argv[1] == "--only" and sys.argv[2] == "input_patch":
+        out = json.loads((HERE / "manifest.json").read_text())
+        gen_input_patch_cases(out)
+        (HERE / "manifest.json").write_text(json.dumps(out, indent=1, sort_keys=True))
+        return
     ref_scoring, ref_config = install_shims()
     out = {"torch": torch.__version__}
     gen_score_cases(ref_scoring, ref_config, out)
     gen_selector_cases(out)
     gen_real_stats_case(out)
     gen_hook_cases(out)
+    gen_input_patch_cases(out)
     (HERE / "manifest.json").write_text(json.dumps(out, indent=1, sort_keys=True))
     print("wrote", [p.name for p in HERE.iterdir()])
 

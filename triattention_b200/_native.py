@@ -42,6 +42,7 @@ EXPORTED_SYMBOLS = (
     "triattn_compress_workspace_bytes",
     "triattn_compress_paged",
     "triattn_rewrite_block_tables",
+    "triattn_apply_effective_overrides",
 )
 
 
@@ -109,6 +110,8 @@ def _declare(lib) -> None:
                                            c_int, c_int, P, c_size_t, P, c_int, P, P]
     lib.triattn_rewrite_block_tables.restype = c_int
     lib.triattn_rewrite_block_tables.argtypes = [P, c_int, c_int, c_int, P, P, P, P, c_int, P, c_int, P, P]
+    lib.triattn_apply_effective_overrides.restype = c_int
+    lib.triattn_apply_effective_overrides.argtypes = [P, P, c_int, P, P, c_int, P, P, P, c_int, P, c_int, P]
 
 
 def load():

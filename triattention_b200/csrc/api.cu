@@ -13,6 +13,7 @@
 #include "common.cuh"
 #include "compact.cuh"
 #include "finalize.cuh"
+#include "overrides.cuh"
 #include "prep.cuh"
 #include "reclaim.cuh"
 #include "score.cuh"
@@ -485,6 +486,33 @@ int triattn_rewrite_block_tables(int32_t* block_table, int num_reqs, int max_blo
   p.freed_capacity = freed_capacity;
   p.fill_value = fill_value;
   rewrite_block_tables_kernel<<<1, kReclaimThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return check_launch();
+}
+
+int triattn_apply_effective_overrides(const int32_t* idx_mapping, const int32_t* query_start_loc, int num_reqs,
+                                      const int32_t* effective_base, const int32_t* pos_delta, int num_rows,
+                                      int32_t* seq_lens, const int64_t* positions, int64_t* positions_out,
+                                      int num_tokens, int32_t* counters, int apply, void* stream) {
+  if (!idx_mapping || !query_start_loc || !counters || num_reqs <= 0 || num_rows < 0 || num_tokens < 0)
+    return TRIATTN_ERR_INVALID_ARGUMENT;
+  if (positions != nullptr && positions_out == nullptr) return TRIATTN_ERR_INVALID_ARGUMENT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (cudaMemsetAsync(counters, 0, 4 * sizeof(int32_t), st) != cudaSuccess) return TRIATTN_ERR_CUDA;
+  OverrideParams p{};
+  p.idx_mapping = idx_mapping;
+  p.query_start_loc = query_start_loc;
+  p.num_reqs = num_reqs;
+  p.effective_base = effective_base;
+  p.pos_delta = pos_delta;
+  p.num_rows = num_rows;
+  p.seq_lens = seq_lens;
+  p.positions = positions;
+  p.positions_out = positions_out;
+  p.num_tokens = num_tokens;
+  p.counters = counters;
+  p.apply = apply ? 1 : 0;
+  const int n = std::max(num_reqs, positions != nullptr ? num_tokens : 0);
+  apply_effective_overrides_kernel<<<(n + 255) / 256, 256, 0, st>>>(p);
   return check_launch();
 }
 
