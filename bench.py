@@ -64,9 +64,9 @@ def measured_peaks():
 
 
 # DRAM traffic of the score kernel per key from the ncu capture summarised in
-# profiles/score_paged_mma_kernel_c1_2layers.md (dram__bytes_read + dram__bytes_write = 1.0743 GB + 64.7 MB for
+# profiles/score_paged_mma_kernel_c1_2layers.md (dram__bytes_read + dram__bytes_write = 1.0743 GB + 64.5 MB for
 # 4 194 304 keys); traffic grows in proportion to the keys scored, so a full launch is this figure x its keys.
-SCORE_DRAM_BYTES_PER_KEY_NCU = (1.074314e9 + 64.68e6) / 4194304.0
+SCORE_DRAM_BYTES_PER_KEY_NCU = (1.074343e9 + 64.52e6) / 4194304.0
 
 
 def algorithmic_bytes_per_key(T: int, k: int) -> float:
