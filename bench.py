@@ -433,7 +433,8 @@ def run_ours(args, world, rank, local):
         "keys_per_s_per_gpu": value / world,
         "step_hbm_gbs": bytes_step / (step_ms * 1e-3) / 1e9, "step_hbm_frac": bytes_step / (step_ms * 1e-3) / 1e9 / peak,
         "stage_ms": stage,
-        "roofline": {"kernel": "score_paged_mma_kernel", "bound": "hbm", "achieved": achieved, "peak": peak,
+        "roofline": {"kernel": ("score_paged_mean_kernel" if os.environ.get("TRIATTN_SCORE_PATH") == "fma"
+                                else "score_paged_mma_kernel"), "bound": "hbm", "achieved": achieved, "peak": peak,
                      "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
                      "traffic": (keys_per_gpu * SCORE_DRAM_BYTES_PER_KEY_NCU
                                  if (c["D"], c["g"], c["Hkv_local"]) == (128, 4, 8) else None),
