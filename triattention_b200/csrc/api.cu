@@ -264,17 +264,30 @@ int triattn_score_paged(const triattn_paged_layout* layout, const void* const* k
     p.mb = mb;
     p.stages = stages;
     const int max_tiles = (Y.max_blocks_per_req + mb - 1) / mb;
-    const long long total_tiles = (long long)max_tiles * Y.num_layers * Y.num_reqs;
-    // Tiles per CTA: every CTA pays a fixed start-up (weight fragments, first copies: about two tiles' worth),
-    // while few CTAs per SM leave a ragged last wave; tpc ~ sqrt(total_tiles / (SMs/2)) balances the two.
-    // At least ~64 KB and at most ~2 MB of keys per CTA, and the CTA's block ids must fit its shared-memory table.
+    // Tiles per CTA: every CTA pays a fixed start-up (weight fragments, first copies: about two tiles' worth) and
+    // the CTAs run in waves of 2 per SM, so the launch takes about waves(tpc) * (tpc + 2) tile times; take the
+    // tpc that minimises it.  At least ~64 KB and at most ~2 MB of keys per CTA, and the CTA's block ids must
+    // fit its shared-memory table.
     const int min_tpc = (int)std::max<long long>(1, (64 * 1024) / stage_bytes);
     int max_tpc = (int)std::max<long long>(min_tpc, (2 * 1024 * 1024) / stage_bytes);
     max_tpc = std::max(1, std::min(max_tpc, kMaxPrefetchedBlocks / mb));
-    int tpc = (int)std::lround(std::sqrt((double)total_tiles / (kSMs / 2.0)));
-    tpc = std::max(std::min(min_tpc, max_tpc), std::min(tpc, max_tpc));
-    // equal shares for the CTAs of one (layer, request)
-    tpc = (max_tiles + (max_tiles + tpc - 1) / tpc - 1) / ((max_tiles + tpc - 1) / tpc);
+    const int lo_tpc = std::min(min_tpc, max_tpc);
+    int tpc = lo_tpc;
+    {
+      const long long slots = (long long)kSMs * 2;
+      const long long lb = (long long)Y.num_layers * Y.num_reqs;
+      long long best = -1;
+      for (int c = lo_tpc; c <= std::min(max_tpc, max_tiles); ++c) {
+        const long long per_lb = (max_tiles + c - 1) / c;
+        const int share = (int)((max_tiles + per_lb - 1) / per_lb);  // equal shares for the CTAs of one (layer, request)
+        const long long waves = (per_lb * lb + slots - 1) / slots;
+        const long long cost = waves * (share + 2);
+        if (best < 0 || cost < best) {
+          best = cost;
+          tpc = share;
+        }
+      }
+    }
     tpc = env_int("TRIATTN_SCORE_TILES_PER_CTA", tpc, 1, 1 << 20);
     p.tiles_per_cta = tpc;
     dim3 grid((unsigned)((max_tiles + tpc - 1) / tpc), (unsigned)Y.num_layers, (unsigned)Y.num_reqs);

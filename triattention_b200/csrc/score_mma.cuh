@@ -249,11 +249,12 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
     const int tkA = tt * kMmaKeys + rg, tkB = tkA + 8;
     const uint32_t rowA = stage_addr + row_offset(min(tkA, stage_tokens - 1), kvh) + 16u * rt;
     const uint32_t rowB = stage_addr + row_offset(min(tkB, stage_tokens - 1), kvh) + 16u * rt;
-    float acc[NT][2][4];  // two accumulator chains per column tile
+    constexpr int NCH = NT == 1 ? 2 : 1;  // accumulator chains per column tile (two independent chains in total)
+    float acc[NT][NCH][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-      for (int ch = 0; ch < 2; ++ch)
+      for (int ch = 0; ch < NCH; ++ch)
 #pragma unroll
         for (int e = 0; e < 4; ++e) acc[nt][ch][e] = 0.f;
 
@@ -273,9 +274,9 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
           mma_bf16_16816(acc[nt][0], reA.x, reB.x, reA.y, reB.y, bri[nt][q][0][0], bri[nt][q][0][1]);
-          mma_bf16_16816(acc[nt][1], reA.z, reB.z, reA.w, reB.w, bri[nt][q][1][0], bri[nt][q][1][1]);
+          mma_bf16_16816(acc[nt][NCH - 1], reA.z, reB.z, reA.w, reB.w, bri[nt][q][1][0], bri[nt][q][1][1]);
           mma_bf16_16816(acc[nt][0], imA.x, imB.x, imA.y, imB.y, bri[nt][q + QI][0][0], bri[nt][q + QI][0][1]);
-          mma_bf16_16816(acc[nt][1], imA.z, imB.z, imA.w, imB.w, bri[nt][q + QI][1][0], bri[nt][q + QI][1][1]);
+          mma_bf16_16816(acc[nt][NCH - 1], imA.z, imB.z, imA.w, imB.w, bri[nt][q + QI][1][0], bri[nt][q + QI][1][1]);
         }
         const uint32_t rA[4] = {reA.x, reA.y, reA.z, reA.w}, rB[4] = {reB.x, reB.y, reB.z, reB.w};
         const uint32_t iA[4] = {imA.x, imA.y, imA.z, imA.w}, iB[4] = {imB.x, imB.y, imB.z, imB.w};
@@ -294,9 +295,9 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
             const int j = 2 * q + hh;
-            mma_bf16_16816(acc[nt][hh], hA[2 * hh], hB[2 * hh], hA[2 * hh + 1], hB[2 * hh + 1], bmg[nt][j][0],
+            mma_bf16_16816(acc[nt][hh % NCH], hA[2 * hh], hB[2 * hh], hA[2 * hh + 1], hB[2 * hh + 1], bmg[nt][j][0],
                            bmg[nt][j][1]);
-            mma_bf16_16816(acc[nt][hh ^ 1], lA[2 * hh], lB[2 * hh], lA[2 * hh + 1], lB[2 * hh + 1], bmg[nt][j][0],
+            mma_bf16_16816(acc[nt][(hh ^ 1) % NCH], lA[2 * hh], lB[2 * hh], lA[2 * hh + 1], lB[2 * hh + 1], bmg[nt][j][0],
                            bmg[nt][j][1]);
           }
       }
@@ -307,7 +308,7 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
           mma_bf16_16816(acc[nt][0], xA.x, xB.x, xA.y, xB.y, bri[nt][c][0][0], bri[nt][c][0][1]);
-          mma_bf16_16816(acc[nt][1], xA.z, xB.z, xA.w, xB.w, bri[nt][c][1][0], bri[nt][c][1][1]);
+          mma_bf16_16816(acc[nt][NCH - 1], xA.z, xB.z, xA.w, xB.w, bri[nt][c][1][0], bri[nt][c][1][1]);
         }
         const uint32_t wA[4] = {xA.x, xA.y, xA.z, xA.w}, wB[4] = {xB.x, xB.y, xB.z, xB.w};
         float mA[4], mB[4];
@@ -326,7 +327,7 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
           mma_bf16_16816(acc[nt][0], hA[0], hB[0], hA[1], hB[1], bmg[nt][c][0], bmg[nt][c][1]);
-          mma_bf16_16816(acc[nt][1], lA[0], lB[0], lA[1], lB[1], bmg[nt][c][0], bmg[nt][c][1]);
+          mma_bf16_16816(acc[nt][NCH - 1], lA[0], lB[0], lA[1], lB[1], bmg[nt][c][0], bmg[nt][c][1]);
         }
       }
     }
@@ -336,8 +337,14 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
     const bool okB = full || (tkB < stage_tokens && gA + 8 < seq_len);
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-      const float scA = (acc[nt][0][0] + acc[nt][1][0]) + (acc[nt][0][1] + acc[nt][1][1]);
-      const float scB = (acc[nt][0][2] + acc[nt][1][2]) + (acc[nt][0][3] + acc[nt][1][3]);
+      float c4[4];  // the column tile's accumulator, chains summed
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        if constexpr (NCH == 2) c4[e] = acc[nt][0][e] + acc[nt][1][e];
+        else c4[e] = acc[nt][0][e];
+      }
+      const float scA = c4[0] + c4[1];
+      const float scB = c4[2] + c4[3];
       if (4 * nt + rt < cur_nq) {
         float* out = raw_head + (size_t)gA * gp_total + 4 * nt;
         if (okA) {
