@@ -50,6 +50,9 @@ def parse_args():
     ap.add_argument("--tokens", type=int, default=0, help="override the cached length")
     ap.add_argument("--budget", type=int, default=0, help="override the KV budget")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--shard-of", type=int, default=0,
+                    help="on ONE GPU, run the shard one rank owns under tensor parallelism of this degree "
+                         "(the path has no collective, so this is that rank's whole job)")
     return ap.parse_args()
 
 
@@ -320,7 +323,8 @@ def run_ours(args, world, rank, local):
     _native.load()
     device = torch.device("cuda", local)
     torch.cuda.set_device(device)
-    c = resolve_config(args, world)
+    shard_of = args.shard_of if (args.shard_of and world == 1) else 0
+    c = resolve_config(args, shard_of or world)
     config_idx = sorted(CONFIGS).index(args.config)
     caches, block_ids, stats = build_device_workload(c, rank, device, config_idx)
     view = ops.PagedCacheView.from_layers(caches, kv_axis=0)
@@ -428,7 +432,8 @@ def run_ours(args, world, rank, local):
         "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
         "config": {"workload": workload_name(args, c), "per_gpu": f"{H} KV heads x {B} requests",
-                   "sharding": f"tp{world} by KV head, no collective", "l2": "inputs larger than L2 (K alone is "
+                   "sharding": (f"shard 0 of tp{shard_of} run alone on one GPU (no collective in the path)" if shard_of
+                                else f"tp{world} by KV head, no collective"), "l2": "inputs larger than L2 (K alone is "
                    f"{score_bytes / 1e9:.1f} GB per step); compacted prefix restored untimed between steps"},
         "keys_per_s_per_gpu": value / world,
         "step_hbm_gbs": bytes_step / (step_ms * 1e-3) / 1e9, "step_hbm_frac": bytes_step / (step_ms * 1e-3) / 1e9 / peak,
