@@ -330,7 +330,7 @@ def run_ours(args, world, rank, local):
     view = ops.PagedCacheView.from_layers(caches, kv_axis=0)
     B, T, k, L, H = c["B_local"], c["T"], c["k"], c["L"], c["Hkv_local"]
     saver = PrefixSaver(caches, block_ids, k)
-    comp = engine.PagedCompressor(stats, window=c["window"])
+    comp = engine.PagedCompressor(stats, window=c["window"], use_cuda_graph=os.environ.get("TRIATTN_BENCH_CUDA_GRAPH") == "1")
     seq_lens, round_starts, budgets = [T] * B, [T] * B, [k] * B
     keys_per_gpu = L * B * H * T
 

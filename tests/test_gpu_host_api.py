@@ -258,3 +258,43 @@ def test_dense_api(manifest, score_cases, tmp_path):
     assert ok, nd
     small_k, _, small_idx = comp.compress(k[:, :, :100], vv[:, :, :100])
     assert small_k.shape[2] == 100 and torch.equal(small_idx.cpu(), torch.arange(100))
+
+
+def test_engine_cuda_graph_replay_matches_eager():
+    """The batched step replayed from a CUDA graph gives the keep sets and caches of the eager call."""
+    from gpu_utils import device_stats
+    from triattention_b200 import engine
+
+    gen = torch.Generator().manual_seed(synth.seed_for(3, 5))
+    L, Hq, Hkv, D, bs, lens, budget = 2, 8, 2, 128, 16, [300, 257], 128
+    inv = synth.rope_inv_freq(D, 5e5)
+    stats = synth.make_stats(L, Hq, D, inv, gen)
+    nblk = [(t + bs - 1) // bs for t in lens]
+    total = sum(nblk) + 3
+    perm = synth.random_block_ids(sum(nblk), total, gen)
+    ids = [perm[:nblk[0]], perm[nblk[0]:]]
+    caches = []
+    for _ in range(L):
+        c = synth.make_paged_layer(total, bs, Hkv, D, kv_axis=0)
+        for b, t in enumerate(lens):
+            synth.write_tokens_to_paged(c, 0, ids[b], bs, synth.make_rotated_keys(Hkv, t, D, inv, gen),
+                                        synth.make_values(Hkv, t, D, gen))
+        caches.append(c)
+    dstats = device_stats(stats, oracle.geometric_offsets())
+    eager = engine.PagedCompressor(dstats, window=32)
+    dc = [c.cuda() for c in caches]
+    ref = eager.compress(ops.PagedCacheView.from_layers(dc, kv_axis=0), ids, lens, lens, [budget] * 2)
+    ref_keep, ref_caches = ref.keep.clone(), [c.clone() for c in dc]
+
+    graphed = engine.PagedCompressor(dstats, window=32, use_cuda_graph=True)
+    work = [c.cuda() for c in caches]
+    view = ops.PagedCacheView.from_layers(work, kv_axis=0)
+    for round_ in range(4):  # eager, capture + replay, replay, replay
+        for w, c in zip(work, caches):
+            w.copy_(c)
+        res = graphed.compress(view, ids, lens, lens, [budget] * 2)
+        assert res.device_status == 0
+        assert torch.equal(res.keep, ref_keep), f"round {round_}"
+        for w, r in zip(work, ref_caches):
+            assert torch.equal(w.view(torch.int16), r.view(torch.int16)), f"round {round_}"
+    assert len(graphed._graphs) == 1

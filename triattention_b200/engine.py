@@ -55,17 +55,25 @@ class PagedCompressor:
     offset_agg: int = _native.OFFSETS_MEAN
     flags: int = 0
     layer_reduce: int = _native.REDUCE_MEAN
+    # Replay the step from a CUDA graph once the same geometry (cache group, batch size, table width, keep pitch)
+    # has been seen twice: a decode loop compresses the same shapes over and over, and the dozen launches of a
+    # small step cost more on the host than on the device.
+    use_cuda_graph: bool = False
     _workspace: Optional[torch.Tensor] = field(default=None, repr=False)
     _staging: Optional[torch.Tensor] = field(default=None, repr=False)
     _dev_meta: Optional[torch.Tensor] = field(default=None, repr=False)
     _status_host: Optional[torch.Tensor] = field(default=None, repr=False)
+    _graphs: dict = field(default_factory=dict, repr=False)
+    _seen: set = field(default_factory=set, repr=False)
 
     def _buffers(self, n_ints: int, ws_bytes: int, device: torch.device):
         if self._staging is None or self._staging.numel() < n_ints:
             self._staging = torch.empty(n_ints, dtype=torch.int32).pin_memory()
             self._dev_meta = torch.empty(n_ints, dtype=torch.int32, device=device)
+            self._graphs.clear()  # captured graphs hold the old buffer addresses
         if self._workspace is None or self._workspace.numel() < ws_bytes:
             self._workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=device)
+            self._graphs.clear()
         if self._status_host is None:
             self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
 
@@ -123,7 +131,6 @@ class PagedCompressor:
         if prefill_lens is not None:
             sn[off + 3 * B : off + 4 * B] = prefill_lens
         dm = self._dev_meta[:n_ints]
-        dm.copy_(st, non_blocking=True)
         bt = dm[: B * max_blocks].view(B, max_blocks)
         d_seq = dm[off : off + B]
         d_rs = dm[off + B : off + 2 * B]
@@ -132,10 +139,32 @@ class PagedCompressor:
         d_status = dm[off + 4 * B : off + 4 * B + 1]
         ws = self._workspace
         keep = ws[ws_bytes // 256 * 256 + 256 :][:keep_bytes].view(torch.int32).view(B, view.num_kv_heads, keep_pitch)
-        ops.compress_paged(
-            view, layout, self.stats, bt, d_seq, d_rs, d_pre, d_kc, keep_pitch, self.window, self.normalize,
-            self.offset_agg, self.flags, self.layer_reduce, workspace=ws, keep_out=keep, status=d_status)
-        self._status_host.copy_(d_status, non_blocking=True)
+
+        def launch():
+            dm.copy_(st, non_blocking=True)
+            ops.compress_paged(
+                view, layout, self.stats, bt, d_seq, d_rs, d_pre, d_kc, keep_pitch, self.window, self.normalize,
+                self.offset_agg, self.flags, self.layer_reduce, workspace=ws, keep_out=keep, status=d_status)
+            self._status_host.copy_(d_status, non_blocking=True)
+
+        if not self.use_cuda_graph:
+            launch()
+        else:
+            key = (int(view.k_ptrs.data_ptr()), int(view.v_ptrs.data_ptr()), view.num_layers, view.num_blocks,
+                   view.block_stride, view.token_stride, view.head_stride, B, max_blocks, keep_pitch,
+                   prefill_lens is not None, int(st.data_ptr()), int(ws.data_ptr()))
+            graph = self._graphs.get(key)
+            if graph is not None:
+                graph.replay()
+            elif key not in self._seen:
+                self._seen.add(key)  # first sight: run eagerly (also the warm-up a capture needs)
+                launch()
+            else:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    launch()
+                self._graphs[key] = graph
+                graph.replay()  # a capture records, it does not execute
         torch.cuda.current_stream().synchronize()
         status = int(self._status_host.item())
         kept, removed = [], []
