@@ -263,6 +263,9 @@ int triattn_score_paged(const triattn_paged_layout* layout, const void* const* k
     p.block_bytes = (int)block_bytes;
     p.mb = mb;
     p.stages = stages;
+    p.block_group = (gp <= 8 && Y.block_size == 16 && Y.num_kv_heads * mb == kScoreConsumerWarps &&
+                     !score_path_is_fma() && env_int("TRIATTN_SCORE_BLOCK_GROUPS", 1, 0, 1) == 1)
+                        ? Y.num_kv_heads : 0;
     const int max_tiles = (Y.max_blocks_per_req + mb - 1) / mb;
     // Tiles per CTA: every CTA pays a fixed start-up (weight fragments, first copies: about two tiles' worth) and
     // the CTAs run in waves of 2 per SM, so the launch takes about waves(tpc) * (tpc + 2) tile times; take the

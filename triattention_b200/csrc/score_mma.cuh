@@ -75,6 +75,8 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
 
   extern __shared__ __align__(128) unsigned char smem_tiles[];
   __shared__ __align__(8) uint64_t full_bar[kMaxStages];
+  __shared__ __align__(8) uint64_t blk_bar[kMaxStages][kScoreConsumerWarps];  // block-group mode: one per block
+  __shared__ unsigned int s_blk_released[kMaxStages][kScoreConsumerWarps];
   __shared__ unsigned int s_released[kMaxStages];
   __shared__ int s_bt[kMaxPrefetchedBlocks];
   __shared__ int s_err;
@@ -104,6 +106,10 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(smem_u32(&full_bar[s]), 1);
       s_released[s] = 0u;
+      for (int w = 0; w < kScoreConsumerWarps; ++w) {
+        mbar_init(smem_u32(&blk_bar[s][w]), 1);
+        s_blk_released[s][w] = 0u;
+      }
     }
     mbar_fence_init();
     s_err = 0;
@@ -146,7 +152,36 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
                     kbase + (long long)blk * p.block_stride_bytes, (uint32_t)p.block_bytes, bar);
     }
   };
-  if (tid < 32) {
+  // Block-group mode (16-token blocks, Hkv * mb == 8, one virtual head per KV head): block j of every stage is
+  // read only by the Hkv warps that own its heads, so every block has its own barrier and release counter and is
+  // refilled as soon as ITS readers are done - a single-head shard runs 8 independent per-warp rings, two heads
+  // 4 rings of 2 warps, and nobody waits for the slowest warp of the CTA.  Called by one lane.
+  auto issue_block = [&](int it, int stage, int j) {
+    const int bi = (tile0 + it) * p.mb + j;
+    if (bi >= nblk) return;
+    int blk;
+    if (bt_in_smem) {
+      blk = s_bt[it * p.mb + j];
+    } else {
+      blk = bt[bi];
+      if ((unsigned)blk >= (unsigned)p.num_blocks) {
+        flag_status(p.status, TRIATTN_DEV_BAD_BLOCK_ID);
+        blk = 0;
+      }
+    }
+    const uint32_t bar = smem_u32(&blk_bar[stage][j]);
+    mbar_arrive_expect_tx(bar, (uint32_t)p.block_bytes);
+    bulk_copy_g2s(smem_u32(smem_tiles + (size_t)stage * stage_bytes + (size_t)j * p.block_bytes),
+                  kbase + (long long)blk * p.block_stride_bytes, (uint32_t)p.block_bytes, bar);
+  };
+  if (p.block_group > 0) {
+    // the first warp of each reader group starts its block's ring
+    const int w0 = tid >> 5;
+    if ((tid & 31) == 0 && (w0 % p.block_group) == 0) {
+      const int pre = min(p.stages, my_tiles);
+      for (int it = 0; it < pre; ++it) issue_block(it, it, w0 / p.block_group);
+    }
+  } else if (tid < 32) {
     const int pre = min(p.stages, my_tiles);
     for (int it = 0; it < pre; ++it) issue(it, it, tid);
   }
@@ -372,6 +407,38 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
   const int fixed_kvh = cur_vh >= 0 ? cur_vh / nsub : 0;
   int stage = 0;
   uint32_t parity = 0;
+  if (p.block_group > 0) {
+    const int G = p.block_group;           // warps (KV heads) per block
+    const int j = wid / G, kvh = wid - j * G;
+    unsigned target = (unsigned)G;
+    for (int it = 0; it < my_tiles; ++it) {
+      if ((tile0 + it) * p.mb + j >= nblk) break;  // this warp's block of the tile (and of all later tiles) does not exist
+      const bool ready = __all_sync(kFull, mbar_wait_bounded(smem_u32(&blk_bar[stage][j]), parity));
+      if (!ready) {
+        s_err = 1;
+        if (lane == 0) flag_status(p.status, TRIATTN_DEV_WAIT_TIMEOUT);
+        break;
+      }
+      const int stage_tok0 = (tile0 + it) * stage_tokens;
+      const int tok_end = min(seq_len - stage_tok0, stage_tokens);
+      compute_item(smem_base + (uint32_t)(stage * stage_bytes), j, kvh, stage_tok0, (j + 1) * kMmaKeys <= tok_end);
+      __syncwarp();
+      if (lane == 0) {
+        const unsigned done = G == 1 ? target : atomicAdd(&s_blk_released[stage][j], 1u) + 1u;
+        if (done == target && it + p.stages < my_tiles) {
+          fence_proxy_async();  // generic-proxy reads of the block before the async-proxy refill
+          issue_block(it + p.stages, stage, j);
+        }
+      }
+      if (++stage == p.stages) {
+        stage = 0;
+        parity ^= 1u;
+        target += (unsigned)G;
+      }
+    }
+    flush_moments();
+    return;
+  }
   unsigned release_target = (unsigned)kScoreConsumerWarps;
   for (int it = 0; it < my_tiles; ++it) {
     const bool ready = __all_sync(kFull, mbar_wait_bounded(smem_u32(&full_bar[stage]), parity));
