@@ -19,6 +19,7 @@
 #include "score.cuh"
 #include "score_fma.cuh"
 #include "score_mma.cuh"
+#include "score_mma_max.cuh"
 #include "select.cuh"
 
 using namespace triattn;
@@ -315,6 +316,28 @@ int triattn_score_paged(const triattn_paged_layout* layout, const void* const* k
                                 : launch_score_mma<128, false>(p, grid, smem, st);
     return Y.rope_interleaved ? launch_score_mma<64, true>(p, grid, smem, st)
                               : launch_score_mma<64, false>(p, grid, smem, st);
+  }
+  // max over offsets on the tensor cores: one CTA per (layer, request, virtual head, run of 16-key tiles)
+  if (p.agg_max && (Y.head_dim == 64 || Y.head_dim == 128) && (p.block_stride_bytes % 16) == 0 &&
+      max_agg_smem_bytes(Y.head_dim, num_offsets) <= 220 * 1024 && env_int("TRIATTN_SCORE_MAX_MMA", 1, 0, 1) == 1) {
+    const int nvh = Y.num_kv_heads * ((gp + 3) / 4);
+    const int n_tiles = (p.t_pad + kMmaKeys - 1) / kMmaKeys;
+    p.tiles_per_cta = std::min(n_tiles, 16 * kMaxAggWarps);
+    const int chunks = (n_tiles + p.tiles_per_cta - 1) / p.tiles_per_cta;
+    dim3 grid((unsigned)(nvh * chunks), (unsigned)Y.num_layers, (unsigned)Y.num_reqs);
+    const size_t smem = max_agg_smem_bytes(Y.head_dim, num_offsets);
+#define TRIATTN_LAUNCH(D, IL)                                                                      \
+  {                                                                                                \
+    if (!ensure_dynamic_smem<score_paged_mma_max_kernel<D, IL>>(smem)) return TRIATTN_ERR_CUDA;    \
+    score_paged_mma_max_kernel<D, IL><<<grid, kMaxAggThreads, smem, st>>>(p);                      \
+    return check_launch();                                                                         \
+  }
+    if (Y.head_dim == 128) {
+      if (Y.rope_interleaved) TRIATTN_LAUNCH(128, true) else TRIATTN_LAUNCH(128, false)
+    } else {
+      if (Y.rope_interleaved) TRIATTN_LAUNCH(64, true) else TRIATTN_LAUNCH(64, false)
+    }
+#undef TRIATTN_LAUNCH
   }
   dim3 grid((unsigned)((p.t_pad + 127) / 128), (unsigned)Y.num_kv_heads, (unsigned)(Y.num_layers * Y.num_reqs));
   if ((long long)Y.num_layers * Y.num_reqs > 65535) return TRIATTN_ERR_UNSUPPORTED_SHAPE;

@@ -1,0 +1,282 @@
+// Key scorer for offset aggregation = max on the warp-level tensor-core path.
+//
+// score(key, head) = max over the O offsets of sum_d k_d * W[o][head][d]  +  sum_f |k_f| * w_mag[head][f]
+// is O dot products of length D per (key, head): [16 keys x D] x [D x (O x 4 heads x 2 parts)] on m16n8k16 bf16
+// MMAs, one column tile per offset (column n = 2*head + part, bf16 high part and bf16 of the remainder of the
+// fp32 weight, as in score_mma.cuh), so a thread sees the finished dot product of query head lane%4 for its two
+// keys after every offset and keeps a running maximum in registers.  The magnitude term is the one of
+// score_mma.cuh (|k| in fp32 on the CUDA cores, split into two bf16 parts).
+//
+// The work is bound by the tensor pipe (8*O + 8 MMAs per 16 keys), not by HBM, so the data movement is chosen for
+// simplicity: a CTA works on ONE (layer, request, virtual head); its weight fragments for all offsets live in
+// shared memory in fragment order (conflict-free 16-byte loads), and every warp streams its own 16-key tiles of
+// that head through a private ring of three 16-row slots, fetched row by row with 1-D bulk async copies on the
+// warp's own mbarriers (bounded waits).  No warp ever waits for another.
+#pragma once
+
+#include "score_mma.cuh"
+
+namespace triattn {
+
+constexpr int kMaxAggWarps = 12;
+constexpr int kMaxAggThreads = kMaxAggWarps * 32;
+constexpr int kMaxAggSlots = 3;
+constexpr int kMaxAggOffsets = 32;  // offsets the shared-memory weight table is sized for
+
+// dynamic shared memory: weight fragments [O][KS/2][32 lanes][4 words] + rings [warps][slots][16 rows][D*2 bytes]
+inline size_t max_agg_smem_bytes(int D, int num_offsets) {
+  return (size_t)num_offsets * (D / 32) * 32 * 16 + (size_t)kMaxAggWarps * kMaxAggSlots * kMmaKeys * D * 2;
+}
+
+template <int D, bool INTERLEAVED>
+__global__ void __launch_bounds__(kMaxAggThreads, 1) score_paged_mma_max_kernel(const __grid_constant__ ScoreParams p) {
+  constexpr int F = D / 2;
+  constexpr int NQ = D / 32;   // 16-byte chunks per key and thread
+  constexpr int KS = D / 16;   // k-steps (MMAs) per offset
+  constexpr int GP = 4;
+  constexpr int ROW_BYTES = D * 2;
+  constexpr int SLOT_BYTES = kMmaKeys * ROW_BYTES;
+
+  extern __shared__ __align__(128) unsigned char smem_dyn[];
+  __shared__ __align__(8) uint64_t bars[kMaxAggWarps][kMaxAggSlots];
+
+  const int O = p.num_offsets;
+  uint4* s_w = reinterpret_cast<uint4*>(smem_dyn);  // [O][KS/2][32]
+  unsigned char* s_ring = smem_dyn + (size_t)O * (KS / 2) * 32 * 16;
+
+  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  const int l = blockIdx.y, b = blockIdx.z;
+  const int nsub = (p.gp_total + GP - 1) / GP;
+  const int nvh = p.Hkv * nsub;
+  const int vh = blockIdx.x % nvh, chunk = blockIdx.x / nvh;
+  const int kvh = vh / nsub, sub = vh - kvh * nsub;
+  int seq_len = p.seq_lens[b];
+  if (seq_len > p.t_pad) {
+    if (tid == 0 && blockIdx.x == 0) flag_status(p.status, TRIATTN_DEV_BAD_LENGTH);
+    seq_len = p.t_pad;
+  }
+  const int n_tiles = (seq_len + kMmaKeys - 1) / kMmaKeys;  // 16-key tiles of the request
+  const int tile0 = chunk * p.tiles_per_cta;
+  if (tile0 >= n_tiles) return;
+  const int my_tiles = min(p.tiles_per_cta, n_tiles - tile0);
+  const int Hq = p.Hkv * p.g;
+  const int rows_w = 2 * O + 1;  // weight rows per query head: re[o]..., im[o]..., magnitude
+  const int qbase = kvh * p.g + sub * GP;
+  const int nq = min(GP, p.g - sub * GP);
+  const int rg = lane >> 2, rt = lane & 3;
+
+  if (tid < kMaxAggWarps * kMaxAggSlots) mbar_init(smem_u32(&bars[tid / kMaxAggSlots][tid % kMaxAggSlots]), 1);
+  if (tid == 0) mbar_fence_init();
+
+  // weight fragments of all offsets -> shared memory, fragment order: entry (o, ks, lane') = (b0, b1) of k-step ks
+  for (int e = tid; e < O * KS * 32; e += kMaxAggThreads) {
+    const int ln = e & 31, ks = (e >> 5) % KS, o = e / (32 * KS);
+    const int crg = ln >> 2, crt = ln & 3;
+    const int head = crg >> 1, part = crg & 1;
+    const bool on = head < nq;
+    const float* w = p.weights + (((size_t)l * p.B + b) * Hq + (size_t)qbase + (on ? head : 0)) * rows_w * F;
+    const int d0 = 8 * (crt + 4 * (ks >> 1)) + 4 * (ks & 1);
+    uint32_t v[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int d = d0 + i;
+      const int comp = INTERLEAVED ? (d & 1) : (d >= F ? 1 : 0);
+      const int f = INTERLEAVED ? (d >> 1) : (d >= F ? d - F : d);
+      const float x = on ? __ldg(w + (size_t)(comp * O + o) * F + f) : 0.f;
+      uint32_t hi, lo;
+      bf16_split(x, hi, lo);
+      v[i] = part ? lo : hi;
+    }
+    uint32_t* dst = reinterpret_cast<uint32_t*>(s_w + ((size_t)o * (KS / 2) + (ks >> 1)) * 32 + ln) + 2 * (ks & 1);
+    dst[0] = v[0] | (v[1] << 16);
+    dst[1] = v[2] | (v[3] << 16);
+  }
+  // magnitude fragments stay in registers
+  uint32_t bmg[NQ][2];
+  {
+    const int head = rg >> 1, part = rg & 1;
+    const bool on = head < nq;
+    const float* wm = p.weights + ((((size_t)l * p.B + b) * Hq + (size_t)qbase + (on ? head : 0)) * rows_w + 2 * O) * F;
+#pragma unroll
+    for (int j = 0; j < NQ; ++j) {
+      const int f0 = INTERLEAVED ? 4 * (rt + 4 * j) : 8 * (rt + 4 * (j >> 1)) + 4 * (j & 1);
+      uint32_t v[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint32_t hi, lo;
+        bf16_split(on ? __ldg(wm + f0 + i) : 0.f, hi, lo);
+        v[i] = part ? lo : hi;
+      }
+      bmg[j][0] = v[0] | (v[1] << 16);
+      bmg[j][1] = v[2] | (v[3] << 16);
+    }
+  }
+  __syncthreads();
+
+  const unsigned char* kbase = reinterpret_cast<const unsigned char*>(p.k_ptrs[l]);
+  const int32_t* bt = p.block_table + (size_t)b * p.max_blocks;
+  unsigned char* my_ring = s_ring + (size_t)wid * kMaxAggSlots * SLOT_BYTES;
+  constexpr unsigned kFull = 0xffffffffu;
+
+  // fetch the 16 rows of this warp's tile `i` (tile index within the CTA's range): lane r copies row r
+  auto fetch = [&](int i, int slot) {
+    const int tok0 = (tile0 + i) * kMmaKeys;
+    const int rows = min(kMmaKeys, seq_len - tok0);
+    const uint32_t bar = smem_u32(&bars[wid][slot]);
+    if (lane == 0) mbar_arrive_expect_tx(bar, (uint32_t)(rows * ROW_BYTES));
+    __syncwarp();
+    if (lane < rows) {
+      const int t = tok0 + lane;
+      const int bi = t / p.bs;
+      int blk = bt[bi];
+      if ((unsigned)blk >= (unsigned)p.num_blocks) {
+        flag_status(p.status, TRIATTN_DEV_BAD_BLOCK_ID);
+        blk = 0;
+      }
+      const unsigned char* src = kbase + (long long)blk * p.block_stride_bytes +
+                                 ((long long)(t - bi * p.bs) * p.token_stride + (long long)kvh * p.head_stride) * 2;
+      bulk_copy_g2s(smem_u32(my_ring + (size_t)slot * SLOT_BYTES + (size_t)lane * ROW_BYTES), src, ROW_BYTES, bar);
+    }
+  };
+
+  // this warp's tiles: wid, wid + W, ... of the CTA's range
+  const int n_mine = my_tiles > wid ? (my_tiles - wid + kMaxAggWarps - 1) / kMaxAggWarps : 0;
+  for (int i = 0; i < min(kMaxAggSlots, n_mine); ++i) fetch(wid + i * kMaxAggWarps, i);
+
+  float s1 = 0.f, s2 = 0.f;
+  float* raw_head = p.raw + (((size_t)l * p.B + b) * p.Hkv + kvh) * (size_t)p.t_pad * p.gp_total + sub * GP + rt;
+  int slot = 0;
+  uint32_t parity = 0;
+  for (int i = 0; i < n_mine; ++i) {
+    const bool ready = __all_sync(kFull, mbar_wait_bounded(smem_u32(&bars[wid][slot]), parity));
+    if (!ready) {
+      if (lane == 0) flag_status(p.status, TRIATTN_DEV_WAIT_TIMEOUT);
+      break;
+    }
+    const int tok0 = (tile0 + wid + i * kMaxAggWarps) * kMmaKeys;
+    const uint32_t base = smem_u32(my_ring + (size_t)slot * SLOT_BYTES);
+    const uint32_t rowA = base + (uint32_t)(rg * ROW_BYTES) + 16u * rt, rowB = rowA + 8u * ROW_BYTES;
+
+    // A fragments of the whole tile (kept for all offsets) and the magnitude term
+    uint32_t a[KS][4];
+    float accm[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    auto split_pair = [&](float m0, float m1, uint32_t& hi, uint32_t& lo) {
+      const uint32_t u0 = __float_as_uint(m0), u1 = __float_as_uint(m1);
+      hi = __byte_perm(u0, u1, 0x7632);
+      lo = pack_bf16x2_rn(m0 - __uint_as_float(u0 & 0xffff0000u), m1 - __uint_as_float(u1 & 0xffff0000u));
+    };
+#pragma unroll
+    for (int c = 0; c < NQ; ++c) {
+      const uint4 xA = lds128(rowA + 64u * c), xB = lds128(rowB + 64u * c);
+      a[2 * c][0] = xA.x; a[2 * c][1] = xB.x; a[2 * c][2] = xA.y; a[2 * c][3] = xB.y;
+      a[2 * c + 1][0] = xA.z; a[2 * c + 1][1] = xB.z; a[2 * c + 1][2] = xA.w; a[2 * c + 1][3] = xB.w;
+    }
+    if constexpr (!INTERLEAVED) {
+#pragma unroll
+      for (int q = 0; q < NQ / 2; ++q) {
+        // chunk q holds re of 8 frequencies, chunk q + NQ/2 their im
+        uint32_t hA[4], lA[4], hB[4], lB[4];
+#pragma unroll
+        for (int i2 = 0; i2 < 4; ++i2) {
+          const int ks = 2 * q + (i2 >> 1), kr = 2 * (i2 & 1);  // word i2 of the chunk: a[ks][kr] (row A), a[ks][kr+1] (row B)
+          const int ksi = ks + NQ;                               // same word of the im chunk
+          const float2 ra = bf16x2_to_float2(a[ks][kr]), ia = bf16x2_to_float2(a[ksi][kr]);
+          const float2 rb = bf16x2_to_float2(a[ks][kr + 1]), ib = bf16x2_to_float2(a[ksi][kr + 1]);
+          const float2 ma = ffma2(ia, ia, fmul2(ra, ra));
+          const float2 mb = ffma2(ib, ib, fmul2(rb, rb));
+          split_pair(sqrt_approx(ma.x), sqrt_approx(ma.y), hA[i2], lA[i2]);
+          split_pair(sqrt_approx(mb.x), sqrt_approx(mb.y), hB[i2], lB[i2]);
+        }
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          const int j = 2 * q + hh;
+          mma_bf16_16816(accm[0], hA[2 * hh], hB[2 * hh], hA[2 * hh + 1], hB[2 * hh + 1], bmg[j][0], bmg[j][1]);
+          mma_bf16_16816(accm[1], lA[2 * hh], lB[2 * hh], lA[2 * hh + 1], lB[2 * hh + 1], bmg[j][0], bmg[j][1]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int c = 0; c < NQ; ++c) {
+        float mA[4], mB[4];
+#pragma unroll
+        for (int i2 = 0; i2 < 4; ++i2) {
+          const int ks = 2 * c + (i2 >> 1), kr = 2 * (i2 & 1);
+          const float2 va = bf16x2_to_float2(a[ks][kr]), vb = bf16x2_to_float2(a[ks][kr + 1]);
+          const float2 pa = fmul2(va, va), pb = fmul2(vb, vb);
+          mA[i2] = sqrt_approx(pa.x + pa.y);
+          mB[i2] = sqrt_approx(pb.x + pb.y);
+        }
+        uint32_t hA[2], lA[2], hB[2], lB[2];
+        split_pair(mA[0], mA[1], hA[0], lA[0]);
+        split_pair(mA[2], mA[3], hA[1], lA[1]);
+        split_pair(mB[0], mB[1], hB[0], lB[0]);
+        split_pair(mB[2], mB[3], hB[1], lB[1]);
+        mma_bf16_16816(accm[0], hA[0], hB[0], hA[1], hB[1], bmg[c][0], bmg[c][1]);
+        mma_bf16_16816(accm[1], lA[0], lB[0], lA[1], lB[1], bmg[c][0], bmg[c][1]);
+      }
+    }
+    // all shared-memory reads of the slot are done: refill it with the tile kMaxAggSlots ahead
+    __syncwarp();
+    if (i + kMaxAggSlots < n_mine) {
+      if (lane == 0) fence_proxy_async();
+      __syncwarp();
+      fetch(wid + (i + kMaxAggSlots) * kMaxAggWarps, slot);
+    }
+
+    // offsets: one column tile each, two accumulator chains in flight
+    float bestA = -INFINITY, bestB = -INFINITY;
+    for (int o = 0; o < O; o += 2) {
+      float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+      const bool two = o + 1 < O;
+      const uint4* w0 = s_w + (size_t)o * (KS / 2) * 32 + lane;
+      const uint4* w1 = s_w + (size_t)(two ? o + 1 : o) * (KS / 2) * 32 + lane;
+#pragma unroll
+      for (int r = 0; r < KS / 2; ++r) {
+        const uint4 u = w0[r * 32], v = w1[r * 32];
+        mma_bf16_16816(c0, a[2 * r][0], a[2 * r][1], a[2 * r][2], a[2 * r][3], u.x, u.y);
+        mma_bf16_16816(c1, a[2 * r][0], a[2 * r][1], a[2 * r][2], a[2 * r][3], v.x, v.y);
+        mma_bf16_16816(c0, a[2 * r + 1][0], a[2 * r + 1][1], a[2 * r + 1][2], a[2 * r + 1][3], u.z, u.w);
+        mma_bf16_16816(c1, a[2 * r + 1][0], a[2 * r + 1][1], a[2 * r + 1][2], a[2 * r + 1][3], v.z, v.w);
+      }
+      bestA = fmaxf(bestA, c0[0] + c0[1]);
+      bestB = fmaxf(bestB, c0[2] + c0[3]);
+      if (two) {
+        bestA = fmaxf(bestA, c1[0] + c1[1]);
+        bestB = fmaxf(bestB, c1[2] + c1[3]);
+      }
+    }
+    const float scA = bestA + ((accm[0][0] + accm[1][0]) + (accm[0][1] + accm[1][1]));
+    const float scB = bestB + ((accm[0][2] + accm[1][2]) + (accm[0][3] + accm[1][3]));
+    if (rt < nq) {
+      const int gA = tok0 + rg;
+      float* out = raw_head + (size_t)gA * p.gp_total;
+      if (gA < seq_len) {
+        out[0] = scA;
+        s1 += scA;
+        s2 = fmaf(scA, scA, s2);
+      }
+      if (gA + 8 < seq_len) {
+        out[(size_t)8 * p.gp_total] = scB;
+        s1 += scB;
+        s2 = fmaf(scB, scB, s2);
+      }
+    }
+    if (++slot == kMaxAggSlots) {
+      slot = 0;
+      parity ^= 1u;
+    }
+  }
+  // moments of query slot rt over this warp's keys
+#pragma unroll
+  for (int s = 4; s < 32; s <<= 1) {
+    s1 += __shfl_xor_sync(kFull, s1, s);
+    s2 += __shfl_xor_sync(kFull, s2, s);
+  }
+  if (lane < 4 && lane < nq && n_mine > 0) {
+    double* m = p.moments + (((size_t)l * p.B + b) * Hq + (size_t)qbase + lane) * 2;
+    atomicAdd(m, (double)s1);
+    atomicAdd(m + 1, (double)s2);
+  }
+}
+
+}  // namespace triattn
