@@ -219,21 +219,7 @@ def test_token_pool_layout_block_size_one():
     assert res.kept_block_ids[0] == slots[:budget] and res.removed_block_ids[0] == slots[budget:]
 
 
-@pytest.mark.parametrize("score_path", ["mma", "fma"])
-@pytest.mark.parametrize("hkv,g,D,bs,hnd,rope_style", [
-    (8, 4, 128, 16, False, "half"),        # the benchmark geometry
-    (8, 4, 128, 16, True, "half"),         # head-major blocks
-    (2, 3, 128, 16, False, "half"),        # odd group size, padded to 4 slots
-    (4, 1, 64, 16, False, "half"),         # no grouping, head_dim 64
-    (2, 2, 64, 32, True, "interleaved"),   # interleaved RoPE pairs, 32-token head-major blocks
-    (1, 6, 128, 16, False, "interleaved"), # 6 query heads per KV head: two column tiles
-    (2, 8, 128, 8, False, "half"),         # blocks smaller than a 16-key tile
-    (1, 12, 128, 16, False, "half"),       # more than 8 query heads: virtual heads
-    (3, 4, 128, 16, False, "half"),        # KV-head count that does not divide the warp count
-])
-def test_scorer_shape_sweep(hkv, g, D, bs, hnd, rope_style, score_path, monkeypatch):
-    """Raw scores of both streaming scorers against the checker over head/group/block geometries, ragged lengths."""
-    monkeypatch.setenv("TRIATTN_SCORE_PATH", score_path)
+def _check_scorer_against_checker(hkv, g, D, bs, hnd, rope_style, aggregation="mean"):
     gen = torch.Generator().manual_seed(synth.seed_for(7, hkv * 100 + g * 10 + (1 if hnd else 0)))
     L, lens = 2, [333, 150, 16]
     Hq = hkv * g
@@ -272,15 +258,17 @@ def test_scorer_shape_sweep(hkv, g, D, bs, hnd, rope_style, score_path, monkeypa
     seq = torch.tensor(lens, dtype=torch.int32, device=DEV)
     rs = torch.tensor([t + 5 for t in lens], dtype=torch.int32, device=DEV)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    w = ops.prep_weights(dstats, rs)
-    raw, mom = ops.score_paged(view, layout, bt, seq, w, status=status)
+    from triattention_b200 import _native
+    agg = _native.OFFSETS_MAX if aggregation == "max" else _native.OFFSETS_MEAN
+    w = ops.prep_weights(dstats, rs, agg)
+    raw, mom = ops.score_paged(view, layout, bt, seq, w, agg, 17, status=status)
     torch.cuda.synchronize()
     assert int(status.item()) == 0
     for b, t in enumerate(lens):
         layers = [(l, c, ids[b], bs) for l, c in enumerate(caches)]
         _, ref_raws = oracle.final_scores_group_per_head(layers, _stats_dict(stats), inv, oracle.geometric_offsets(), t,
                                                          t + 5, window_size=0, return_raw=True, kv_axis=0,
-                                                         rope_style=rope_style)
+                                                         rope_style=rope_style, aggregation=aggregation)
         got = raw[:, b, :, :t, :g].permute(0, 1, 3, 2).reshape(L, Hq, t).cpu()
         ref = torch.stack(ref_raws)
         sigma = ref.std(dim=-1, keepdim=True)
@@ -289,3 +277,32 @@ def test_scorer_shape_sweep(hkv, g, D, bs, hnd, rope_style, score_path, monkeypa
         m = mom[:, b].cpu()
         assert torch.allclose(m[..., 0], got.double().sum(-1), rtol=1e-6, atol=1e-4)
         assert torch.allclose(m[..., 1], (got.double() ** 2).sum(-1), rtol=1e-6, atol=1e-4)
+
+
+@pytest.mark.parametrize("score_path", ["mma", "fma"])
+@pytest.mark.parametrize("hkv,g,D,bs,hnd,rope_style", [
+    (8, 4, 128, 16, False, "half"),        # the benchmark geometry
+    (8, 4, 128, 16, True, "half"),         # head-major blocks
+    (2, 3, 128, 16, False, "half"),        # odd group size, padded to 4 slots
+    (4, 1, 64, 16, False, "half"),         # no grouping, head_dim 64
+    (2, 2, 64, 32, True, "interleaved"),   # interleaved RoPE pairs, 32-token head-major blocks
+    (1, 6, 128, 16, False, "interleaved"), # 6 query heads per KV head: two column tiles
+    (2, 8, 128, 8, False, "half"),         # blocks smaller than a 16-key tile
+    (1, 12, 128, 16, False, "half"),       # more than 8 query heads: virtual heads
+    (3, 4, 128, 16, False, "half"),        # KV-head count that does not divide the warp count
+])
+def test_scorer_shape_sweep(hkv, g, D, bs, hnd, rope_style, score_path, monkeypatch):
+    """Raw scores of both streaming scorers against the checker over head/group/block geometries, ragged lengths."""
+    monkeypatch.setenv("TRIATTN_SCORE_PATH", score_path)
+    _check_scorer_against_checker(hkv, g, D, bs, hnd, rope_style)
+
+
+@pytest.mark.parametrize("hkv,g,D,bs,hnd,rope_style", [
+    (8, 4, 128, 16, False, "half"),
+    (2, 4, 128, 16, True, "half"),
+    (2, 3, 64, 32, True, "interleaved"),
+    (1, 6, 128, 8, False, "interleaved"),
+])
+def test_max_aggregation_scorer_shape_sweep(hkv, g, D, bs, hnd, rope_style):
+    """The tensor-core scorer for max aggregation against the checker (one column tile per offset, running max)."""
+    _check_scorer_against_checker(hkv, g, D, bs, hnd, rope_style, aggregation="max")

@@ -21,7 +21,7 @@ namespace triattn {
 constexpr int kMaxAggWarps = 12;
 constexpr int kMaxAggThreads = kMaxAggWarps * 32;
 constexpr int kMaxAggSlots = 3;
-constexpr int kMaxAggOffsets = 32;  // offsets the shared-memory weight table is sized for
+constexpr int kMaxAggChains = 2;  // offsets (accumulator chains) a warp keeps in flight
 
 // dynamic shared memory: weight fragments [O][KS/2][32 lanes][4 words] + rings [warps][slots][16 rows][D*2 bytes]
 inline size_t max_agg_smem_bytes(int D, int num_offsets) {
@@ -223,26 +223,34 @@ __global__ void __launch_bounds__(kMaxAggThreads, 1) score_paged_mma_max_kernel(
       fetch(wid + (i + kMaxAggSlots) * kMaxAggWarps, slot);
     }
 
-    // offsets: one column tile each, two accumulator chains in flight
+    // offsets: one column tile each, kMaxAggChains independent accumulator chains in flight
     float bestA = -INFINITY, bestB = -INFINITY;
-    for (int o = 0; o < O; o += 2) {
-      float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
-      const bool two = o + 1 < O;
-      const uint4* w0 = s_w + (size_t)o * (KS / 2) * 32 + lane;
-      const uint4* w1 = s_w + (size_t)(two ? o + 1 : o) * (KS / 2) * 32 + lane;
+    for (int o = 0; o < O; o += kMaxAggChains) {
+      float c[kMaxAggChains][4];
+      const uint4* w[kMaxAggChains];
+#pragma unroll
+      for (int n = 0; n < kMaxAggChains; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) c[n][e] = 0.f;
+        w[n] = s_w + (size_t)min(o + n, O - 1) * (KS / 2) * 32 + lane;  // past the last offset: recompute it, ignored below
+      }
 #pragma unroll
       for (int r = 0; r < KS / 2; ++r) {
-        const uint4 u = w0[r * 32], v = w1[r * 32];
-        mma_bf16_16816(c0, a[2 * r][0], a[2 * r][1], a[2 * r][2], a[2 * r][3], u.x, u.y);
-        mma_bf16_16816(c1, a[2 * r][0], a[2 * r][1], a[2 * r][2], a[2 * r][3], v.x, v.y);
-        mma_bf16_16816(c0, a[2 * r + 1][0], a[2 * r + 1][1], a[2 * r + 1][2], a[2 * r + 1][3], u.z, u.w);
-        mma_bf16_16816(c1, a[2 * r + 1][0], a[2 * r + 1][1], a[2 * r + 1][2], a[2 * r + 1][3], v.z, v.w);
+        uint4 u[kMaxAggChains];
+#pragma unroll
+        for (int n = 0; n < kMaxAggChains; ++n) u[n] = w[n][r * 32];
+#pragma unroll
+        for (int n = 0; n < kMaxAggChains; ++n)
+          mma_bf16_16816(c[n], a[2 * r][0], a[2 * r][1], a[2 * r][2], a[2 * r][3], u[n].x, u[n].y);
+#pragma unroll
+        for (int n = 0; n < kMaxAggChains; ++n)
+          mma_bf16_16816(c[n], a[2 * r + 1][0], a[2 * r + 1][1], a[2 * r + 1][2], a[2 * r + 1][3], u[n].z, u[n].w);
       }
-      bestA = fmaxf(bestA, c0[0] + c0[1]);
-      bestB = fmaxf(bestB, c0[2] + c0[3]);
-      if (two) {
-        bestA = fmaxf(bestA, c1[0] + c1[1]);
-        bestB = fmaxf(bestB, c1[2] + c1[3]);
+#pragma unroll
+      for (int n = 0; n < kMaxAggChains; ++n) {
+        // a duplicate of the last offset (o + n >= O) leaves the maximum unchanged
+        bestA = fmaxf(bestA, c[n][0] + c[n][1]);
+        bestB = fmaxf(bestB, c[n][2] + c[n][3]);
       }
     }
     const float scA = bestA + ((accm[0][0] + accm[1][0]) + (accm[0][1] + accm[1][1]));
