@@ -50,6 +50,8 @@ def parse_args():
     ap.add_argument("--tokens", type=int, default=0, help="override the cached length")
     ap.add_argument("--budget", type=int, default=0, help="override the KV budget")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--aggregation", choices=("mean", "max"), default="mean",
+                    help="aggregation over the future-offset set (the reference's default is mean)")
     ap.add_argument("--shard-of", type=int, default=0,
                     help="on ONE GPU, run the shard one rank owns under tensor parallelism of this degree "
                          "(the path has no collective, so this is that rank's whole job)")
@@ -311,7 +313,8 @@ def run_reference(args, world, rank):
 
 def workload_name(args, c):
     return (f"{args.config}: {c['L']} layers, {c['Hq']}q/{c['Hkv']}kv heads, head_dim {c['D']}, "
-            f"{c['B']} requests x {c['T']} tokens, paged bf16 block {BLOCK_SIZE}, budget {c['budget']}, window {c['window']}")
+            f"{c['B']} requests x {c['T']} tokens, paged bf16 block {BLOCK_SIZE}, budget {c['budget']}, window {c['window']}"
+            + (", max over offsets" if getattr(args, "aggregation", "mean") == "max" else ""))
 
 
 # ----------------------------------------------------------------------------- our arm
@@ -330,7 +333,9 @@ def run_ours(args, world, rank, local):
     view = ops.PagedCacheView.from_layers(caches, kv_axis=0)
     B, T, k, L, H = c["B_local"], c["T"], c["k"], c["L"], c["Hkv_local"]
     saver = PrefixSaver(caches, block_ids, k)
-    comp = engine.PagedCompressor(stats, window=c["window"], use_cuda_graph=os.environ.get("TRIATTN_BENCH_CUDA_GRAPH") == "1")
+    comp = engine.PagedCompressor(stats, window=c["window"],
+                                  offset_agg=(_native.OFFSETS_MAX if args.aggregation == "max" else _native.OFFSETS_MEAN),
+                                  use_cuda_graph=os.environ.get("TRIATTN_BENCH_CUDA_GRAPH") == "1")
     seq_lens, round_starts, budgets = [T] * B, [T] * B, [k] * B
     keys_per_gpu = L * B * H * T
 
@@ -342,12 +347,13 @@ def run_ours(args, world, rank, local):
     d_kc = torch.tensor(budgets, dtype=torch.int32, device=device)
     d_status = torch.zeros(1, dtype=torch.int32, device=device)
     layout = view.layout(B, c["g"], nblk)
-    ws = torch.empty(ops.compress_workspace_bytes(layout, 17, 0, k), dtype=torch.uint8, device=device)
+    agg = _native.OFFSETS_MAX if args.aggregation == "max" else _native.OFFSETS_MEAN
+    ws = torch.empty(ops.compress_workspace_bytes(layout, 17, agg, k), dtype=torch.uint8, device=device)
     keep_out = torch.empty((B, H, k), dtype=torch.int32, device=device)
 
     def device_step():
-        ops.compress_paged(view, layout, stats, bt, d_seq, d_rs, None, d_kc, k, c["window"], workspace=ws,
-                           keep_out=keep_out, status=d_status)
+        ops.compress_paged(view, layout, stats, bt, d_seq, d_rs, None, d_kc, k, c["window"], offset_agg=agg,
+                           workspace=ws, keep_out=keep_out, status=d_status)
 
     def timed(fn, steps):
         """Per-step CUDA-event time on the launching stream; the cache prefix is restored (untimed) between steps."""
@@ -408,9 +414,9 @@ def run_ours(args, world, rank, local):
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
         torch.cuda.synchronize()
         ev[0].record()
-        w = ops.prep_weights(stats, d_rs)
+        w = ops.prep_weights(stats, d_rs, agg)
         ev[1].record()
-        raw, mom = ops.score_paged(view, layout, bt, d_seq, w, status=d_status)
+        raw, mom = ops.score_paged(view, layout, bt, d_seq, w, agg, 17, status=d_status)
         ev[2].record()
         fin = ops.finalize_scores(layout, raw, mom, d_seq, None, c["window"])
         ev[3].record()
@@ -442,7 +448,8 @@ def run_ours(args, world, rank, local):
         "keys_per_s_per_gpu": value / world,
         "step_hbm_gbs": bytes_step / (step_ms * 1e-3) / 1e9, "step_hbm_frac": bytes_step / (step_ms * 1e-3) / 1e9 / peak,
         "stage_ms": stage,
-        "roofline": {"kernel": ("score_paged_mean_kernel" if os.environ.get("TRIATTN_SCORE_PATH") == "fma"
+        "roofline": {"kernel": ("score_paged_mma_max_kernel" if args.aggregation == "max" else
+                                "score_paged_mean_kernel" if os.environ.get("TRIATTN_SCORE_PATH") == "fma"
                                 else "score_paged_mma_kernel"), "bound": "hbm", "achieved": achieved, "peak": peak,
                      "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
                      "traffic": (keys_per_gpu * SCORE_DRAM_BYTES_PER_KEY_NCU
