@@ -290,6 +290,8 @@ def _check_scorer_against_checker(hkv, g, D, bs, hnd, rope_style, aggregation="m
     (2, 8, 128, 8, False, "half"),         # blocks smaller than a 16-key tile
     (1, 12, 128, 16, False, "half"),       # more than 8 query heads: virtual heads
     (3, 4, 128, 16, False, "half"),        # KV-head count that does not divide the warp count
+    (4, 2, 128, 16, False, "half"),        # 4 local KV heads: two cache blocks per stage, reader groups of 4 warps
+    (1, 4, 128, 16, True, "half"),         # single-head shard: eight per-warp rings
 ])
 def test_scorer_shape_sweep(hkv, g, D, bs, hnd, rope_style, score_path, monkeypatch):
     """Raw scores of both streaming scorers against the checker over head/group/block geometries, ragged lengths."""
