@@ -10,8 +10,9 @@
 // The work is bound by the tensor pipe (8*O + 8 MMAs per 16 keys), not by HBM, so the data movement is chosen for
 // simplicity: a CTA works on ONE (layer, request, virtual head); its weight fragments for all offsets live in
 // shared memory in fragment order (conflict-free 16-byte loads), and every warp streams its own 16-key tiles of
-// that head through a private ring of three 16-row slots, fetched row by row with 1-D bulk async copies on the
-// warp's own mbarriers (bounded waits).  No warp ever waits for another.
+// that head, two at a time (one load of an offset's weight fragments feeds both), through private 16-row slots
+// fetched row by row with 1-D bulk async copies on the warp's own mbarriers (bounded waits): the tiles move to
+// registers, the slots are refilled at once and the copies land during the 17 offsets.  No warp waits for another.
 #pragma once
 
 #include "score_mma.cuh"
@@ -20,8 +21,8 @@ namespace triattn {
 
 constexpr int kMaxAggWarps = 12;
 constexpr int kMaxAggThreads = kMaxAggWarps * 32;
-constexpr int kMaxAggSlots = 3;
-constexpr int kMaxAggChains = 2;  // offsets (accumulator chains) a warp keeps in flight
+constexpr int kMaxAggTiles = 2;   // 16-key tiles a warp works on at once (independent accumulator chains)
+constexpr int kMaxAggSlots = kMaxAggTiles;  // ring slots per warp: the tiles move to registers, then the slots refill
 
 // dynamic shared memory: weight fragments [O][KS/2][32 lanes][4 words] + rings [warps][slots][16 rows][D*2 bytes]
 inline size_t max_agg_smem_bytes(int D, int num_offsets) {
@@ -139,32 +140,20 @@ __global__ void __launch_bounds__(kMaxAggThreads, 1) score_paged_mma_max_kernel(
     }
   };
 
-  // this warp's tiles: wid, wid + W, ... of the CTA's range
+  // this warp's tiles: wid, wid + W, ... of the CTA's range, taken kMaxAggTiles at a time: the weight fragments
+  // of an offset are loaded from shared memory once and used for all of them
   const int n_mine = my_tiles > wid ? (my_tiles - wid + kMaxAggWarps - 1) / kMaxAggWarps : 0;
-  for (int i = 0; i < min(kMaxAggSlots, n_mine); ++i) fetch(wid + i * kMaxAggWarps, i);
+  for (int i = 0; i < min(kMaxAggTiles, n_mine); ++i) fetch(wid + i * kMaxAggWarps, i);
 
-  float s1 = 0.f, s2 = 0.f;
-  float* raw_head = p.raw + (((size_t)l * p.B + b) * p.Hkv + kvh) * (size_t)p.t_pad * p.gp_total + sub * GP + rt;
-  int slot = 0;
-  uint32_t parity = 0;
-  for (int i = 0; i < n_mine; ++i) {
-    const bool ready = __all_sync(kFull, mbar_wait_bounded(smem_u32(&bars[wid][slot]), parity));
-    if (!ready) {
-      if (lane == 0) flag_status(p.status, TRIATTN_DEV_WAIT_TIMEOUT);
-      break;
-    }
-    const int tok0 = (tile0 + wid + i * kMaxAggWarps) * kMmaKeys;
-    const uint32_t base = smem_u32(my_ring + (size_t)slot * SLOT_BYTES);
+  auto split_pair = [&](float m0, float m1, uint32_t& hi, uint32_t& lo) {
+    const uint32_t u0 = __float_as_uint(m0), u1 = __float_as_uint(m1);
+    hi = __byte_perm(u0, u1, 0x7632);
+    lo = pack_bf16x2_rn(m0 - __uint_as_float(u0 & 0xffff0000u), m1 - __uint_as_float(u1 & 0xffff0000u));
+  };
+  // A fragments of one tile (kept for all offsets) and its magnitude term for this thread's two keys
+  auto load_tile = [&](uint32_t base, uint32_t (&a)[KS][4], float& magA, float& magB) {
     const uint32_t rowA = base + (uint32_t)(rg * ROW_BYTES) + 16u * rt, rowB = rowA + 8u * ROW_BYTES;
-
-    // A fragments of the whole tile (kept for all offsets) and the magnitude term
-    uint32_t a[KS][4];
     float accm[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-    auto split_pair = [&](float m0, float m1, uint32_t& hi, uint32_t& lo) {
-      const uint32_t u0 = __float_as_uint(m0), u1 = __float_as_uint(m1);
-      hi = __byte_perm(u0, u1, 0x7632);
-      lo = pack_bf16x2_rn(m0 - __uint_as_float(u0 & 0xffff0000u), m1 - __uint_as_float(u1 & 0xffff0000u));
-    };
 #pragma unroll
     for (int c = 0; c < NQ; ++c) {
       const uint4 xA = lds128(rowA + 64u * c), xB = lds128(rowB + 64u * c);
@@ -215,63 +204,95 @@ __global__ void __launch_bounds__(kMaxAggThreads, 1) score_paged_mma_max_kernel(
         mma_bf16_16816(accm[1], lA[0], lB[0], lA[1], lB[1], bmg[c][0], bmg[c][1]);
       }
     }
-    // all shared-memory reads of the slot are done: refill it with the tile kMaxAggSlots ahead
+    magA = (accm[0][0] + accm[1][0]) + (accm[0][1] + accm[1][1]);
+    magB = (accm[0][2] + accm[1][2]) + (accm[0][3] + accm[1][3]);
+  };
+
+  float s1 = 0.f, s2 = 0.f;
+  float* raw_head = p.raw + (((size_t)l * p.B + b) * p.Hkv + kvh) * (size_t)p.t_pad * p.gp_total + sub * GP + rt;
+  uint32_t parity = 0;
+  bool failed = false;
+  for (int i = 0; i < n_mine && !failed; i += kMaxAggTiles) {
+    uint32_t a[kMaxAggTiles][KS][4];
+    float mag[kMaxAggTiles][2];
+    bool have[kMaxAggTiles];
+#pragma unroll
+    for (int t = 0; t < kMaxAggTiles; ++t) {
+      have[t] = i + t < n_mine;  // warp-uniform
+      mag[t][0] = mag[t][1] = 0.f;
+      if (have[t]) {
+        const bool ready = __all_sync(kFull, mbar_wait_bounded(smem_u32(&bars[wid][t]), parity));
+        if (!ready) {
+          if (lane == 0) flag_status(p.status, TRIATTN_DEV_WAIT_TIMEOUT);
+          failed = true;
+          have[t] = false;
+        }
+      }
+      if (have[t]) {
+        load_tile(smem_u32(my_ring + (size_t)t * SLOT_BYTES), a[t], mag[t][0], mag[t][1]);
+      } else {
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) a[t][ks][e] = 0u;
+      }
+    }
+    if (failed) break;
+    // every shared-memory value of the slots is in registers: refill them with the next tiles of this warp
     __syncwarp();
-    if (i + kMaxAggSlots < n_mine) {
+    if (i + kMaxAggTiles < n_mine) {
       if (lane == 0) fence_proxy_async();
       __syncwarp();
-      fetch(wid + (i + kMaxAggSlots) * kMaxAggWarps, slot);
+#pragma unroll
+      for (int t = 0; t < kMaxAggTiles; ++t)
+        if (i + kMaxAggTiles + t < n_mine) fetch(wid + (i + kMaxAggTiles + t) * kMaxAggWarps, t);
     }
+    parity ^= 1u;
 
-    // offsets: one column tile each, kMaxAggChains independent accumulator chains in flight
-    float bestA = -INFINITY, bestB = -INFINITY;
-    for (int o = 0; o < O; o += kMaxAggChains) {
-      float c[kMaxAggChains][4];
-      const uint4* w[kMaxAggChains];
+    // offsets: one column tile each; the weight fragments of an offset feed all tiles
+    float best[kMaxAggTiles][2];
 #pragma unroll
-      for (int n = 0; n < kMaxAggChains; ++n) {
+    for (int t = 0; t < kMaxAggTiles; ++t) best[t][0] = best[t][1] = -INFINITY;
+    for (int o = 0; o < O; ++o) {
+      float c[kMaxAggTiles][4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) c[n][e] = 0.f;
-        w[n] = s_w + (size_t)min(o + n, O - 1) * (KS / 2) * 32 + lane;  // past the last offset: recompute it, ignored below
-      }
+      for (int t = 0; t < kMaxAggTiles; ++t)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) c[t][e] = 0.f;
+      const uint4* w = s_w + (size_t)o * (KS / 2) * 32 + lane;
 #pragma unroll
       for (int r = 0; r < KS / 2; ++r) {
-        uint4 u[kMaxAggChains];
+        const uint4 u = w[r * 32];
 #pragma unroll
-        for (int n = 0; n < kMaxAggChains; ++n) u[n] = w[n][r * 32];
+        for (int t = 0; t < kMaxAggTiles; ++t)
+          mma_bf16_16816(c[t], a[t][2 * r][0], a[t][2 * r][1], a[t][2 * r][2], a[t][2 * r][3], u.x, u.y);
 #pragma unroll
-        for (int n = 0; n < kMaxAggChains; ++n)
-          mma_bf16_16816(c[n], a[2 * r][0], a[2 * r][1], a[2 * r][2], a[2 * r][3], u[n].x, u[n].y);
-#pragma unroll
-        for (int n = 0; n < kMaxAggChains; ++n)
-          mma_bf16_16816(c[n], a[2 * r + 1][0], a[2 * r + 1][1], a[2 * r + 1][2], a[2 * r + 1][3], u[n].z, u[n].w);
+        for (int t = 0; t < kMaxAggTiles; ++t)
+          mma_bf16_16816(c[t], a[t][2 * r + 1][0], a[t][2 * r + 1][1], a[t][2 * r + 1][2], a[t][2 * r + 1][3], u.z, u.w);
       }
 #pragma unroll
-      for (int n = 0; n < kMaxAggChains; ++n) {
-        // a duplicate of the last offset (o + n >= O) leaves the maximum unchanged
-        bestA = fmaxf(bestA, c[n][0] + c[n][1]);
-        bestB = fmaxf(bestB, c[n][2] + c[n][3]);
+      for (int t = 0; t < kMaxAggTiles; ++t) {
+        best[t][0] = fmaxf(best[t][0], c[t][0] + c[t][1]);
+        best[t][1] = fmaxf(best[t][1], c[t][2] + c[t][3]);
       }
     }
-    const float scA = bestA + ((accm[0][0] + accm[1][0]) + (accm[0][1] + accm[1][1]));
-    const float scB = bestB + ((accm[0][2] + accm[1][2]) + (accm[0][3] + accm[1][3]));
-    if (rt < nq) {
-      const int gA = tok0 + rg;
-      float* out = raw_head + (size_t)gA * p.gp_total;
-      if (gA < seq_len) {
-        out[0] = scA;
-        s1 += scA;
-        s2 = fmaf(scA, scA, s2);
+#pragma unroll
+    for (int t = 0; t < kMaxAggTiles; ++t) {
+      if (have[t] && rt < nq) {
+        const int gA = (tile0 + wid + (i + t) * kMaxAggWarps) * kMmaKeys + rg;
+        float* out = raw_head + (size_t)gA * p.gp_total;
+        const float scA = best[t][0] + mag[t][0], scB = best[t][1] + mag[t][1];
+        if (gA < seq_len) {
+          out[0] = scA;
+          s1 += scA;
+          s2 = fmaf(scA, scA, s2);
+        }
+        if (gA + 8 < seq_len) {
+          out[(size_t)8 * p.gp_total] = scB;
+          s1 += scB;
+          s2 = fmaf(scB, scB, s2);
+        }
       }
-      if (gA + 8 < seq_len) {
-        out[(size_t)8 * p.gp_total] = scB;
-        s1 += scB;
-        s2 = fmaf(scB, scB, s2);
-      }
-    }
-    if (++slot == kMaxAggSlots) {
-      slot = 0;
-      parity ^= 1u;
     }
   }
   // moments of query slot rt over this warp's keys
