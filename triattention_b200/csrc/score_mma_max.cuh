@@ -21,6 +21,10 @@ namespace triattn {
 
 constexpr int kMaxAggWarps = 12;
 constexpr int kMaxAggThreads = kMaxAggWarps * 32;
+#ifndef MAXAGG_UNROLL
+#define MAXAGG_UNROLL 1
+#endif
+constexpr int kMaxAggUnroll = MAXAGG_UNROLL;  // unroll factor of the loop over offsets
 constexpr int kMaxAggTiles = 2;   // 16-key tiles a warp works on at once (independent accumulator chains)
 constexpr int kMaxAggSlots = kMaxAggTiles;  // ring slots per warp: the tiles move to registers, then the slots refill
 
@@ -253,6 +257,7 @@ __global__ void __launch_bounds__(kMaxAggThreads, 1) score_paged_mma_max_kernel(
     float best[kMaxAggTiles][2];
 #pragma unroll
     for (int t = 0; t < kMaxAggTiles; ++t) best[t][0] = best[t][1] = -INFINITY;
+#pragma unroll(kMaxAggUnroll)
     for (int o = 0; o < O; ++o) {
       float c[kMaxAggTiles][4];
 #pragma unroll
