@@ -6,6 +6,7 @@ Run where a checkout of the reference is available (default: a directory
 
     python tests/golden/make_golden.py                       # everything
     python tests/golden/make_golden.py --only input_patch    # only input_patch_cases.npz
+    python tests/golden/make_golden.py --only calibration    # only calibration_cases.npz
 
 The reference is imported unmodified, on CPU, with three test-side shims:
 
@@ -449,7 +450,54 @@ def gen_input_patch_cases(out: dict):
     out["input_patch_cases"] = {"file": "input_patch_cases.npz", "cases": cases}
 
 
+def gen_calibration_cases(out: dict):
+    """Statistics the reference's calibration arithmetic (scripts/calibrate.py:49-95, 223-240) derives from rotated queries."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("ref_calibrate", str(REF / "scripts" / "calibrate.py"))
+    ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref)
+    gen = torch.Generator().manual_seed(20269002)
+    arrays, cases = {}, {}
+    for name, (H, T, D, style, scale) in {"half_d128": (3, 37, 128, "half", 1.0),
+                                          "interleaved_d64_scaled": (2, 20, 64, "interleaved", 0.5)}.items():
+        inv = synth.rope_inv_freq(D, 1e6)
+        pos = torch.arange(T, dtype=torch.float32)
+        ang = pos[:, None] * inv[None, :]
+        cosF, sinF = torch.cos(ang), torch.sin(ang)
+        if style == "interleaved":
+            cos = cosF.repeat_interleave(2, dim=-1)
+            sin = sinF.repeat_interleave(2, dim=-1)
+        else:
+            cos = torch.cat((cosF, cosF), dim=-1)
+            sin = torch.cat((sinF, sinF), dim=-1)
+        q = torch.randn((1, H, T, D), generator=gen, dtype=torch.float32)
+        q_rot = (q * cos[None, None] + ref._rotate_half(q, style=style) * sin[None, None]) * scale
+        # the reference receives the model's rotary tables, which carry the attention scaling factor
+        base = ref._invert_rope(q_rot, cos[None, None] * scale, sin[None, None] * scale, scale, style=style)
+        mr, mi, ma = [], [], []
+        for h in range(H):
+            zc = ref._to_complex_pairs(base[0, h], style=style)
+            m = zc.mean(dim=0)
+            mr.append(m.real)
+            mi.append(m.imag)
+            ma.append(zc.abs().mean(dim=0))
+        arrays[f"{name}/q_rot"] = q_rot.numpy()
+        arrays[f"{name}/cos"] = cosF.numpy()
+        arrays[f"{name}/sin"] = sinF.numpy()
+        arrays[f"{name}/q_mean_real"] = torch.stack(mr).numpy()
+        arrays[f"{name}/q_mean_imag"] = torch.stack(mi).numpy()
+        arrays[f"{name}/q_abs_mean"] = torch.stack(ma).numpy()
+        cases[name] = dict(rope_style=style, attn_scale=scale, head_dim=D)
+    np.savez_compressed(HERE / "calibration_cases.npz", **arrays)
+    out["calibration_cases"] = {"file": "calibration_cases.npz", "cases": cases}
+
+
 def main():
+    if len(sys.argv) > 2 and sys.argv[1] == "--only" and sys.argv[2] == "calibration":
+        out = json.loads((HERE / "manifest.json").read_text())
+        gen_calibration_cases(out)
+        (HERE / "manifest.json").write_text(json.dumps(out, indent=1, sort_keys=True))
+        return
     if len(sys.argv) > 2 and sys.argv[1] == "--only" and sys.argv[2] == "input_patch":
         out = json.loads((HERE / "manifest.json").read_text())
         gen_input_patch_cases(out)
@@ -462,6 +510,7 @@ def main():
     gen_real_stats_case(out)
     gen_hook_cases(out)
     gen_input_patch_cases(out)
+    gen_calibration_cases(out)
     (HERE / "manifest.json").write_text(json.dumps(out, indent=1, sort_keys=True))
     print("wrote", [p.name for p in HERE.iterdir()])
 
