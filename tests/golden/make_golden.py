@@ -199,7 +199,7 @@ def gen_selector_cases(out: dict):
         "chunked_group": dict(seed=synth.seed_for(91, 1), num_layers=3, num_q_heads=8, num_kv_heads=2, head_dim=128,
                               theta=1e6, total_tokens=4500, block_size=16, kv_axis=1, budget=1024, window=128,
                               round_start=4500),
-        # BASELINE config-0 head shapes, shorter, round_start != T, consecutive blocks (view fast path)
+        # head shapes of the single-layer benchmark configuration, shorter, round_start != T, consecutive blocks (view fast path)
         "c0_like": dict(seed=synth.seed_for(91, 2), num_layers=1, num_q_heads=32, num_kv_heads=8, head_dim=128,
                         theta=1e6, total_tokens=2100, block_size=16, kv_axis=0, budget=512, window=128,
                         round_start=9000, consecutive_blocks=True),

@@ -45,7 +45,7 @@ def _stats_dict(stats):
 
 
 def test_config0_full_size_parity():
-    """BASELINE config 0: 1 layer, 32q/8kv heads, D 128, 4096 tokens at positions 0..4095, query position 4096,
+    """The single-layer benchmark configuration: 1 layer, 32q/8kv heads, D 128, 4096 tokens at positions 0..4095, query position 4096,
     budget 2048, window 128."""
     gen = torch.Generator().manual_seed(synth.seed_for(0, 0))
     T, budget, window = 4096, 2048, 128
