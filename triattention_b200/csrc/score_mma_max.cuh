@@ -11,8 +11,10 @@
 // simplicity: a CTA works on ONE (layer, request, virtual head); its weight fragments for all offsets live in
 // shared memory in fragment order (conflict-free 16-byte loads), and every warp streams its own 16-key tiles of
 // that head, two at a time (one load of an offset's weight fragments feeds both), through private 16-row slots
-// fetched row by row with 1-D bulk async copies on the warp's own mbarriers (bounded waits): the tiles move to
-// registers, the slots are refilled at once and the copies land during the 17 offsets.  No warp waits for another.
+// fetched row by row with 1-D bulk async copies on the warp's own mbarriers (bounded waits).  Rows are padded by
+// 16 bytes, so ldmatrix.x4 delivers the key fragments conflict-free and already in MMA register order; the tiles
+// move to registers, the slots are refilled at once and the copies land during the 17 offsets.  No warp waits for
+// another.
 #pragma once
 
 #include "score_mma.cuh"
@@ -29,18 +31,27 @@ constexpr int kMaxAggTiles = 2;   // 16-key tiles a warp works on at once (indep
 constexpr int kMaxAggSlots = kMaxAggTiles;  // ring slots per warp: the tiles move to registers, then the slots refill
 
 // dynamic shared memory: weight fragments [O][KS/2][32 lanes][4 words] + rings [warps][slots][16 rows][D*2 bytes]
+// (rows are padded by 16 bytes so that the 8 row addresses of an ldmatrix phase fall into 8 different bank groups)
 inline size_t max_agg_smem_bytes(int D, int num_offsets) {
-  return (size_t)num_offsets * (D / 32) * 32 * 16 + (size_t)kMaxAggWarps * kMaxAggSlots * kMmaKeys * D * 2;
+  return (size_t)num_offsets * (D / 32) * 32 * 16 + (size_t)kMaxAggWarps * kMaxAggSlots * kMmaKeys * (D * 2 + 16);
+}
+
+// four 8x8 b16 matrices -> the A fragment (a0..a3) of one m16n8k16 MMA, straight in fragment order
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&a)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3])
+               : "r"(addr));
 }
 
 template <int D, bool INTERLEAVED>
 __global__ void __launch_bounds__(kMaxAggThreads, 1) score_paged_mma_max_kernel(const __grid_constant__ ScoreParams p) {
   constexpr int F = D / 2;
-  constexpr int NQ = D / 32;   // 16-byte chunks per key and thread
   constexpr int KS = D / 16;   // k-steps (MMAs) per offset
   constexpr int GP = 4;
   constexpr int ROW_BYTES = D * 2;
-  constexpr int SLOT_BYTES = kMmaKeys * ROW_BYTES;
+  constexpr int ROW_STRIDE = ROW_BYTES + 16;  // padded row pitch inside a slot
+  constexpr int SLOT_BYTES = kMmaKeys * ROW_STRIDE;
+  constexpr int NMG = KS / 2;                 // magnitude MMAs per part (16 frequencies each)
 
   extern __shared__ __align__(128) unsigned char smem_dyn[];
   __shared__ __align__(8) uint64_t bars[kMaxAggWarps][kMaxAggSlots];
@@ -80,11 +91,10 @@ __global__ void __launch_bounds__(kMaxAggThreads, 1) score_paged_mma_max_kernel(
     const int head = crg >> 1, part = crg & 1;
     const bool on = head < nq;
     const float* w = p.weights + (((size_t)l * p.B + b) * Hq + (size_t)qbase + (on ? head : 0)) * rows_w * F;
-    const int d0 = 8 * (crt + 4 * (ks >> 1)) + 4 * (ks & 1);
     uint32_t v[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const int d = d0 + i;
+      const int d = 16 * ks + 8 * (i >> 1) + 2 * crt + (i & 1);  // b0: k = 2t, 2t+1; b1: k = 2t+8, 2t+9
       const int comp = INTERLEAVED ? (d & 1) : (d >= F ? 1 : 0);
       const int f = INTERLEAVED ? (d >> 1) : (d >= F ? d - F : d);
       const float x = on ? __ldg(w + (size_t)(comp * O + o) * F + f) : 0.f;
@@ -97,19 +107,20 @@ __global__ void __launch_bounds__(kMaxAggThreads, 1) score_paged_mma_max_kernel(
     dst[1] = v[2] | (v[3] << 16);
   }
   // magnitude fragments stay in registers
-  uint32_t bmg[NQ][2];
+  uint32_t bmg[NMG][2];
   {
     const int head = rg >> 1, part = rg & 1;
     const bool on = head < nq;
     const float* wm = p.weights + ((((size_t)l * p.B + b) * Hq + (size_t)qbase + (on ? head : 0)) * rows_w + 2 * O) * F;
 #pragma unroll
-    for (int j = 0; j < NQ; ++j) {
-      const int f0 = INTERLEAVED ? 4 * (rt + 4 * j) : 8 * (rt + 4 * (j >> 1)) + 4 * (j & 1);
+    for (int j = 0; j < NMG; ++j) {
       uint32_t v[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
+        // the 4 frequencies this thread feeds into magnitude MMA j, in the order load_tile packs |k|
+        const int f = INTERLEAVED ? 16 * j + 4 * i + rt : 16 * j + 8 * (i >> 1) + 2 * rt + (i & 1);
         uint32_t hi, lo;
-        bf16_split(on ? __ldg(wm + f0 + i) : 0.f, hi, lo);
+        bf16_split(on ? __ldg(wm + f) : 0.f, hi, lo);
         v[i] = part ? lo : hi;
       }
       bmg[j][0] = v[0] | (v[1] << 16);
@@ -140,7 +151,7 @@ __global__ void __launch_bounds__(kMaxAggThreads, 1) score_paged_mma_max_kernel(
       }
       const unsigned char* src = kbase + (long long)blk * p.block_stride_bytes +
                                  ((long long)(t - bi * p.bs) * p.token_stride + (long long)kvh * p.head_stride) * 2;
-      bulk_copy_g2s(smem_u32(my_ring + (size_t)slot * SLOT_BYTES + (size_t)lane * ROW_BYTES), src, ROW_BYTES, bar);
+      bulk_copy_g2s(smem_u32(my_ring + (size_t)slot * SLOT_BYTES + (size_t)lane * ROW_STRIDE), src, ROW_BYTES, bar);
     }
   };
 
@@ -156,56 +167,46 @@ __global__ void __launch_bounds__(kMaxAggThreads, 1) score_paged_mma_max_kernel(
   };
   // A fragments of one tile (kept for all offsets) and its magnitude term for this thread's two keys
   auto load_tile = [&](uint32_t base, uint32_t (&a)[KS][4], float& magA, float& magB) {
-    const uint32_t rowA = base + (uint32_t)(rg * ROW_BYTES) + 16u * rt, rowB = rowA + 8u * ROW_BYTES;
+    // lane -> (row, 8-column block) of the 8x8 matrix it addresses: matrices 0..3 = (rows 0-7 | 8-15) x (k 0-7 | 8-15)
+    const uint32_t lm = base + (uint32_t)(((lane & 7) + 8 * ((lane >> 3) & 1)) * ROW_STRIDE) + 16u * (lane >> 4);
     float accm[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
-    for (int c = 0; c < NQ; ++c) {
-      const uint4 xA = lds128(rowA + 64u * c), xB = lds128(rowB + 64u * c);
-      a[2 * c][0] = xA.x; a[2 * c][1] = xB.x; a[2 * c][2] = xA.y; a[2 * c][3] = xB.y;
-      a[2 * c + 1][0] = xA.z; a[2 * c + 1][1] = xB.z; a[2 * c + 1][2] = xA.w; a[2 * c + 1][3] = xB.w;
-    }
+    for (int ks = 0; ks < KS; ++ks) ldmatrix_x4(a[ks], lm + 32u * ks);
+    // a[ks] = {(key rg, dims 16ks+2rt,+1), (key rg+8, same), (key rg, dims 16ks+8+2rt,+1), (key rg+8, same)}
     if constexpr (!INTERLEAVED) {
 #pragma unroll
-      for (int q = 0; q < NQ / 2; ++q) {
-        // chunk q holds re of 8 frequencies, chunk q + NQ/2 their im
-        uint32_t hA[4], lA[4], hB[4], lB[4];
+      for (int j = 0; j < NMG; ++j) {
+        // k-step j holds re of 16 frequencies, k-step j + NMG their im: |k| comes out in fragment order
+        uint32_t h[4], lo[4];
 #pragma unroll
-        for (int i2 = 0; i2 < 4; ++i2) {
-          const int ks = 2 * q + (i2 >> 1), kr = 2 * (i2 & 1);  // word i2 of the chunk: a[ks][kr] (row A), a[ks][kr+1] (row B)
-          const int ksi = ks + NQ;                               // same word of the im chunk
-          const float2 ra = bf16x2_to_float2(a[ks][kr]), ia = bf16x2_to_float2(a[ksi][kr]);
-          const float2 rb = bf16x2_to_float2(a[ks][kr + 1]), ib = bf16x2_to_float2(a[ksi][kr + 1]);
-          const float2 ma = ffma2(ia, ia, fmul2(ra, ra));
-          const float2 mb = ffma2(ib, ib, fmul2(rb, rb));
-          split_pair(sqrt_approx(ma.x), sqrt_approx(ma.y), hA[i2], lA[i2]);
-          split_pair(sqrt_approx(mb.x), sqrt_approx(mb.y), hB[i2], lB[i2]);
+        for (int e = 0; e < 4; ++e) {
+          const float2 re = bf16x2_to_float2(a[j][e]), im = bf16x2_to_float2(a[j + NMG][e]);
+          const float2 m = ffma2(im, im, fmul2(re, re));
+          split_pair(sqrt_approx(m.x), sqrt_approx(m.y), h[e], lo[e]);
         }
-#pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          const int j = 2 * q + hh;
-          mma_bf16_16816(accm[0], hA[2 * hh], hB[2 * hh], hA[2 * hh + 1], hB[2 * hh + 1], bmg[j][0], bmg[j][1]);
-          mma_bf16_16816(accm[1], lA[2 * hh], lB[2 * hh], lA[2 * hh + 1], lB[2 * hh + 1], bmg[j][0], bmg[j][1]);
-        }
+        mma_bf16_16816(accm[0], h[0], h[1], h[2], h[3], bmg[j][0], bmg[j][1]);
+        mma_bf16_16816(accm[1], lo[0], lo[1], lo[2], lo[3], bmg[j][0], bmg[j][1]);
       }
     } else {
 #pragma unroll
-      for (int c = 0; c < NQ; ++c) {
-        float mA[4], mB[4];
+      for (int j = 0; j < NMG; ++j) {
+        // a word is (re, im) of one frequency: k-steps 2j, 2j+1 give this thread 4 frequencies per key
+        float m[2][4];  // [k-step of the pair][fragment element]
 #pragma unroll
-        for (int i2 = 0; i2 < 4; ++i2) {
-          const int ks = 2 * c + (i2 >> 1), kr = 2 * (i2 & 1);
-          const float2 va = bf16x2_to_float2(a[ks][kr]), vb = bf16x2_to_float2(a[ks][kr + 1]);
-          const float2 pa = fmul2(va, va), pb = fmul2(vb, vb);
-          mA[i2] = sqrt_approx(pa.x + pa.y);
-          mB[i2] = sqrt_approx(pb.x + pb.y);
-        }
-        uint32_t hA[2], lA[2], hB[2], lB[2];
-        split_pair(mA[0], mA[1], hA[0], lA[0]);
-        split_pair(mA[2], mA[3], hA[1], lA[1]);
-        split_pair(mB[0], mB[1], hB[0], lB[0]);
-        split_pair(mB[2], mB[3], hB[1], lB[1]);
-        mma_bf16_16816(accm[0], hA[0], hB[0], hA[1], hB[1], bmg[c][0], bmg[c][1]);
-        mma_bf16_16816(accm[1], lA[0], lB[0], lA[1], lB[1], bmg[c][0], bmg[c][1]);
+        for (int s2 = 0; s2 < 2; ++s2)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 v = bf16x2_to_float2(a[2 * j + s2][e]);
+            const float2 q = fmul2(v, v);
+            m[s2][e] = sqrt_approx(q.x + q.y);
+          }
+        uint32_t h[4], lo[4];
+        split_pair(m[0][0], m[0][2], h[0], lo[0]);  // key rg:   frequencies 16j + rt, 16j + 4 + rt
+        split_pair(m[0][1], m[0][3], h[1], lo[1]);  // key rg+8
+        split_pair(m[1][0], m[1][2], h[2], lo[2]);  // key rg:   frequencies 16j + 8 + rt, 16j + 12 + rt
+        split_pair(m[1][1], m[1][3], h[3], lo[3]);  // key rg+8
+        mma_bf16_16816(accm[0], h[0], h[1], h[2], h[3], bmg[j][0], bmg[j][1]);
+        mma_bf16_16816(accm[1], lo[0], lo[1], lo[2], lo[3], bmg[j][0], bmg[j][1]);
       }
     }
     magA = (accm[0][0] + accm[1][0]) + (accm[0][1] + accm[1][1]);
