@@ -23,10 +23,10 @@ namespace triattn {
 
 constexpr int kMaxAggWarps = 12;
 constexpr int kMaxAggThreads = kMaxAggWarps * 32;
-#ifndef MAXAGG_UNROLL
-#define MAXAGG_UNROLL 1
+#ifndef MAXAGG_OFFSETS
+#define MAXAGG_OFFSETS 1
 #endif
-constexpr int kMaxAggUnroll = MAXAGG_UNROLL;  // unroll factor of the loop over offsets
+constexpr int kMaxAggOffsets = MAXAGG_OFFSETS;  // offsets a warp works on at once
 constexpr int kMaxAggTiles = 2;   // 16-key tiles a warp works on at once (independent accumulator chains)
 constexpr int kMaxAggSlots = kMaxAggTiles;  // ring slots per warp: the tiles move to registers, then the slots refill
 
@@ -258,29 +258,42 @@ __global__ void __launch_bounds__(kMaxAggThreads, 1) score_paged_mma_max_kernel(
     float best[kMaxAggTiles][2];
 #pragma unroll
     for (int t = 0; t < kMaxAggTiles; ++t) best[t][0] = best[t][1] = -INFINITY;
-#pragma unroll(kMaxAggUnroll)
-    for (int o = 0; o < O; ++o) {
-      float c[kMaxAggTiles][4];
+    // kMaxAggOffsets offsets at a time: with the tiles that gives tiles x offsets independent accumulator chains
+    for (int o = 0; o < O; o += kMaxAggOffsets) {
+      float c[kMaxAggOffsets][kMaxAggTiles][4];
+      const uint4* w[kMaxAggOffsets];
 #pragma unroll
-      for (int t = 0; t < kMaxAggTiles; ++t)
+      for (int n = 0; n < kMaxAggOffsets; ++n) {
+        w[n] = s_w + (size_t)min(o + n, O - 1) * (KS / 2) * 32 + lane;  // past the end: the last offset again (max unchanged)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) c[t][e] = 0.f;
-      const uint4* w = s_w + (size_t)o * (KS / 2) * 32 + lane;
+        for (int t = 0; t < kMaxAggTiles; ++t)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) c[n][t][e] = 0.f;
+      }
 #pragma unroll
       for (int r = 0; r < KS / 2; ++r) {
-        const uint4 u = w[r * 32];
+        uint4 u[kMaxAggOffsets];
 #pragma unroll
-        for (int t = 0; t < kMaxAggTiles; ++t)
-          mma_bf16_16816(c[t], a[t][2 * r][0], a[t][2 * r][1], a[t][2 * r][2], a[t][2 * r][3], u.x, u.y);
+        for (int n = 0; n < kMaxAggOffsets; ++n) u[n] = w[n][r * 32];
 #pragma unroll
-        for (int t = 0; t < kMaxAggTiles; ++t)
-          mma_bf16_16816(c[t], a[t][2 * r + 1][0], a[t][2 * r + 1][1], a[t][2 * r + 1][2], a[t][2 * r + 1][3], u.z, u.w);
+        for (int n = 0; n < kMaxAggOffsets; ++n)
+#pragma unroll
+          for (int t = 0; t < kMaxAggTiles; ++t)
+            mma_bf16_16816(c[n][t], a[t][2 * r][0], a[t][2 * r][1], a[t][2 * r][2], a[t][2 * r][3], u[n].x, u[n].y);
+#pragma unroll
+        for (int n = 0; n < kMaxAggOffsets; ++n)
+#pragma unroll
+          for (int t = 0; t < kMaxAggTiles; ++t)
+            mma_bf16_16816(c[n][t], a[t][2 * r + 1][0], a[t][2 * r + 1][1], a[t][2 * r + 1][2], a[t][2 * r + 1][3],
+                           u[n].z, u[n].w);
       }
 #pragma unroll
-      for (int t = 0; t < kMaxAggTiles; ++t) {
-        best[t][0] = fmaxf(best[t][0], c[t][0] + c[t][1]);
-        best[t][1] = fmaxf(best[t][1], c[t][2] + c[t][3]);
-      }
+      for (int n = 0; n < kMaxAggOffsets; ++n)
+#pragma unroll
+        for (int t = 0; t < kMaxAggTiles; ++t) {
+          best[t][0] = fmaxf(best[t][0], c[n][t][0] + c[n][t][1]);
+          best[t][1] = fmaxf(best[t][1], c[n][t][2] + c[n][t][3]);
+        }
     }
 #pragma unroll
     for (int t = 0; t < kMaxAggTiles; ++t) {
