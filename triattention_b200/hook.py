@@ -262,21 +262,40 @@ def run_group_compaction_pipeline(*, req_id, signal, config, strict, num_compute
         prefill_len = min(int(signal.prefill_len), total)
         group_budget = min(budget_total, total)
         round_start = int(max(0, num_computed_tokens))
+        # Default mode with the native selector and the native compaction: one fused call does the whole group.
+        fused = getattr(select_keep_indices_for_group, "_fused_group_compress", None)
+        fused_result = None
+        if (fused is not None and per_head_compact_fn is _NATIVE_PER_HEAD_COMPACT
+                and not bool(getattr(config, "preserve_dropped_tokens", False))
+                and config.pruning_mode == "per_head"
+                and config.per_head_selection_semantics == "hf_aligned_global_per_head"
+                and len({t.device for _, t in layer_tensors}) == 1):
+            try:
+                fused_result = fused(
+                    caches=[t for _, t in layer_tensors], layer_indices=[i for i, _ in layer_tensors],
+                    block_ids=block_ids, total_tokens=total, prefill_len=prefill_len,
+                    protect_prefill=signal.protect_prefill, round_start=round_start, budget_total=group_budget)
+            except Exception as exc:
+                raise RuntimeError(
+                    f"{TRITON_SCORING_REQUIRED_MARKER}:req={req_id}:gid={gid}:global_per_head:{type(exc).__name__}") from exc
         try:
-            tasks, label = _select_for_group(
-                req_id=req_id, gid=gid, layer_tensors=layer_tensors, block_ids=block_ids, block_size=block_size,
-                total_tokens=total, prefill_len=prefill_len, protect_prefill=signal.protect_prefill,
-                round_start=round_start, budget_total=group_budget, config=config, strict=strict,
-                select_keep_indices=select_keep_indices, select_keep_indices_for_group=select_keep_indices_for_group)
+            if fused_result is not None:
+                tasks, label = [], KeepPlan.from_selector_result(fused_result).selection_mode_label
+            else:
+                tasks, label = _select_for_group(
+                    req_id=req_id, gid=gid, layer_tensors=layer_tensors, block_ids=block_ids, block_size=block_size,
+                    total_tokens=total, prefill_len=prefill_len, protect_prefill=signal.protect_prefill,
+                    round_start=round_start, budget_total=group_budget, config=config, strict=strict,
+                    select_keep_indices=select_keep_indices, select_keep_indices_for_group=select_keep_indices_for_group)
         except ValueError as exc:
             if str(exc) == "prefill_exceeds_budget":
                 return {"applied": False, "reason": "prefill_exceeds_budget"}
             raise
-        group_len = None
+        group_len = int(fused_result["cache_len_after"]) if fused_result is not None else None
         try:
             bt_cache: dict = {}
             preserve = bool(getattr(config, "preserve_dropped_tokens", False))
-            one_plan = (len(tasks) > 1 and tasks[0][2].mode == "per_head"
+            one_plan = (fused_result is None and len(tasks) > 1 and tasks[0][2].mode == "per_head"
                         and all(t[2] is tasks[0][2] or t[2].indices is tasks[0][2].indices for t in tasks)
                         and per_head_compact_fn is _NATIVE_PER_HEAD_COMPACT
                         and len({t[1].device for t in tasks}) == 1)
@@ -325,7 +344,7 @@ def run_group_compaction_pipeline(*, req_id, signal, config, strict, num_compute
             if cache_len_after is not None and group_len != cache_len_after:
                 raise RuntimeError(
                     f"{TRITON_SCORING_REQUIRED_MARKER}:inconsistent_cache_len_after:req={req_id}:gid={gid}:"
-                    f"layer={tasks[0][0]}:expected={cache_len_after}:actual={group_len}")
+                    f"layer={tasks[0][0] if tasks else -1}:expected={cache_len_after}:actual={group_len}")
             cache_len_after = group_len
             compacted_any = True
             if config.enable_experimental_block_reclaim:

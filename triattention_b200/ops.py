@@ -49,6 +49,9 @@ def split_kv_axes(kv_cache: torch.Tensor, kv_axis: Optional[int] = None):
     raise ValueError("Unsupported KV layout for compaction: expected a dimension with size 2")
 
 
+_VIEW_CACHE: dict = {}
+
+
 @dataclass
 class PagedCacheView:
     """Device-side description of the layers of one KV-cache group (shared block table)."""
@@ -70,6 +73,21 @@ class PagedCacheView:
     def from_layers(cls, kv_caches: Sequence[torch.Tensor], kv_axis: Optional[int] = None) -> "PagedCacheView":
         if not kv_caches:
             raise ValueError("no kv cache layers")
+        # An engine keeps the same cache tensors for its whole life: remember the view (device pointer arrays
+        # included) per set of layers, so a compression step costs no per-layer Python and no pointer upload.
+        key = (kv_axis, tuple(int(c.data_ptr()) for c in kv_caches), tuple(kv_caches[0].shape),
+               tuple(kv_caches[0].stride()), kv_caches[0].dtype, str(kv_caches[0].device))
+        hit = _VIEW_CACHE.get(key)
+        if hit is not None:
+            return hit
+        view = cls._build(kv_caches, kv_axis)
+        if len(_VIEW_CACHE) >= 64:
+            _VIEW_CACHE.clear()
+        _VIEW_CACHE[key] = view
+        return view
+
+    @classmethod
+    def _build(cls, kv_caches: Sequence[torch.Tensor], kv_axis: Optional[int]) -> "PagedCacheView":
         k0, v0 = split_kv_axes(kv_caches[0], kv_axis)
         if k0.dtype not in (torch.bfloat16, torch.float16):
             raise ValueError(f"paged cache must be 16-bit, got {k0.dtype}")

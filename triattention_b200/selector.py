@@ -231,6 +231,59 @@ def build_triattention_selector(
             "debug_recent_count": _recent(total_tokens),
         }
 
+    fused_engines: dict = {}
+
+    def _compress_group_fused(*, caches: list, layer_indices: list, block_ids, total_tokens: int, prefill_len: int,
+                              protect_prefill: bool, round_start: int, budget_total: int):
+        """Default mode in ONE native call: score -> select -> compact every layer of the group with the shared
+        per-KV-head keep set (what the group selector followed by the per-layer compaction loop produce,
+        selector_hf.py:749-1083 + layout_engine.py:112-139).  Returns the selector's result dictionary (plus
+        ``cache_len_after``) or None when this request needs the staged path (another mode, nothing to drop,
+        protected prefill larger than the budget)."""
+        if requested_mode != "per_head" or semantics != "hf_aligned_global_per_head":
+            return None
+        if total_tokens <= budget_total or not caches:
+            return None
+        if protect_prefill and config.include_prefill_in_budget and prefill_len > budget_total:
+            return None
+        k = min(int(budget_total), int(total_tokens))
+        if k <= 0:
+            return None
+        from . import engine as _engine
+        agg = os.environ.get("TRIATTN_RUNTIME_DEBUG_GROUP_PERHEAD_AGG_MODE", "mean").strip().lower()
+        if agg not in {"mean", "max"}:
+            agg = "mean"
+        try:
+            view = ops.PagedCacheView.from_layers(caches, kv_axis=kv_axis_hint(caches[0]))
+            dstats = _packed([int(i) for i in layer_indices], view.device, None)
+            _group_of(dstats.num_heads, view.num_kv_heads)
+            comp = fused_engines.get(str(view.device))
+            if comp is None:
+                comp = _engine.PagedCompressor(dstats)
+                fused_engines[str(view.device)] = comp
+            comp.stats = dstats
+            comp.window = int(config.window_size) if config.window_size > 0 else 0
+            comp.normalize = bool(config.sparse_normalize_scores)
+            comp.offset_agg, comp.flags = offset_agg, flags
+            comp.layer_reduce = _native.REDUCE_MAX if agg == "max" else _native.REDUCE_MEAN
+            ids = block_ids.tolist() if isinstance(block_ids, torch.Tensor) else [int(x) for x in block_ids]
+            res = comp.compress(view, [ids], [int(total_tokens)], [int(round_start)], [k],
+                                prefill_lens=[int(prefill_len)] if (protect_prefill and prefill_len > 0) else None)
+            if res.device_status:
+                raise _native.NativeLibraryError(f"device_status:{res.device_status}")
+        except _native.NativeLibraryError as exc:
+            raise RuntimeError(f"{TRITON_SCORING_REQUIRED_MARKER}:score_failed:{type(exc).__name__}") from exc
+        return {
+            "mode": "per_head",
+            "indices": res.keep[0].long(),   # a copy: the engine reuses its output buffer
+            "semantic": "hf_aligned_global_per_head",
+            "group_agg_mode": agg,
+            "debug_group_layer_indices": [int(i) for i in layer_indices],
+            "debug_recent_count": _recent(total_tokens),
+            "cache_len_after": k,
+        }
+
     setattr(_select_keep_indices, "_supports_paged", True)
     setattr(_select_keep_indices_for_group_per_head, "_supports_paged_group", True)
+    setattr(_select_keep_indices_for_group_per_head, "_fused_group_compress", _compress_group_fused)
     return _select_keep_indices, _select_keep_indices_for_group_per_head, "enabled"
