@@ -23,6 +23,7 @@ import torch
 
 REPO = Path(__file__).resolve().parent
 sys.path.insert(0, str(REPO))
+sys.path.insert(1, str(REPO / "tests"))  # synth.py: the seeded workload generator shared with the tests
 
 CONFIGS = {
     # name: layers, q heads, kv heads, head_dim, theta, batch, tokens, budget, window
@@ -152,7 +153,8 @@ def build_device_workload(c: dict, rank: int, device: torch.device, config_idx: 
     [0.1, 10], rotated at positions 0..T-1; V ~ N(0,1)); drawn with a seeded device generator so that the
     38 GB of the full configuration are produced in seconds.
     """
-    from triattention_b200 import ops, synth
+    from triattention_b200 import ops
+    import synth
 
     seed = synth.seed_for(config_idx, 0, rank)
     gen = torch.Generator(device=device).manual_seed(seed)
@@ -246,7 +248,7 @@ def cpu_baseline_run(c: dict, sample_layers: int, sample_tokens: int, repeats: i
     Returns (keys_per_second, seconds, description).
     """
     import oracle
-    from triattention_b200 import synth
+    import synth
 
     gen = torch.Generator().manual_seed(synth.seed_for(1, 9, 0))
     D, H, g = c["D"], c["Hkv"], c["g"]

@@ -79,8 +79,9 @@ int triattn_abi_version(void);
 /* Static, human-readable text for a triattn_status. */
 const char* triattn_status_string(int status);
 
-/* Query-head slots per KV head in the raw-score layout: group_size rounded up to 1, 2, 4 or 8
- * (0 if group_size is unsupported by the fast scorer, i.e. > 8). */
+/* Query-head slots per KV head in the raw-score layout: group_size rounded up to 1, 2 or 4, and
+ * above 4 to the next multiple of 4 (the scorers split such groups into virtual heads), up to 64.
+ * Returns 0 for group_size <= 0 or > 64. */
 int triattn_padded_group(int group_size);
 
 /* Number of weight rows per (layer, request, query head): 3 for MEAN (w_re, w_im, w_mag),
@@ -184,6 +185,7 @@ int triattn_finalize_scores(const triattn_paged_layout* layout /* host */, const
  * Row r belongs to request b = (r / rows_per_req_inner) % num_reqs, has seq_lens[b] valid scores and
  * keeps keep_counts[b] of them (clamped to the row length).
  *   scores : [num_rows, row_stride] fp32;  keep_out : [num_rows, keep_pitch] int32 (tail filled with -1)
+ * A seq_lens[b] larger than row_stride is clamped to it and raises TRIATTN_DEV_BAD_LENGTH.
  * Replaces the chunked torch.topk / merge / torch.sort of selector_hf.py:990-1025 (and :604-677, :721-747).
  */
 int triattn_select_topk(const float* scores, int num_rows, int64_t row_stride, const int32_t* seq_lens,

@@ -38,9 +38,10 @@ REPO = HERE.parent.parent
 REF = Path(os.environ.get("TRIATTN_REFERENCE_ROOT", str(REPO.parent / "reference")))
 sys.dont_write_bytecode = True
 sys.path.insert(0, str(REPO))
+sys.path.insert(0, str(REPO / "tests"))
 sys.path.insert(0, str(REF))
 
-from triattention_b200 import synth  # noqa: E402
+import synth  # noqa: E402
 
 
 def sha(*tensors) -> str:

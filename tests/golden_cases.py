@@ -3,7 +3,7 @@ from __future__ import annotations
 
 import torch
 
-from triattention_b200 import synth
+import synth
 
 
 def build_paged_case(p: dict):

@@ -3,7 +3,8 @@ from __future__ import annotations
 
 import torch
 
-from triattention_b200 import _native, ops, synth
+from triattention_b200 import _native, ops
+import synth
 
 
 def device_stats(stats: synth.SyntheticStats, offsets: torch.Tensor, freq_scale_sq=None, dev="cuda") -> ops.DeviceStats:

@@ -10,7 +10,8 @@ import oracle
 from conftest import np_to_bf16, tensor_sha
 from golden_cases import build_paged_case, stats_by_layer
 from gpu_utils import device_stats, keep_sets_match_modulo_near_ties, score_tolerance_ok
-from triattention_b200 import _native, engine, hook as hook_mod, kv_compaction, ops, synth
+from triattention_b200 import _native, engine, hook as hook_mod, kv_compaction, ops
+import synth
 from triattention_b200.compressor import TriAttentionCompressor, compute_scores
 from triattention_b200.config import TriAttentionConfig, TriAttentionRuntimeConfig
 from triattention_b200.selector import build_triattention_selector

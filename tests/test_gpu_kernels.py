@@ -10,7 +10,8 @@ from conftest import np_to_bf16, tensor_sha
 from golden_cases import build_paged_case, build_real_stats_case, stats_by_layer
 from gpu_utils import (block_table_tensor, device_stats, keep_sets_match_modulo_near_ties, raw_to_reference_layout,
                        score_tolerance_ok)
-from triattention_b200 import _native, ops, synth
+from triattention_b200 import _native, ops
+import synth
 
 pytestmark = pytest.mark.gpu
 

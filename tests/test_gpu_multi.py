@@ -22,7 +22,7 @@ def _free_port() -> int:
 
 
 def _build(seed=77):
-    from triattention_b200 import synth
+    import synth
     gen = torch.Generator().manual_seed(seed)
     L, Hq, Hkv, D, bs = 2, 16, 4, 128, 16
     lens = [900, 1500]

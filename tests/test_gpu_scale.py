@@ -11,7 +11,8 @@ import torch
 
 import oracle
 from gpu_utils import device_stats, keep_sets_match_modulo_near_ties
-from triattention_b200 import engine, ops, synth
+from triattention_b200 import engine, ops
+import synth
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"

@@ -15,7 +15,8 @@ import oracle
 from conftest import tensor_sha
 from golden_cases import build_paged_case, stats_by_layer
 from triattention_b200 import hook as hook_mod
-from triattention_b200 import kv_compaction, stats as stats_mod, synth
+from triattention_b200 import kv_compaction, stats as stats_mod
+import synth
 from triattention_b200.config import TriAttentionConfig, TriAttentionRuntimeConfig
 from triattention_b200.plan_models import KeepPlan
 from triattention_b200.signals import CompressionSignal

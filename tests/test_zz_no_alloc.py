@@ -13,7 +13,8 @@ import ctypes
 import pytest
 import torch
 
-from triattention_b200 import _native, ops, synth
+from triattention_b200 import _native, ops
+import synth
 
 pytestmark = pytest.mark.gpu
 

@@ -12,6 +12,7 @@ import torch
 
 from . import _native, ops
 from .config import TriAttentionConfig
+from .rope import resolve_rope_spec
 from .stats import geometric_offsets, load_frequency_stats, resolve_omega
 
 _BS = 16
@@ -114,7 +115,10 @@ class TriAttentionCompressor:
         cfg.num_layers = cfg.num_layers or int(self.metadata["num_layers"])
         if "rope_style" in self.metadata:
             cfg.rope_style = str(self.metadata["rope_style"])
-        self.inv_freq = resolve_omega(self.metadata, cfg.head_dim, device=cfg.device)
+        # metadata.inv_freq, then a local model config under model_path, then metadata rope_theta (default 1e4)
+        spec = resolve_rope_spec(self.metadata, cfg.head_dim, model_path=cfg.model_path)
+        self.inv_freq = (spec.inv_freq.to(cfg.device) if spec is not None
+                         else resolve_omega(self.metadata, cfg.head_dim, device=cfg.device))
         self.omega = self.inv_freq
         F = cfg.head_dim // 2
         self.freq_scale_sq = torch.zeros(cfg.num_layers, cfg.num_kv_heads, F, device=cfg.device, dtype=torch.float32)

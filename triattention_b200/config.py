@@ -34,6 +34,39 @@ def _parse_path(raw: str) -> Optional[Path]:
     return Path(raw) if raw else None
 
 
+# legacy variable -> runtime variable (plugin.py:37-45)
+_LEGACY_ENV = {
+    "TRIATTENTION_KV_BUDGET": "TRIATTN_RUNTIME_KV_BUDGET",
+    "TRIATTENTION_DIVIDE_LENGTH": "TRIATTN_RUNTIME_DIVIDE_LENGTH",
+    "TRIATTENTION_WINDOW_SIZE": "TRIATTN_RUNTIME_WINDOW_SIZE",
+    "TRIATTENTION_LOG_DECISIONS": "TRIATTN_RUNTIME_LOG_DECISIONS",
+    "TRIATTENTION_STATS_PATH": "TRIATTN_RUNTIME_SPARSE_STATS_PATH",
+}
+# switches the plugin turns on unless the operator set them (plugin.py:47-51)
+_STRICT_DEFAULTS = ("ENABLE_EXPERIMENTAL_KV_COMPACTION", "ENABLE_EXPERIMENTAL_BLOCK_RECLAIM",
+                    "REQUIRE_TRITON_SCORING", "REQUIRE_PHYSICAL_RECLAIM")
+
+
+def bridge_legacy_env(environ=None) -> None:
+    """Map the older ``TRIATTENTION_*`` variables onto ``TRIATTN_RUNTIME_*`` (plugin.py:37-58).
+
+    A runtime variable that is already set (non-empty) wins; empty legacy values are ignored; the four strictness
+    switches default to ``true``; ``TRIATTENTION_PRUNING_MODE`` is lower-cased and its old spelling
+    ``per_layer_head`` becomes ``per_layer_per_head``.  Call before :meth:`TriAttentionRuntimeConfig.from_env`.
+    """
+    env = os.environ if environ is None else environ
+    for legacy, runtime in _LEGACY_ENV.items():
+        value = env.get(legacy)
+        if not env.get(runtime) and value:
+            env[runtime] = value
+    for name in _STRICT_DEFAULTS:
+        env.setdefault("TRIATTN_RUNTIME_" + name, "true")
+    if not env.get("TRIATTN_RUNTIME_PRUNING_MODE"):
+        mode = (env.get("TRIATTENTION_PRUNING_MODE") or "").strip().lower()
+        if mode:
+            env["TRIATTN_RUNTIME_PRUNING_MODE"] = "per_layer_per_head" if mode == "per_layer_head" else mode
+
+
 @dataclass
 class TriAttentionRuntimeConfig:
     """Runtime config loaded by scheduler and worker (fields and defaults of runtime/config.py:27-60)."""

@@ -74,7 +74,12 @@ __global__ void __launch_bounds__(kSelectThreads) select_topk_kernel(const __gri
 
   const int row = blockIdx.x;
   const int b = (row / p.rows_inner) % p.num_reqs;
-  const int n = p.seq_lens[b];
+  // a length beyond the row (bad metadata) is clamped and reported, like the scorer and the compaction do
+  int n = p.seq_lens[b];
+  if ((long long)n > p.row_stride) {
+    if (threadIdx.x == 0) flag_status(p.status, TRIATTN_DEV_BAD_LENGTH);
+    n = (int)p.row_stride;
+  }
   const int k = min(p.keep_counts[b], min(n, p.keep_pitch));
   const float* x = p.scores + (size_t)row * p.row_stride;
   int32_t* out = p.keep_out + (size_t)row * p.keep_pitch;

@@ -95,11 +95,12 @@ class PagedCompressor:
         if not (B == len(seq_lens) == len(round_starts) == len(budgets)) or B == 0:
             raise ValueError("block_ids, seq_lens, round_starts and budgets must be non-empty and of equal length")
         bs = view.block_size
-        for ids, n in zip(block_ids, seq_lens):
-            if num_required_blocks(int(n), bs) > len(ids):
-                raise IndexError(
-                    f"token indices require block_idx={num_required_blocks(int(n), bs) - 1}, "
-                    f"but only {len(ids)} blocks exist")
+        seq_np = np.asarray(seq_lens, dtype=np.int64)
+        need_np = np.where(seq_np > 0, (seq_np + bs - 1) // bs, 0)
+        have_np = np.fromiter((len(ids) for ids in block_ids), dtype=np.int64, count=B)
+        if (need_np > have_np).any():
+            b = int(np.argmax(need_np > have_np))
+            raise IndexError(f"token indices require block_idx={int(need_np[b]) - 1}, but only {int(have_np[b])} blocks exist")
         g, rem = divmod(self.stats.num_heads, view.num_kv_heads)
         if rem or g <= 0:
             raise RuntimeError(
@@ -107,9 +108,10 @@ class PagedCompressor:
                 f"source={self.stats.num_heads},target={view.num_kv_heads}")
         if self.stats.num_layers != view.num_layers:
             raise ValueError(f"stats cover {self.stats.num_layers} layers, the cache group has {view.num_layers}")
-        max_blocks = max(num_required_blocks(int(n), bs) for n in seq_lens)
-        keep_counts = [min(int(k), int(n)) for k, n in zip(budgets, seq_lens)]
-        keep_pitch = max(max(keep_counts), 1)
+        max_blocks = int(need_np.max())
+        kc_np = np.minimum(np.asarray(budgets, dtype=np.int64), seq_np)
+        keep_counts = kc_np.tolist()
+        keep_pitch = max(int(kc_np.max()), 1)
         layout = view.layout(B, g, max_blocks, rope_interleaved=self.stats.rope_interleaved)
         O = int(self.stats.offsets.numel())
         ws_bytes = ops.compress_workspace_bytes(layout, O, self.offset_agg, keep_pitch)
@@ -119,17 +121,22 @@ class PagedCompressor:
         self._buffers(n_ints, ws_bytes + keep_bytes + 256, view.device)
         st = self._staging[:n_ints]
         sn = st.numpy()  # the pinned staging buffer, filled through numpy (block ids may be lists or int arrays)
-        sn[:] = 0
-        bt_host = sn[: B * max_blocks].reshape(B, max_blocks)
-        for b, ids in enumerate(block_ids):
-            nb = num_required_blocks(int(seq_lens[b]), bs)
-            bt_host[b, :nb] = ids[:nb]
+        # block table: one concatenation of the used id prefixes scattered into the padded rows (no per-row writes)
+        bt_flat = sn[: B * max_blocks]
+        starts = np.cumsum(need_np) - need_np
+        total = int(need_np.sum())
+        if total == B * max_blocks:
+            bt_flat[:] = np.concatenate([np.asarray(ids[:n], dtype=np.int32) for ids, n in zip(block_ids, need_np.tolist())])
+        else:
+            bt_flat[:] = 0
+            dst = np.arange(total, dtype=np.int64) + np.repeat(np.arange(B, dtype=np.int64) * max_blocks - starts, need_np)
+            bt_flat[dst] = np.concatenate([np.asarray(ids[:n], dtype=np.int32) for ids, n in zip(block_ids, need_np.tolist())])
         off = B * max_blocks
-        sn[off : off + B] = seq_lens
+        sn[off : off + B] = seq_np
         sn[off + B : off + 2 * B] = round_starts
-        sn[off + 2 * B : off + 3 * B] = keep_counts
-        if prefill_lens is not None:
-            sn[off + 3 * B : off + 4 * B] = prefill_lens
+        sn[off + 2 * B : off + 3 * B] = kc_np
+        sn[off + 3 * B : off + 4 * B] = prefill_lens if prefill_lens is not None else 0
+        sn[off + 4 * B : n_ints] = 0
         dm = self._dev_meta[:n_ints]
         bt = dm[: B * max_blocks].view(B, max_blocks)
         d_seq = dm[off : off + B]
@@ -150,9 +157,15 @@ class PagedCompressor:
         if not self.use_cuda_graph:
             launch()
         else:
+            # everything the captured launches bake in: cache and statistics addresses, geometry, scoring switches
+            sp = self.stats
             key = (int(view.k_ptrs.data_ptr()), int(view.v_ptrs.data_ptr()), view.num_layers, view.num_blocks,
                    view.block_stride, view.token_stride, view.head_stride, B, max_blocks, keep_pitch,
-                   prefill_lens is not None, int(st.data_ptr()), int(ws.data_ptr()))
+                   prefill_lens is not None, int(st.data_ptr()), int(ws.data_ptr()),
+                   int(sp.q_mean_real.data_ptr()), int(sp.q_mean_imag.data_ptr()), int(sp.q_abs_mean.data_ptr()),
+                   int(sp.freq_scale_sq.data_ptr()), int(sp.omega.data_ptr()), int(sp.offsets.data_ptr()),
+                   bool(sp.rope_interleaved), int(self.window), bool(self.normalize), int(self.offset_agg),
+                   int(self.flags), int(self.layer_reduce))
             graph = self._graphs.get(key)
             if graph is not None:
                 graph.replay()
@@ -167,15 +180,9 @@ class PagedCompressor:
                 graph.replay()  # a capture records, it does not execute
         torch.cuda.current_stream().synchronize()
         status = int(self._status_host.item())
-        kept, removed = [], []
-        for b, ids in enumerate(block_ids):
-            req = num_required_blocks(keep_counts[b], bs)
-            if isinstance(ids, np.ndarray):
-                kept.append(ids[:req])
-                removed.append(ids[req:])
-            else:
-                kept.append([int(x) for x in ids[:req]])
-                removed.append([int(x) for x in ids[req:]])
+        req_blocks = ((kc_np + bs - 1) // bs).tolist()
+        kept = [ids[:r] if isinstance(ids, np.ndarray) else [int(x) for x in ids[:r]] for ids, r in zip(block_ids, req_blocks)]
+        removed = [ids[r:] if isinstance(ids, np.ndarray) else [int(x) for x in ids[r:]] for ids, r in zip(block_ids, req_blocks)]
         return CompressResult(keep=keep, keep_counts=keep_counts, kept_block_ids=kept, removed_block_ids=removed,
                               device_status=status, h2d_bytes=n_ints * 4, d2h_bytes=4)
 

@@ -21,7 +21,7 @@ from .kv_compaction import (build_keep_token_indices, compact_group_kv_in_place_
 from .layout_engine import num_required_blocks, truncate_tail_reclaim_group
 from .plan_models import KeepPlan, PlacementPlan, ReclaimEvent
 from .request_state import resolve_hook_request_context, scheduled_tokens_for_req
-from .selector import build_triattention_selector as _build_triattention_selector
+from .selector import FusedCompactionError, build_triattention_selector as _build_triattention_selector
 from .signals import CompressionSignal
 
 
@@ -275,6 +275,9 @@ def run_group_compaction_pipeline(*, req_id, signal, config, strict, num_compute
                     caches=[t for _, t in layer_tensors], layer_indices=[i for i, _ in layer_tensors],
                     block_ids=block_ids, total_tokens=total, prefill_len=prefill_len,
                     protect_prefill=signal.protect_prefill, round_start=round_start, budget_total=group_budget)
+            except FusedCompactionError as exc:
+                first = layer_tensors[0][0] if layer_tensors else -1
+                return {"applied": False, "reason": f"compaction_failed:g{gid}:l{first}:{type(exc).__name__}"}
             except Exception as exc:
                 raise RuntimeError(
                     f"{TRITON_SCORING_REQUIRED_MARKER}:req={req_id}:gid={gid}:global_per_head:{type(exc).__name__}") from exc
@@ -292,6 +295,7 @@ def run_group_compaction_pipeline(*, req_id, signal, config, strict, num_compute
                 return {"applied": False, "reason": "prefill_exceeds_budget"}
             raise
         group_len = int(fused_result["cache_len_after"]) if fused_result is not None else None
+        layer_lens: list = []
         try:
             bt_cache: dict = {}
             preserve = bool(getattr(config, "preserve_dropped_tokens", False))
@@ -319,13 +323,9 @@ def run_group_compaction_pipeline(*, req_id, signal, config, strict, num_compute
                     n = shared_compact_fn(kv_cache=kv_cache, block_ids=bt, block_size=block_size,
                                           keep_token_indices=plan.indices, total_tokens=total,
                                           preserve_dropped_tokens=preserve)
-                n = int(n)
+                layer_lens.append((layer_idx, int(n)))
                 if group_len is None:
-                    group_len = n
-                elif n != group_len:
-                    raise RuntimeError(
-                        f"{TRITON_SCORING_REQUIRED_MARKER}:inconsistent_cache_len_after:req={req_id}:gid={gid}:"
-                        f"layer={layer_idx}:expected={group_len}:actual={n}")
+                    group_len = int(n)
             kept_ids, removed_ids, reclaim = list(block_ids), [], None
             if config.enable_experimental_block_reclaim and group_len is not None:
                 kept_ids, removed_ids, reclaim = truncate_tail_reclaim_group(
@@ -340,6 +340,14 @@ def run_group_compaction_pipeline(*, req_id, signal, config, strict, num_compute
         except Exception as exc:
             first = tasks[0][0] if tasks else -1
             return {"applied": False, "reason": f"compaction_failed:g{gid}:l{first}:{type(exc).__name__}"}
+        # every layer of every group must end at the same length; a mismatch is fatal, not a soft
+        # compaction failure (hook_group_pipeline.py:128-135 raises it outside the try block)
+        for layer_idx, n in layer_lens:
+            expect = cache_len_after if cache_len_after is not None else group_len
+            if n != expect:
+                raise RuntimeError(
+                    f"{TRITON_SCORING_REQUIRED_MARKER}:inconsistent_cache_len_after:req={req_id}:gid={gid}:"
+                    f"layer={layer_idx}:expected={expect}:actual={n}")
         if group_len is not None:
             if cache_len_after is not None and group_len != cache_len_after:
                 raise RuntimeError(

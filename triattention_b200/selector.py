@@ -9,6 +9,7 @@ guards, group/layer reductions and top-k all happen on the device; the reference
 from __future__ import annotations
 
 import os
+import warnings
 from pathlib import Path
 from typing import Any, Callable, Iterable, Optional
 
@@ -18,7 +19,8 @@ from . import _native, ops
 from .config import TriAttentionRuntimeConfig
 from .constants import TRITON_SCORING_REQUIRED_MARKER
 from .kv_compaction import kv_axis_hint
-from .stats import geometric_offsets, load_frequency_stats, pack_device_stats, resolve_omega
+from .rope import resolve_rope_spec, rope_spec_from_parameters
+from .stats import geometric_offsets, load_frequency_stats, pack_device_stats
 
 
 def _dense_keys_view(keys_dense: torch.Tensor, block_size: int = 16):
@@ -35,6 +37,41 @@ def _dense_keys_view(keys_dense: torch.Tensor, block_size: int = 16):
                               num_kv_heads=H, head_dim=D, block_stride=buf.stride(0), token_stride=buf.stride(1),
                               head_stride=buf.stride(2), device=buf.device, dtype=buf.dtype)
     return view, list(range(nb)), buf
+
+
+class FusedCompactionError(RuntimeError):
+    """The compaction stage of the fused group call failed (scoring and selection were fine)."""
+
+
+def load_scoring_state(stats_path, config, base_runner: Any | None, strict: bool) -> dict:
+    """Statistics of ``stats_path`` plus the frequencies they are scored with (host side, no device work).
+
+    omega and the cos/sin factor of the model's rotary embedding come from the statistics metadata, else from the
+    model config the worker holds locally (the reference fetches that config by model name: core/compressor.py:119-194,
+    core/utils.py:186-297).  When nothing names them: fatal in strict mode, a warning and ``rope_theta = 10000``
+    (core/compressor.py:186-191) otherwise.
+    """
+    metadata, head_stats = load_frequency_stats(stats_path, device="cpu", dtype=torch.float32)
+    head_dim = int(metadata["head_dim"])
+    spec = resolve_rope_spec(metadata, head_dim, model_path=getattr(config, "model_path", None),
+                             base_runner=base_runner)
+    if spec is None:
+        if strict:
+            raise RuntimeError(
+                f"{TRITON_SCORING_REQUIRED_MARKER}:rope_unresolved:stats metadata has no inv_freq/rope_theta "
+                "and no local model config was found (set TRIATTN_RUNTIME_MODEL_PATH to the model directory)")
+        warnings.warn("TriAttention: rotary frequencies unresolved, falling back to rope_theta=10000; "
+                      "keep sets will be wrong for models with another base or scaled RoPE")
+        spec = rope_spec_from_parameters(head_dim, float(metadata.get("rope_theta", 10000.0)),
+                                         source="fallback.rope_theta")
+    if spec.attention_factor != 1.0 and "rkv_metadata" in metadata:
+        # converted calibration files carry freq_scale_sq = 1; the reference replaces it with the square of the
+        # rotary embedding's cos/sin factor when it can build the model's rotary (core/utils.py:253-297)
+        for rec in head_stats.values():
+            rec["freq_scale_sq"] = rec["freq_scale_sq"] * float(spec.attention_factor) ** 2
+    return dict(loaded=True, metadata=metadata, head_stats=head_stats, head_dim=head_dim, omega=spec.inv_freq,
+                rope_source=spec.source, attention_factor=spec.attention_factor, offsets=geometric_offsets(65536),
+                interleaved=str(metadata.get("rope_style", "half")) == "interleaved")
 
 
 def build_triattention_selector(
@@ -73,12 +110,10 @@ def build_triattention_selector(
 
     def _load():
         if not state["loaded"]:
-            metadata, head_stats = load_frequency_stats(stats_path, device="cpu", dtype=torch.float32)
-            head_dim = int(metadata["head_dim"])
-            state.update(loaded=True, metadata=metadata, head_stats=head_stats, head_dim=head_dim,
-                         omega=resolve_omega(metadata, head_dim), offsets=geometric_offsets(65536),
-                         interleaved=str(metadata.get("rope_style", "half")) == "interleaved")
+            state.update(load_scoring_state(stats_path, config, base_runner, strict))
         return state
+
+    _load()  # at start-up: a statistics file whose frequencies cannot be resolved must not fail mid-serving
 
     def _packed(layer_indices, device, reduce_to: Optional[int]) -> ops.DeviceStats:
         st = _load()
@@ -269,10 +304,13 @@ def build_triattention_selector(
             ids = block_ids.tolist() if isinstance(block_ids, torch.Tensor) else [int(x) for x in block_ids]
             res = comp.compress(view, [ids], [int(total_tokens)], [int(round_start)], [k],
                                 prefill_lens=[int(prefill_len)] if (protect_prefill and prefill_len > 0) else None)
-            if res.device_status:
+            if res.device_status & ~_native.DEV_BAD_KEEP_INDEX:
                 raise _native.NativeLibraryError(f"device_status:{res.device_status}")
         except _native.NativeLibraryError as exc:
             raise RuntimeError(f"{TRITON_SCORING_REQUIRED_MARKER}:score_failed:{type(exc).__name__}") from exc
+        if res.device_status:
+            # only the compaction stage reports keep-index faults: a soft failure, as in the per-layer loop
+            raise FusedCompactionError(f"device_status:{res.device_status}")
         return {
             "mode": "per_head",
             "indices": res.keep[0].long(),   # a copy: the engine reuses its output buffer
