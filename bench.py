@@ -416,7 +416,7 @@ def run_ours(args, world, rank, local):
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
         torch.cuda.synchronize()
         ev[0].record()
-        w = ops.prep_weights(stats, d_rs, agg)
+        w = ops.prep_weights_fused(stats, d_rs, agg)
         ev[1].record()
         raw, mom = ops.score_paged(view, layout, bt, d_seq, w, agg, 17, status=d_status)
         ev[2].record()
@@ -450,16 +450,15 @@ def run_ours(args, world, rank, local):
         "keys_per_s_per_gpu": value / world,
         "step_hbm_gbs": bytes_step / (step_ms * 1e-3) / 1e9, "step_hbm_frac": bytes_step / (step_ms * 1e-3) / 1e9 / peak,
         "stage_ms": stage,
-        "roofline": {"kernel": ("score_paged_mma_max_kernel" if args.aggregation == "max" else
-                                "score_paged_mean_kernel" if os.environ.get("TRIATTN_SCORE_PATH") == "fma"
-                                else "score_paged_mma_kernel"), "bound": "hbm", "achieved": achieved, "peak": peak,
+        "roofline": {"kernel": ("score_paged_mma_max_kernel" if args.aggregation == "max" else "score_paged_mma_kernel"),
+                     "bound": "hbm", "achieved": achieved, "peak": peak,
                      "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
                      "traffic": (keys_per_gpu * SCORE_DRAM_BYTES_PER_KEY_NCU
                                  if (c["D"], c["g"], c["Hkv_local"]) == (128, 4, 8) else None),
                      "traffic_note": "bytes per launch, scaled by keys from a 2-layer ncu capture of the same shape"},
         "e2e": {"value": keys_per_gpu * world / e2e_s, "unit": UNIT, "h2d_bytes_per_step": res.h2d_bytes,
                 "d2h_bytes_per_step": res.d2h_bytes, "ms_per_step": e2e_s * 1e3},
-        "gpu_launches": 7 * args.steps,
+        "gpu_launches": 5 * args.steps,
         "clocks": clocks, "device_status": status_bits | res.device_status,
     }
     if not args.no_cpu_baseline and world == 1:

@@ -25,7 +25,7 @@
 extern "C" {
 #endif
 
-#define TRIATTN_ABI_VERSION 1
+#define TRIATTN_ABI_VERSION 2
 
 typedef enum triattn_status {
   TRIATTN_OK = 0,
@@ -111,6 +111,19 @@ int triattn_prep_weights(const float* q_mean_real, const float* q_mean_imag, con
                          int num_freqs, int num_offsets, int offset_agg, int flags,
                          float* scratch, float* weights_out, void* stream);
 
+/*
+ * triattn_prep_weights in ONE launch and without scratch: each CTA evaluates the offset phases of its request
+ * into shared memory (the O x F double-precision sincos calls run in parallel) and folds a slice of the
+ * (layer, query head) rows.  weights_out is bit-identical to triattn_prep_weights.  If moments_to_clear is not
+ * NULL, the [L, B, Hq, 2] fp64 array it names is zeroed by the same launch (the scorer accumulates into it).
+ * Replaces the same reference code as triattn_prep_weights (scoring.py:258-271, :313-332, :346-356).
+ */
+int triattn_prep_weights_fused(const float* q_mean_real, const float* q_mean_imag, const float* q_abs_mean,
+                               const float* freq_scale_sq, const float* omega, const float* offsets,
+                               const int32_t* round_start, int num_layers, int num_reqs, int num_q_heads,
+                               int num_freqs, int num_offsets, int offset_agg, int flags, float* weights_out,
+                               double* moments_to_clear, void* stream);
+
 /* Capacity, in floats, of the built-in scratch of triattn_prep_weights_noalloc (256 KiB). */
 #define TRIATTN_NOALLOC_PREP_SCRATCH_FLOATS 65536
 
@@ -165,6 +178,18 @@ int triattn_score_paged(const triattn_paged_layout* layout /* host */, const voi
                         uint32_t* device_status, void* stream);
 
 /*
+ * triattn_score_paged on the CUDA cores only: every product is an fp32 FMA (fma.rn.f32x2), no operand is split
+ * into bf16 parts.  Same arguments, same outputs.  It exists as the all-fp32 cross-check of the tensor-core
+ * scorer's error budget (the parity tests run both) and covers mean aggregation with head_dim 64/128 on dense
+ * blocks; other shapes return TRIATTN_ERR_UNSUPPORTED_SHAPE.  Replaces the same reference code as
+ * triattn_score_paged.
+ */
+int triattn_score_paged_cuda_cores(const triattn_paged_layout* layout /* host */, const void* const* k_layer_ptrs,
+                                   const int32_t* block_table, const int32_t* seq_lens, const float* weights,
+                                   int offset_agg, int num_offsets, float* raw_scores, double* moments,
+                                   uint32_t* device_status, void* stream);
+
+/*
  * Turn raw scores into the scores the top-k runs on: z-normalise per (layer, query head) with the
  * unbiased streaming variance (sigma < 1e-8 -> 1), force +inf on the last `window` tokens and on
  * tokens < prefill_lens[b] (prefill_lens may be NULL), reduce the g query heads of each KV head
@@ -178,7 +203,7 @@ int triattn_score_paged(const triattn_paged_layout* layout /* host */, const voi
 int triattn_finalize_scores(const triattn_paged_layout* layout /* host */, const float* raw_scores,
                             const double* moments, const int32_t* seq_lens, const int32_t* prefill_lens,
                             int window, int normalize, int group_reduce, int head_reduce, int layer_reduce,
-                            float* mean_std_scratch /* [L,B,Hkv*g,2] fp32 */, float* scores_out, void* stream);
+                            float* scores_out, void* stream);
 
 /*
  * Per-row top-k with deterministic lowest-index tie-break; indices come out ascending.
@@ -257,15 +282,25 @@ int triattn_apply_effective_overrides(const int32_t* idx_mapping, const int32_t*
                                       int32_t* seq_lens, const int64_t* positions, int64_t* positions_out,
                                       int num_tokens, int32_t* counters, int apply, void* stream);
 
-/* Bytes of workspace triattn_compress_paged needs for this geometry. */
+/* Bytes of workspace with which triattn_compress_paged scores all layers in one launch (the raw scores of
+ * every layer, 4 * triattn_padded_group(g) bytes per key, dominate it). */
 size_t triattn_compress_workspace_bytes(const triattn_paged_layout* layout /* host */, int num_offsets,
                                         int offset_agg, int keep_pitch);
+
+/* Smallest workspace triattn_compress_paged accepts: raw scores of ONE layer at a time.  Any size between this
+ * and triattn_compress_workspace_bytes() works; the step is then cut into chunks of as many layers as fit, each
+ * scored and folded into the running per-KV-head rows before the next (results are bit-identical). */
+size_t triattn_compress_workspace_bytes_min(const triattn_paged_layout* layout /* host */, int num_offsets,
+                                            int offset_agg, int keep_pitch);
 
 /*
  * The whole default-mode step for a batch of requests in one call and no host synchronisation:
  * prep -> score -> finalize (z-norm, window/prefill guards, group max, layer mean) -> per-KV-head
  * top-k -> in-place compaction of every layer with the shared keep set.
  * keep_out [B, Hkv, keep_pitch] int32 receives the ascending keep indices.
+ * workspace_bytes selects how many layers are scored per launch (see triattn_compress_workspace_bytes_min).
+ * The launches after the first are programmatic dependents of their predecessors (each kernel starts with
+ * griddepcontrol.wait), so the tail of one kernel overlaps the launch of the next.
  * Replaces, for all requests of a step at once, select_keep_indices_for_group
  * (selector_hf.py:749-1033) followed by execute_group_compaction's per-layer calls
  * (triattention/vllm/runtime/layout_engine.py:112-139).

@@ -218,8 +218,11 @@ def select_layer_local(
     rope_style: str = "half",
     score_chunk_max_tokens: int = 4096,
     kv_axis: int | None = None,
+    return_scores: bool = False,
 ):
     """Per-layer selection (selector_hf.py:473-677): z-norm -> group reduce -> guards -> top-k.
+
+    ``return_scores=True`` returns ``(keep, scores)`` with the rows the top-k ran on (``[Hkv, T]`` or ``[1, T]``).
 
     ``mode == 'per_head'`` returns ``[Hkv, k]``; ``mode == 'shared'`` takes the
     max over heads first (:636-637) and returns ``[k]``.  ``reduce_stats``
@@ -253,5 +256,6 @@ def select_layer_local(
         z = z.masked_fill(guard.view(1, -1), float("inf"))
     k = min(int(budget_total), total_tokens)
     if mode == "shared":
-        return topk_lowest_index(z.max(dim=0).values, k)
-    return topk_lowest_index(z, k)
+        z = z.max(dim=0).values
+    keep = topk_lowest_index(z, k)
+    return (keep, z.view(-1, z.shape[-1])) if return_scores else keep

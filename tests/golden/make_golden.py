@@ -7,6 +7,9 @@ Run where a checkout of the reference is available (default: a directory
     python tests/golden/make_golden.py                       # everything
     python tests/golden/make_golden.py --only input_patch    # only input_patch_cases.npz
     python tests/golden/make_golden.py --only calibration    # only calibration_cases.npz
+    python tests/golden/make_golden.py --only bench_shapes   # only bench_shape_cases.npz (minutes of CPU time)
+    python tests/golden/make_golden.py --only shipped_stats  # only shipped_stats_cases.npz
+    python tests/golden/make_golden.py --only stats_loader   # only the stats_loader_cases entry of manifest.json
 
 The reference is imported unmodified, on CPU, with three test-side shims:
 
@@ -350,6 +353,178 @@ def gen_real_stats_case(out: dict):
                               "source": "layers 0-1 of triattention/calibration/for_aime25_experiment/qwen3_8b.pt"}
 
 
+def _reference_group_run(ref_runtime_config, build_triattention_selector, compact_fn, stats, caches, block_ids, p, td, tag):
+    """Group selector + per-layer compaction of the reference on one request; returns (keep, output hashes)."""
+    sp = Path(td) / f"{tag}.pt"
+    synth.save_stats_pt(stats, sp)
+    cfg = runtime_config(ref_runtime_config, sp, p)
+    _, sel_group, status = build_triattention_selector(cfg)
+    assert status == "enabled", status
+    T, bs = p["total_tokens"], p["block_size"]
+
+    def _iter():
+        for l, c in enumerate(caches):
+            yield l, c, block_ids, bs
+    res = sel_group(layer_inputs=None, layer_input_iter=None, layer_kv_iter=_iter, total_tokens=T, prefill_len=0,
+                    protect_prefill=False, round_start=p["round_start"], budget_total=min(p["budget"], T))
+    keep = res["indices"]
+    hashes = []
+    bt = torch.as_tensor(block_ids, dtype=torch.long)
+    for c in caches:
+        n = compact_fn(kv_cache=c, block_ids=bt, block_size=bs, keep_token_indices_per_head=keep, total_tokens=T,
+                       preserve_dropped_tokens=True)
+        assert n == min(p["budget"], T)
+        hashes.append(sha(c))
+    return keep, hashes
+
+
+def gen_bench_shape_cases(out: dict):
+    """The reference at the benchmark shapes: the single-layer configuration exactly (4096 tokens, budget 2048) and a
+    one-request x two-layer slice at the benchmark length (32768 tokens).  Keep sets and output hashes only."""
+    import triattention.vllm.runtime.config as ref_runtime_config
+    from triattention.vllm.runtime.selector_hf import build_triattention_selector
+    from triattention.vllm.runtime.kv_compaction import compact_request_kv_in_place_per_head
+
+    cases = {
+        "c0_exact": dict(seed=synth.seed_for(94, 0), num_layers=1, num_q_heads=32, num_kv_heads=8, head_dim=128,
+                         theta=1e6, total_tokens=4096, block_size=16, kv_axis=0, budget=2048, window=128,
+                         round_start=4096),
+        "c1_slice": dict(seed=synth.seed_for(94, 1), num_layers=2, num_q_heads=32, num_kv_heads=8, head_dim=128,
+                         theta=1e6, total_tokens=32768, block_size=16, kv_axis=0, budget=2048, window=128,
+                         round_start=32768),
+    }
+    arrays = {}
+    with tempfile.TemporaryDirectory() as td:
+        for name, p in cases.items():
+            stats, caches, block_ids = build_paged_case(p)
+            p["input_sha256"] = sha(stats.q_mean_real, stats.q_mean_imag, stats.q_abs_mean, *caches)
+            keep, hashes = _reference_group_run(ref_runtime_config, build_triattention_selector,
+                                                compact_request_kv_in_place_per_head, stats, caches, block_ids, p, td, name)
+            arrays[f"{name}/keep"] = keep.numpy().astype(np.int32)
+            p["cache_out_sha256"] = hashes
+    np.savez_compressed(HERE / "bench_shape_cases.npz", **arrays)
+    out["bench_shape_cases"] = {"file": "bench_shape_cases.npz", "cases": cases}
+
+
+def _stack_rkv(payload, layers, heads, key):
+    return torch.stack([torch.stack([payload["stats"][f"layer{l:02d}_head{h:02d}"][key] for h in heads])
+                        for l in layers]).float()
+
+
+def gen_shipped_stats_cases(out: dict):
+    """Shipped statistics as the stats source: all 36 layers of the Qwen3-8B file, and four layers of the head_dim-64
+    GPT-OSS file with its YaRN frequencies (built by the installed transformers from the file's own rope_scaling)."""
+    import triattention.vllm.runtime.config as ref_runtime_config
+    from triattention.vllm.runtime.selector_hf import build_triattention_selector
+    from triattention.vllm.runtime.kv_compaction import compact_request_kv_in_place_per_head
+
+    arrays, cases = {}, {}
+    with tempfile.TemporaryDirectory() as td:
+        # ---- Qwen3-8B, every layer
+        payload = torch.load(REF / "triattention/calibration/for_aime24_experiment/qwen3_8b.pt", map_location="cpu",
+                             weights_only=False)
+        L, H, D = 36, 32, 128
+        inv_freq = synth.rope_inv_freq(D, 1e6)
+        stats = synth.SyntheticStats(_stack_rkv(payload, range(L), range(H), "q_mean_real"),
+                                     _stack_rkv(payload, range(L), range(H), "q_mean_imag"),
+                                     _stack_rkv(payload, range(L), range(H), "q_abs_mean"), inv_freq, D, "half")
+        p = dict(seed=synth.seed_for(95, 0), num_layers=L, num_q_heads=H, num_kv_heads=8, head_dim=D, theta=1e6,
+                 total_tokens=1200, block_size=16, kv_axis=0, budget=512, window=128, round_start=5000)
+        _, caches, block_ids = build_paged_case(p)   # K/V and block ids from the seed; statistics from the file
+        p["input_sha256"] = sha(*caches)
+        keep, hashes = _reference_group_run(ref_runtime_config, build_triattention_selector,
+                                            compact_request_kv_in_place_per_head, stats, caches, block_ids, p, td, "qwen3")
+        arrays["qwen3_8b_all_layers/keep"] = keep.numpy().astype(np.int32)
+        for k in ("q_mean_real", "q_mean_imag", "q_abs_mean"):
+            arrays[f"qwen3_8b_all_layers/{k}"] = getattr(stats, k).numpy()
+        p["cache_out_sha256_first_last"] = [hashes[0], hashes[-1]]
+        p["source"] = "all 36 layers of triattention/calibration/for_aime24_experiment/qwen3_8b.pt"
+        cases["qwen3_8b_all_layers"] = p
+
+        # ---- GPT-OSS-120B statistics (head_dim 64, 64 query / 8 KV heads, YaRN)
+        payload = torch.load(REF / "triattention/vllm/stats/gpt_oss_120b_stats.pt", map_location="cpu", weights_only=False)
+        md = payload["metadata"]
+        from transformers import LlamaConfig
+        from transformers.modeling_rope_utils import ROPE_INIT_FUNCTIONS
+        rp = dict(md["rope_scaling"], rope_theta=float(md["rope_theta"]))
+        yarn_inv, yarn_af = ROPE_INIT_FUNCTIONS["yarn"](
+            LlamaConfig(hidden_size=64 * 64, num_attention_heads=64, head_dim=64, max_position_embeddings=131072,
+                        rope_parameters=rp), "cpu")
+        layers = [0, 11, 23, 35]
+        L, H, D = len(layers), 64, 64
+        stats = synth.SyntheticStats(_stack_rkv(payload, layers, range(H), "q_mean_real"),
+                                     _stack_rkv(payload, layers, range(H), "q_mean_imag"),
+                                     _stack_rkv(payload, layers, range(H), "q_abs_mean"), yarn_inv.float(), D, "half")
+        p = dict(seed=synth.seed_for(95, 1), num_layers=L, num_q_heads=H, num_kv_heads=8, head_dim=D,
+                 theta=float(md["rope_theta"]), total_tokens=900, block_size=16, kv_axis=0, budget=300, window=64,
+                 round_start=2000)
+        gen = torch.Generator().manual_seed(p["seed"])
+        T, bs = p["total_tokens"], p["block_size"]
+        nblk = (T + bs - 1) // bs
+        block_ids = synth.random_block_ids(nblk, nblk + 5, gen)
+        caches = []
+        for _l in range(L):
+            cache = synth.make_paged_layer(nblk + 5, bs, 8, D, kv_axis=0)
+            synth.write_tokens_to_paged(cache, 0, block_ids, bs, synth.make_rotated_keys(8, T, D, stats.inv_freq, gen),
+                                        synth.make_values(8, T, D, gen))
+            caches.append(cache)
+        p["input_sha256"] = sha(*caches)
+        p["block_ids"] = block_ids
+        keep, hashes = _reference_group_run(ref_runtime_config, build_triattention_selector,
+                                            compact_request_kv_in_place_per_head, stats, caches, block_ids, p, td, "gptoss")
+        arrays["gpt_oss_yarn/keep"] = keep.numpy().astype(np.int32)
+        arrays["gpt_oss_yarn/inv_freq"] = stats.inv_freq.numpy()
+        for k in ("q_mean_real", "q_mean_imag", "q_abs_mean"):
+            arrays[f"gpt_oss_yarn/{k}"] = getattr(stats, k).numpy()
+        p["cache_out_sha256"] = hashes
+        p["layers"] = layers
+        p["rope_scaling"] = {k: (float(v) if isinstance(v, (int, float)) and not isinstance(v, bool) else v)
+                             for k, v in md["rope_scaling"].items()}
+        p["attention_factor"] = float(yarn_af)
+        p["source"] = "layers 0, 11, 23, 35 of triattention/vllm/stats/gpt_oss_120b_stats.pt"
+        cases["gpt_oss_yarn"] = p
+    np.savez_compressed(HERE / "shipped_stats_cases.npz", **arrays)
+    out["shipped_stats_cases"] = {"file": "shipped_stats_cases.npz", "cases": cases}
+
+
+SHIPPED_STATS = [
+    "triattention/calibration/for_aime24_experiment/qwen3_8b.pt",
+    "triattention/calibration/for_aime24_experiment/ds_llama8b.pt",
+    "triattention/calibration/for_aime24_experiment/ds_qwen7b.pt",
+    "triattention/calibration/for_aime25_experiment/qwen3_8b.pt",
+    "triattention/calibration/for_aime25_experiment/ds_llama8b.pt",
+    "triattention/calibration/for_aime25_experiment/ds_qwen7b.pt",
+    "triattention/vllm/stats/gpt_oss_120b_stats.pt",
+]
+
+
+def gen_stats_loader_cases(out: dict):
+    """What the reference's own loader (core/utils.py:18-134) returns for every statistics file it ships: metadata
+    scalars and a hash of every per-layer tensor.  The Hub is unreachable here, so the loader's model-config
+    fallbacks fail and it reports no inv_freq and freq_scale_sq = 1, which is what gets recorded."""
+    from triattention.vllm.core.utils import load_frequency_stats
+
+    files = {}
+    for rel in SHIPPED_STATS:
+        for nkv in (None, 8):
+            try:
+                md, hs = load_frequency_stats(REF / rel, device=torch.device("cpu"), dtype=torch.float32, num_kv_heads=nkv)
+            except Exception as exc:  # a head count that 8 does not divide
+                files[f"{rel}|kv={nkv}"] = {"error": type(exc).__name__}
+                continue
+            rec = {"metadata": {k: md[k] for k in ("num_attention_heads", "num_kv_heads", "head_dim", "num_layers",
+                                                   "rope_style", "rope_type", "gqa_ratio") if k in md},
+                   "rope_theta": float(md.get("rope_theta", 0.0)), "has_inv_freq": "inv_freq" in md,
+                   "layers": sorted(int(l) for l in hs)}
+            h = hashlib.sha256()
+            for l in sorted(hs):
+                for key in ("q_mean_complex", "q_abs_mean", "freq_scale_sq"):
+                    h.update(hs[l][key].contiguous().numpy().tobytes())
+            rec["tensors_sha256"] = h.hexdigest()
+            files[f"{rel}|kv={nkv}"] = rec
+    out["stats_loader_cases"] = {"files": files}
+
+
 def gen_hook_cases(out: dict):
     """The reference's runner hook (hook_impl.py) driven on CPU with a fake runner: result dicts, block tables, caches."""
     import types
@@ -493,15 +668,22 @@ def gen_calibration_cases(out: dict):
     out["calibration_cases"] = {"file": "calibration_cases.npz", "cases": cases}
 
 
+PARTIAL = {
+    # --only <name>: regenerate one group of fixtures and merge it into manifest.json
+    "calibration": lambda out: gen_calibration_cases(out),
+    "input_patch": lambda out: gen_input_patch_cases(out),
+    "bench_shapes": lambda out: gen_bench_shape_cases(out),
+    "shipped_stats": lambda out: gen_shipped_stats_cases(out),
+    "stats_loader": lambda out: gen_stats_loader_cases(out),
+}
+
+
 def main():
-    if len(sys.argv) > 2 and sys.argv[1] == "--only" and sys.argv[2] == "calibration":
+    if len(sys.argv) > 2 and sys.argv[1] == "--only":
         out = json.loads((HERE / "manifest.json").read_text())
-        gen_calibration_cases(out)
-        (HERE / "manifest.json").write_text(json.dumps(out, indent=1, sort_keys=True))
-        return
-    if len(sys.argv) > 2 and sys.argv[1] == "--only" and sys.argv[2] == "input_patch":
-        out = json.loads((HERE / "manifest.json").read_text())
-        gen_input_patch_cases(out)
+        if sys.argv[2] in ("bench_shapes", "shipped_stats"):
+            install_shims()
+        PARTIAL[sys.argv[2]](out)
         (HERE / "manifest.json").write_text(json.dumps(out, indent=1, sort_keys=True))
         return
     ref_scoring, ref_config = install_shims()
@@ -509,6 +691,9 @@ def main():
     gen_score_cases(ref_scoring, ref_config, out)
     gen_selector_cases(out)
     gen_real_stats_case(out)
+    gen_bench_shape_cases(out)
+    gen_shipped_stats_cases(out)
+    gen_stats_loader_cases(out)
     gen_hook_cases(out)
     gen_input_patch_cases(out)
     gen_calibration_cases(out)

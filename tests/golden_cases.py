@@ -64,3 +64,20 @@ def stats_by_layer(stats: synth.SyntheticStats, freq_scale_sq=None) -> dict:
             "freq_scale_sq": fs,
         }
     return out
+
+
+def build_stats_case(p: dict, inv_freq: torch.Tensor):
+    """(per-layer paged caches, block ids) of a fixture whose statistics come from a file: K/V and the block order are
+    drawn from the seed alone."""
+    gen = torch.Generator().manual_seed(int(p["seed"]))
+    T, bs = p["total_tokens"], p["block_size"]
+    nblk = (T + bs - 1) // bs
+    block_ids = synth.random_block_ids(nblk, nblk + 5, gen)
+    caches = []
+    for _l in range(p["num_layers"]):
+        cache = synth.make_paged_layer(nblk + 5, bs, p["num_kv_heads"], p["head_dim"], kv_axis=0)
+        synth.write_tokens_to_paged(cache, 0, block_ids, bs,
+                                    synth.make_rotated_keys(p["num_kv_heads"], T, p["head_dim"], inv_freq, gen),
+                                    synth.make_values(p["num_kv_heads"], T, p["head_dim"], gen))
+        caches.append(cache)
+    return caches, block_ids

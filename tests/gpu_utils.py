@@ -40,7 +40,8 @@ def score_tolerance_ok(got: torch.Tensor, ref: torch.Tensor, rtol: float = 1e-3)
 
 def keep_sets_match_modulo_near_ties(keep: torch.Tensor, ref_keep: torch.Tensor, ref_scores: torch.Tensor,
                                      rtol: float = 1e-3):
-    """Rows equal as sets except for indices whose reference score is within rtol*sigma of the cut-off.
+    """Rows equal as sets except for indices whose reference score is within rtol*sigma_row of the cut-off
+    (the k-th largest reference score), the tie window of the score contract.
 
     Returns (ok, number_of_differing_indices).
     """
@@ -56,6 +57,6 @@ def keep_sets_match_modulo_near_ties(keep: torch.Tensor, ref_keep: torch.Tensor,
         cutoff = float(row[ref_keep[r]].min())
         for idx in a ^ b:
             diff_total += 1
-            if abs(float(row[idx]) - cutoff) > rtol * max(sigma, 1e-6) * 4:
+            if abs(float(row[idx]) - cutoff) > rtol * max(sigma, 1e-6):
                 return False, diff_total
     return True, diff_total

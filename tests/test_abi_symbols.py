@@ -29,9 +29,9 @@ def test_library_builds_and_exports_every_declared_symbol():
 
 def test_host_only_queries():
     lib = _native.load()
-    assert lib.triattn_abi_version() == 1
+    assert lib.triattn_abi_version() == _native.ABI_VERSION == 2
     assert _native.status_string(0) == "ok"
-    assert [lib.triattn_padded_group(g) for g in (1, 2, 3, 4, 5, 7, 8, 9, 16, 65)] == [1, 2, 4, 4, 8, 8, 8, 12, 16, 0]
+    assert [lib.triattn_padded_group(g) for g in (0, 1, 2, 3, 4, 5, 7, 8, 9, 12, 16, 64, 65)] == [0, 1, 2, 4, 4, 8, 8, 8, 12, 12, 16, 64, 0]
     assert lib.triattn_weight_rows(_native.OFFSETS_MEAN, 17) == 3
     assert lib.triattn_weight_rows(_native.OFFSETS_MAX, 17) == 35
     assert lib.triattn_prep_scratch_floats(8, 64, 17, _native.OFFSETS_MEAN) == 8 * 2 * 64
@@ -41,6 +41,8 @@ def test_host_only_queries():
     ws = lib.triattn_compress_workspace_bytes(ctypes.byref(lay), 17, 0, 2048)
     raw_bytes = 36 * 8 * 8 * 32768 * 4 * 4
     assert raw_bytes < ws < raw_bytes * 1.1
+    ws_min = lib.triattn_compress_workspace_bytes_min(ctypes.byref(lay), 17, 0, 2048)
+    assert ws - ws_min == raw_bytes // 36 * 35 and raw_bytes // 36 < ws_min < raw_bytes // 36 + 32 * 2 ** 20
     assert lib.triattn_compact_preserve_scratch_bytes(ctypes.byref(lay), 100) == 25600 * 2 * 36 * 8 * 8
     bad = _native.PagedLayout(num_layers=0)
     assert lib.triattn_compress_workspace_bytes(ctypes.byref(bad), 17, 0, 2048) == 0

@@ -95,14 +95,14 @@ def test_layer_local_selector_modes(manifest, selector_cases, tmp_path, name, mo
         assert res["mode"] == mode
         ref_keep = torch.from_numpy(selector_cases[f"{name}/keep_l{l}"]).long()
         got = res["indices"].cpu()
-        same = set(got.flatten().tolist()) == set(ref_keep.flatten().tolist()) if mode == "shared" else None
-        if mode == "shared":
-            diff = set(got.tolist()) ^ set(ref_keep.tolist())
-            assert len(diff) <= 4, diff   # near-ties at the cut-off only
-        else:
-            for h in range(got.shape[0]):
-                diff = set(got[h].tolist()) ^ set(ref_keep[h].tolist())
-                assert len(diff) <= 4, (h, diff)
+        # any index that differs from the reference's keep set must be a near-tie at the cut-off (1e-3 sigma_row)
+        _, ref_rows = oracle.select_layer_local(
+            c, block_ids, bs, sl[l], stats.inv_freq, oracle.geometric_offsets(), T, p["round_start"], p["budget"],
+            mode=mode, group_agg="mean" if name == "plph_mean" else "max", reduce_stats=name != "plph_mean",
+            window_size=p["window"], kv_axis=p["kv_axis"], return_scores=True)
+        ok, nd = keep_sets_match_modulo_near_ties(got.view(ref_rows.shape[0], -1), ref_keep.view(ref_rows.shape[0], -1),
+                                                  ref_rows)
+        assert ok, (l, nd)
         # compaction through the mirrored API, whole region equal to the checker with the same keep set
         exp = c.clone()
         if mode == "shared":

@@ -30,7 +30,7 @@ def _oracle_kwargs(p):
         rope_style=p.get("rope_style", "half"), kv_axis=p["kv_axis"])
 
 
-def _run_stages(p, stats, caches, block_ids):
+def _run_stages(p, stats, caches, block_ids, cuda_cores=False):
     """prep -> score -> finalize -> select on the device for one request; returns the intermediate tensors."""
     dev = "cuda"
     T, bs = p["total_tokens"], p["block_size"]
@@ -45,7 +45,12 @@ def _run_stages(p, stats, caches, block_ids):
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     flags = (_native.FLAG_DISABLE_MLR if p.get("disable_mlr") else 0) | (_native.FLAG_DISABLE_TRIG if p.get("disable_trig") else 0)
     w = ops.prep_weights(dstats, rs, _agg(p), flags)
-    raw, mom = ops.score_paged(view, layout, bt, seq, w, _agg(p), 17, status)
+    try:
+        raw, mom = ops.score_paged(view, layout, bt, seq, w, _agg(p), 17, status, cuda_cores=cuda_cores)
+    except _native.NativeLibraryError as exc:
+        if cuda_cores and "unsupported shape" in str(exc):
+            pytest.skip("case outside the CUDA-core cross-check scorer (max aggregation or a generic geometry)")
+        raise
     pre = None
     if p.get("protect_prefill"):
         pre = torch.tensor([p.get("prefill_len", 0)], dtype=torch.int32, device=dev)
@@ -61,9 +66,8 @@ def _run_stages(p, stats, caches, block_ids):
 
 @pytest.mark.parametrize("score_path", ["mma", "fma"])
 @pytest.mark.parametrize("name", GROUP_CASES)
-def test_score_finalize_select_compact_vs_checker(manifest, selector_cases, name, score_path, monkeypatch):
-    # both streaming scorers (tensor-core default, CUDA-core variant) against the same checker and fixtures
-    monkeypatch.setenv("TRIATTN_SCORE_PATH", score_path)
+def test_score_finalize_select_compact_vs_checker(manifest, selector_cases, name, score_path):
+    # both streaming scorers (tensor-core default, CUDA-core cross-check) against the same checker and fixtures
     p = manifest["selector_cases"]["cases"][name]
     stats, caches, block_ids = build_paged_case(p)
     assert tensor_sha(stats.q_mean_real, stats.q_mean_imag, stats.q_abs_mean, *caches) == p["input_sha256"]
@@ -72,7 +76,7 @@ def test_score_finalize_select_compact_vs_checker(manifest, selector_cases, name
     ref_final, ref_raws = oracle.final_scores_group_per_head(
         layers, stats_by_layer(stats), stats.inv_freq, oracle.geometric_offsets(), T, p["round_start"],
         return_raw=True, **_oracle_kwargs(p))
-    out = _run_stages(p, stats, caches, block_ids)
+    out = _run_stages(p, stats, caches, block_ids, cuda_cores=score_path == "fma")
 
     # raw scores: |delta| / max(|ref|, sigma_row) <= 1e-3
     got_raw = raw_to_reference_layout(out["raw"], out["g"], T)[:, 0].cpu()

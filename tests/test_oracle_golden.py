@@ -166,3 +166,112 @@ def test_truncate_and_fallback():
     assert oracle.fallback_keep_indices(10, 4, 2, True) == [0, 1, 8, 9]
     assert oracle.fallback_keep_indices(10, 4, 5, True) is None
     assert oracle.fallback_keep_indices(3, 4, 0, False) == [0, 1, 2]
+
+
+# ------------------------------------------------------------------------------------------ benchmark shapes
+@pytest.fixture(scope="module")
+def bench_shape_cases():
+    import numpy as np
+    from conftest import GOLDEN
+    return np.load(GOLDEN / "bench_shape_cases.npz")
+
+
+@pytest.fixture(scope="module")
+def shipped_stats_cases():
+    import numpy as np
+    from conftest import GOLDEN
+    return np.load(GOLDEN / "shipped_stats_cases.npz")
+
+
+@pytest.mark.parametrize("name", ["c0_exact", "c1_slice"])
+def test_checker_matches_reference_at_benchmark_shapes(manifest, bench_shape_cases, name):
+    """The single-layer configuration exactly (4096 tokens, budget 2048) and a 32768-token, two-layer slice: the
+    checker's keep sets and compacted caches equal the reference's own outputs."""
+    p = manifest["bench_shape_cases"]["cases"][name]
+    stats, caches, block_ids = build_paged_case(p)
+    assert tensor_sha(stats.q_mean_real, stats.q_mean_imag, stats.q_abs_mean, *caches) == p["input_sha256"]
+    T, bs = p["total_tokens"], p["block_size"]
+    layers = [(l, c, block_ids, bs) for l, c in enumerate(caches)]
+    keep = oracle.select_group_per_head(layers, stats_by_layer(stats), stats.inv_freq, oracle.geometric_offsets(), T,
+                                        p["round_start"], p["budget"], window_size=p["window"], kv_axis=p["kv_axis"])
+    assert torch.equal(keep, torch.from_numpy(bench_shape_cases[f"{name}/keep"]).long())
+    for l, c in enumerate(caches):
+        oracle.compact_per_head(c, block_ids, bs, keep, T, kv_axis=p["kv_axis"])
+        assert tensor_sha(c) == p["cache_out_sha256"][l]
+
+
+def test_checker_matches_reference_on_all_layers_of_shipped_qwen3_stats(manifest, shipped_stats_cases):
+    import synth
+    p = manifest["shipped_stats_cases"]["cases"]["qwen3_8b_all_layers"]
+    _, caches, block_ids = build_paged_case(p)
+    assert tensor_sha(*caches) == p["input_sha256"]
+    z = shipped_stats_cases
+    stats = synth.SyntheticStats(torch.from_numpy(z["qwen3_8b_all_layers/q_mean_real"]),
+                                 torch.from_numpy(z["qwen3_8b_all_layers/q_mean_imag"]),
+                                 torch.from_numpy(z["qwen3_8b_all_layers/q_abs_mean"]),
+                                 synth.rope_inv_freq(128, 1e6), 128, "half")
+    T, bs = p["total_tokens"], p["block_size"]
+    layers = [(l, c, block_ids, bs) for l, c in enumerate(caches)]
+    keep = oracle.select_group_per_head(layers, stats_by_layer(stats), stats.inv_freq, oracle.geometric_offsets(), T,
+                                        p["round_start"], p["budget"], window_size=p["window"], kv_axis=0)
+    assert torch.equal(keep, torch.from_numpy(z["qwen3_8b_all_layers/keep"]).long())
+    for l, want in ((0, p["cache_out_sha256_first_last"][0]), (len(caches) - 1, p["cache_out_sha256_first_last"][1])):
+        oracle.compact_per_head(caches[l], block_ids, bs, keep, T, kv_axis=0)
+        assert tensor_sha(caches[l]) == want
+
+
+def test_checker_matches_reference_on_gpt_oss_yarn_stats(manifest, shipped_stats_cases):
+    """head_dim 64, 8 query heads per KV head, YaRN frequencies: the product's own frequency formulas reproduce the
+    inv_freq the fixture was generated with, and the checker reproduces the reference's keep set."""
+    import synth
+    from triattention_b200 import rope
+    p = manifest["shipped_stats_cases"]["cases"]["gpt_oss_yarn"]
+    z = shipped_stats_cases
+    inv = torch.from_numpy(z["gpt_oss_yarn/inv_freq"])
+    spec = rope.rope_spec_from_parameters(64, p["theta"], p["rope_scaling"])
+    assert torch.equal(spec.inv_freq, inv) and spec.attention_factor == pytest.approx(p["attention_factor"])
+    stats = synth.SyntheticStats(torch.from_numpy(z["gpt_oss_yarn/q_mean_real"]), torch.from_numpy(z["gpt_oss_yarn/q_mean_imag"]),
+                                 torch.from_numpy(z["gpt_oss_yarn/q_abs_mean"]), inv, 64, "half")
+    from golden_cases import build_stats_case
+    caches, block_ids = build_stats_case(p, inv)
+    assert tensor_sha(*caches) == p["input_sha256"] and block_ids == p["block_ids"]
+    T, bs = p["total_tokens"], p["block_size"]
+    layers = [(l, c, block_ids, bs) for l, c in enumerate(caches)]
+    keep = oracle.select_group_per_head(layers, stats_by_layer(stats), inv, oracle.geometric_offsets(), T,
+                                        p["round_start"], p["budget"], window_size=p["window"], kv_axis=0)
+    assert torch.equal(keep, torch.from_numpy(z["gpt_oss_yarn/keep"]).long())
+    for l, c in enumerate(caches):
+        oracle.compact_per_head(c, block_ids, bs, keep, T, kv_axis=0)
+        assert tensor_sha(c) == p["cache_out_sha256"][l]
+
+
+def test_stats_loader_reproduces_the_reference_loader_on_shipped_files(manifest):
+    """Every statistics file the reference ships, through this package's loader: metadata scalars and a hash over all
+    per-layer tensors equal what the reference's own loader returned when the fixture was generated.  Needs the
+    reference checkout for the files themselves (skipped where it is absent)."""
+    import hashlib
+    import os
+    from pathlib import Path
+    from conftest import REPO
+    from triattention_b200 import stats as stats_mod
+    ref_root = Path(os.environ.get("TRIATTN_REFERENCE_ROOT", str(REPO.parent / "reference")))
+    files = manifest["stats_loader_cases"]["files"]
+    if not all((ref_root / k.split("|")[0]).exists() for k in files):
+        pytest.skip("statistics files of the reference checkout not present")
+    for key, want in files.items():
+        rel, kv = key.split("|kv=")
+        nkv = None if kv == "None" else int(kv)
+        if "error" in want:
+            with pytest.raises(Exception):
+                stats_mod.load_frequency_stats(ref_root / rel, num_kv_heads=nkv)
+            continue
+        md, hs = stats_mod.load_frequency_stats(ref_root / rel, num_kv_heads=nkv)
+        for k, v in want["metadata"].items():
+            assert md[k] == v, (key, k)
+        assert float(md.get("rope_theta", 0.0)) == want["rope_theta"] and ("inv_freq" in md) == want["has_inv_freq"]
+        assert sorted(int(l) for l in hs) == want["layers"]
+        h = hashlib.sha256()
+        for l in sorted(hs):
+            for name in ("q_mean_complex", "q_abs_mean", "freq_scale_sq"):
+                h.update(hs[l][name].contiguous().numpy().tobytes())
+        assert h.hexdigest() == want["tensors_sha256"], key

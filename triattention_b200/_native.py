@@ -17,6 +17,7 @@ LIB_NAME = "libtriattn_b200.so"
 LIB_PATH = Path(os.environ.get("TRIATTN_B200_LIB") or (Path(__file__).resolve().parent / LIB_NAME))
 
 OK = 0
+ABI_VERSION = 2
 ERR_LIMIT_EXCEEDED = 6
 NOALLOC_PREP_SCRATCH_FLOATS = 65536
 OFFSETS_MEAN, OFFSETS_MAX = 0, 1
@@ -32,14 +33,17 @@ EXPORTED_SYMBOLS = (
     "triattn_weight_rows",
     "triattn_prep_scratch_floats",
     "triattn_prep_weights",
+    "triattn_prep_weights_fused",
     "triattn_prep_weights_noalloc",
     "triattn_score_paged",
+    "triattn_score_paged_cuda_cores",
     "triattn_finalize_scores",
     "triattn_select_topk",
     "triattn_compact_paged",
     "triattn_compact_preserve_scratch_bytes",
     "triattn_compact_paged_preserve",
     "triattn_compress_workspace_bytes",
+    "triattn_compress_workspace_bytes_min",
     "triattn_compress_paged",
     "triattn_rewrite_block_tables",
     "triattn_apply_effective_overrides",
@@ -90,10 +94,14 @@ def _declare(lib) -> None:
     lib.triattn_prep_weights.argtypes = [P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, P, P]
     lib.triattn_prep_weights_noalloc.restype = c_int
     lib.triattn_prep_weights_noalloc.argtypes = [P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, P]
+    lib.triattn_prep_weights_fused.restype = c_int
+    lib.triattn_prep_weights_fused.argtypes = [P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, P, P]
     lib.triattn_score_paged.restype = c_int
     lib.triattn_score_paged.argtypes = [LP, P, P, P, P, c_int, c_int, P, P, P, P]
+    lib.triattn_score_paged_cuda_cores.restype = c_int
+    lib.triattn_score_paged_cuda_cores.argtypes = [LP, P, P, P, P, c_int, c_int, P, P, P, P]
     lib.triattn_finalize_scores.restype = c_int
-    lib.triattn_finalize_scores.argtypes = [LP, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, P, P]
+    lib.triattn_finalize_scores.argtypes = [LP, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, P]
     lib.triattn_select_topk.restype = c_int
     lib.triattn_select_topk.argtypes = [P, c_int, c_int64, P, P, c_int, c_int, P, c_int, P, P]
     lib.triattn_compact_paged.restype = c_int
@@ -105,6 +113,8 @@ def _declare(lib) -> None:
                                                    c_size_t, P, P]
     lib.triattn_compress_workspace_bytes.restype = c_size_t
     lib.triattn_compress_workspace_bytes.argtypes = [LP, c_int, c_int, c_int]
+    lib.triattn_compress_workspace_bytes_min.restype = c_size_t
+    lib.triattn_compress_workspace_bytes_min.argtypes = [LP, c_int, c_int, c_int]
     lib.triattn_compress_paged.restype = c_int
     lib.triattn_compress_paged.argtypes = [LP, P, P, P, P, P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int,
                                            c_int, c_int, P, c_size_t, P, c_int, P, P]
@@ -129,7 +139,7 @@ def load():
     if missing:
         raise NativeLibraryError(f"{TRITON_SCORING_REQUIRED_MARKER}:native_symbols_missing:{missing}")
     _declare(lib)
-    if lib.triattn_abi_version() != 1:
+    if lib.triattn_abi_version() != ABI_VERSION:
         raise NativeLibraryError(f"{TRITON_SCORING_REQUIRED_MARKER}:native_abi_mismatch:{lib.triattn_abi_version()}")
     _lib = lib
     return lib

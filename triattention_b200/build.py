@@ -35,18 +35,29 @@ def find_nvcc() -> str:
     return cand
 
 
-def is_stale() -> bool:
-    if not LIB_PATH.exists():
+# Test-only variant: every bounded wait gives up after about a millisecond and every barrier expects 16 bytes
+# more than are ever copied, so the wait-timeout path runs (after all real copies have landed) without any fault.
+SHORT_WAIT_LIB_PATH = PKG_DIR.parent / "tests" / "_build" / "libtriattn_b200_shortwait.so"
+
+
+def is_stale(lib_path: Path = LIB_PATH) -> bool:
+    if not lib_path.exists():
         return True
-    built = LIB_PATH.stat().st_mtime
+    built = lib_path.stat().st_mtime
     return any((CSRC / f).resolve().stat().st_mtime > built for f in SOURCES + HEADERS)
 
 
-def build_library(force: bool = False, verbose: bool = False) -> Path:
-    """Compile the CUDA sources into ``libtriattn_b200.so`` (skipped when up to date)."""
-    if not force and not is_stale():
-        return LIB_PATH
-    cmd = [find_nvcc(), *NVCC_FLAGS, "-o", str(LIB_PATH), *[str(CSRC / s) for s in SOURCES]]
+def build_library(force: bool = False, verbose: bool = False, short_wait: bool = False) -> Path:
+    """Compile the CUDA sources into ``libtriattn_b200.so`` (skipped when up to date).
+
+    ``short_wait=True`` builds the test-only variant ``tests/_build/libtriattn_b200_shortwait.so`` instead.
+    """
+    lib_path = SHORT_WAIT_LIB_PATH if short_wait else LIB_PATH
+    if not force and not is_stale(lib_path):
+        return lib_path
+    lib_path.parent.mkdir(parents=True, exist_ok=True)
+    cmd = [find_nvcc(), *NVCC_FLAGS, *(["-DTRIATTN_TEST_SHORT_WAIT"] if short_wait else []), "-o", str(lib_path),
+           *[str(CSRC / s) for s in SOURCES]]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
@@ -55,9 +66,9 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
         raise RuntimeError(f"nvcc failed ({res.returncode}):\n{res.stdout}\n{res.stderr}")
     if verbose:
         sys.stderr.write(res.stderr)
-    return LIB_PATH
+    return lib_path
 
 
 if __name__ == "__main__":
-    path = build_library(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    path = build_library(force="--force" in sys.argv, verbose="-v" in sys.argv, short_wait="--short-wait" in sys.argv)
     print(path)

@@ -8,6 +8,7 @@
 #include <cstdint>
 #include <cstdlib>
 #include <mutex>
+#include <utility>
 
 #include "../../include/triattn_b200.h"
 #include "common.cuh"
@@ -29,15 +30,25 @@ namespace {
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
-// tuning knob read from the environment (unset or unparsable -> the built-in choice)
-int env_int(const char* name, int fallback, int lo, int hi) {
-  const char* v = std::getenv(name);
-  if (v == nullptr || *v == 0) return fallback;
-  const long x = std::strtol(v, nullptr, 10);
-  return (x < lo || x > hi) ? fallback : (int)x;
-}
-
 int check_launch() { return cudaGetLastError() == cudaSuccess ? TRIATTN_OK : TRIATTN_ERR_CUDA; }
+
+// Kernel launch, optionally as a programmatic dependent of the preceding kernel in the stream: the launch is
+// processed and its CTAs become resident while that kernel drains (every kernel of this library starts with
+// griddepcontrol.wait, so nothing is read or written before the predecessor has completed).
+template <typename... KArgs, typename... Args>
+int launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...) == cudaSuccess ? TRIATTN_OK : TRIATTN_ERR_CUDA;
+}
 
 // Opt a kernel in to `smem` bytes of dynamic shared memory; the attribute call is made only when a device has
 // not yet been raised to that size for this kernel.
@@ -73,12 +84,11 @@ bool block_is_dense(const triattn_paged_layout* L) {
 }
 
 template <int D, bool IL>
-int launch_score_fma(const ScoreParams& p, int gp, dim3 grid, size_t smem, cudaStream_t st) {
+int launch_score_fma(const ScoreParams& p, int gp, dim3 grid, size_t smem, cudaStream_t st, bool pdl) {
 #define TRIATTN_LAUNCH(GP)                                                                                  \
   {                                                                                                         \
     if (!ensure_dynamic_smem<score_paged_mean_kernel<D, GP, IL>>(smem)) return TRIATTN_ERR_CUDA;             \
-    score_paged_mean_kernel<D, GP, IL><<<grid, kScoreThreadsWS, smem, st>>>(p);                             \
-    return check_launch();                                                                                  \
+    return launch_kernel(score_paged_mean_kernel<D, GP, IL>, grid, dim3(kScoreThreadsWS), smem, st, pdl, p); \
   }
   switch (gp) {
     case 1: TRIATTN_LAUNCH(1)
@@ -89,24 +99,34 @@ int launch_score_fma(const ScoreParams& p, int gp, dim3 grid, size_t smem, cudaS
 #undef TRIATTN_LAUNCH
 }
 
-// TRIATTN_SCORE_PATH=fma selects the CUDA-core streaming kernel (no tensor cores); anything else the default.
-bool score_path_is_fma() {
-  const char* v = std::getenv("TRIATTN_SCORE_PATH");
-  return v != nullptr && v[0] == 'f' && v[1] == 'm' && v[2] == 'a' && v[3] == 0;
-}
-
 template <int D, bool IL>
-int launch_score_mma(const ScoreParams& p, dim3 grid, size_t smem, cudaStream_t st) {
+int launch_score_mma(const ScoreParams& p, dim3 grid, size_t smem, cudaStream_t st, bool pdl) {
 #define TRIATTN_LAUNCH(NT)                                                                                  \
   {                                                                                                         \
     if (!ensure_dynamic_smem<score_paged_mma_kernel<D, IL, NT>>(smem)) return TRIATTN_ERR_CUDA;              \
-    score_paged_mma_kernel<D, IL, NT><<<grid, kScoreThreadsWS, smem, st>>>(p);                              \
-    return check_launch();                                                                                  \
+    return launch_kernel(score_paged_mma_kernel<D, IL, NT>, grid, dim3(kScoreThreadsWS), smem, st, pdl, p);  \
   }
   if (p.gp_total <= 4) TRIATTN_LAUNCH(1)
   TRIATTN_LAUNCH(2)
 #undef TRIATTN_LAUNCH
 }
+
+// How an internal stage is launched: after the preceding kernel as a programmatic dependent or in plain stream
+// order; the scorer can leave the clearing of the moments to whoever ran before it.
+struct StageOpts {
+  bool pdl = false;
+  bool cuda_core_scorer = false;  // the all-fp32 CUDA-core scorer instead of the tensor-core one
+  bool moments_cleared = false;   // moments already zero: skip the memset
+};
+
+int score_paged_impl(const triattn_paged_layout* layout, const void* const* k_layer_ptrs, const int32_t* block_table,
+                     const int32_t* seq_lens, const float* weights, int offset_agg, int num_offsets,
+                     float* raw_scores, double* moments, uint32_t* device_status, cudaStream_t st,
+                     const StageOpts& opt);
+int finalize_scores_impl(const triattn_paged_layout* layout, const float* raw_scores, const double* moments,
+                         const int32_t* seq_lens, const int32_t* prefill_lens, int window, int normalize,
+                         int group_reduce, int head_reduce, int layer_reduce, int l_total, bool first_chunk,
+                         bool last_chunk, float* scores_out, cudaStream_t st, bool pdl);
 
 }  // namespace
 
@@ -207,206 +227,32 @@ int triattn_prep_weights_noalloc(const float* q_mean_real, const float* q_mean_i
 int triattn_score_paged(const triattn_paged_layout* layout, const void* const* k_layer_ptrs,
                         const int32_t* block_table, const int32_t* seq_lens, const float* weights, int offset_agg,
                         int num_offsets, float* raw_scores, double* moments, uint32_t* device_status, void* stream) {
-  int rc = validate_layout(layout);
-  if (rc != TRIATTN_OK) return rc;
-  if (!k_layer_ptrs || !block_table || !seq_lens || !weights || !raw_scores || !moments)
-    return TRIATTN_ERR_INVALID_ARGUMENT;
-  const triattn_paged_layout& Y = *layout;
-  const int gp = triattn_padded_group(Y.group_size);
-  if (gp == 0) return TRIATTN_ERR_UNSUPPORTED_SHAPE;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int Hq = Y.num_kv_heads * Y.group_size;
-  if (cudaMemsetAsync(moments, 0, sizeof(double) * 2 * (size_t)Y.num_layers * Y.num_reqs * Hq, st) != cudaSuccess)
-    return TRIATTN_ERR_CUDA;
+  return score_paged_impl(layout, k_layer_ptrs, block_table, seq_lens, weights, offset_agg, num_offsets, raw_scores,
+                          moments, device_status, static_cast<cudaStream_t>(stream), StageOpts{});
+}
 
-  ScoreParams p{};
-  p.k_ptrs = k_layer_ptrs;
-  p.block_table = block_table;
-  p.seq_lens = seq_lens;
-  p.weights = weights;
-  p.raw = raw_scores;
-  p.moments = moments;
-  p.status = device_status;
-  p.L = Y.num_layers;
-  p.B = Y.num_reqs;
-  p.Hkv = Y.num_kv_heads;
-  p.g = Y.group_size;
-  p.bs = Y.block_size;
-  p.num_blocks = Y.num_blocks;
-  p.max_blocks = Y.max_blocks_per_req;
-  p.t_pad = Y.max_blocks_per_req * Y.block_size;
-  p.block_stride_bytes = (long long)Y.block_stride * 2;
-  p.token_stride = (int)Y.token_stride;
-  p.head_stride = (int)Y.head_stride;
-  p.num_offsets = num_offsets;
-  p.agg_max = offset_agg == TRIATTN_OFFSETS_MAX ? 1 : 0;
-
-  const long long block_bytes = (long long)Y.block_size * Y.num_kv_heads * Y.head_dim * 2;
-  p.gp_total = gp;
-  const bool nhd = Y.head_stride == Y.head_dim && Y.token_stride == (int64_t)Y.num_kv_heads * Y.head_dim;
-  p.nhd = nhd ? 1 : 0;
-  // Streaming tensor-core kernel: mean aggregation, head_dim 64/128, K region of a block one dense run.
-  const bool streamable = !p.agg_max && (Y.head_dim == 64 || Y.head_dim == 128) && block_is_dense(layout) &&
-                          block_bytes <= 64 * 1024 && (block_bytes % 16) == 0 && (p.block_stride_bytes % 16) == 0;
-  if (streamable) {
-    // cache blocks per pipeline stage: a power of two filling ~32 KB (8 work items of 16 keys for 8 KV heads)
-    int mb = 1;
-    while ((mb * 2) * block_bytes <= 32 * 1024) mb *= 2;
-    mb = env_int("TRIATTN_SCORE_MB", mb, 1, 64);
-    while (mb > 1 && (long long)mb * block_bytes > 96 * 1024) mb /= 2;
-    const long long stage_bytes = (long long)mb * block_bytes;
-    // two CTAs per SM share ~200 KB of shared memory
-    const long long budget = 100 * 1024;
-    int stages = (int)std::min<long long>(4, budget / stage_bytes);
-    stages = env_int("TRIATTN_SCORE_STAGES", stages, 1, kMaxStages);
-    if (stages < 2) stages = 2;
-    while (stages > 2 && stages * stage_bytes > 200 * 1024) --stages;
-    p.block_bytes = (int)block_bytes;
-    p.mb = mb;
-    p.stages = stages;
-    p.block_group = (gp <= 8 && Y.block_size == 16 && Y.num_kv_heads * mb == kScoreConsumerWarps &&
-                     !score_path_is_fma() && env_int("TRIATTN_SCORE_BLOCK_GROUPS", 1, 0, 1) == 1)
-                        ? Y.num_kv_heads : 0;
-    const int max_tiles = (Y.max_blocks_per_req + mb - 1) / mb;
-    // Tiles per CTA: every CTA pays a fixed start-up (weight fragments, first copies: about two tiles' worth) and
-    // the CTAs run in waves of 2 per SM, so the launch takes about waves(tpc) * (tpc + 2) tile times; take the
-    // tpc that minimises it.  At least ~64 KB and at most ~2 MB of keys per CTA, and the CTA's block ids must
-    // fit its shared-memory table.
-    const int min_tpc = (int)std::max<long long>(1, (64 * 1024) / stage_bytes);
-    int max_tpc = (int)std::max<long long>(min_tpc, (2 * 1024 * 1024) / stage_bytes);
-    max_tpc = std::max(1, std::min(max_tpc, kMaxPrefetchedBlocks / mb));
-    const int lo_tpc = std::min(min_tpc, max_tpc);
-    int tpc = lo_tpc;
-    {
-      const long long slots = (long long)kSMs * 2;
-      const long long lb = (long long)Y.num_layers * Y.num_reqs;
-      long long best = -1;
-      for (int c = lo_tpc; c <= std::min(max_tpc, max_tiles); ++c) {
-        const long long per_lb = (max_tiles + c - 1) / c;
-        const int share = (int)((max_tiles + per_lb - 1) / per_lb);  // equal shares for the CTAs of one (layer, request)
-        const long long waves = (per_lb * lb + slots - 1) / slots;
-        const long long cost = waves * (share + 2);
-        if (best < 0 || cost < best) {
-          best = cost;
-          tpc = share;
-        }
-      }
-    }
-    tpc = env_int("TRIATTN_SCORE_TILES_PER_CTA", tpc, 1, 1 << 20);
-    p.tiles_per_cta = tpc;
-    dim3 grid((unsigned)((max_tiles + tpc - 1) / tpc), (unsigned)Y.num_layers, (unsigned)Y.num_reqs);
-    const size_t smem = (size_t)stages * stage_bytes;
-    if (score_path_is_fma()) {
-      // the CUDA-core kernel works on batches of 16/gpv tokens and keeps a table of work items per stage
-      const int gpv = std::min(gp, 4), nsub = gp / gpv, nt = kLPK / gpv;
-      const long long stage_tok = (long long)mb * Y.block_size;
-      const long long n_items = nhd ? (long long)Y.num_kv_heads * nsub * (stage_tok / nt)
-                                    : (long long)mb * Y.num_kv_heads * nsub * (Y.block_size / nt);
-      const bool ok = (nhd ? (stage_tok % nt) == 0 : (Y.block_size % nt) == 0) && n_items > 0 && n_items <= kMaxScoreItems;
-      if (ok) {
-        if (Y.head_dim == 128)
-          return Y.rope_interleaved ? launch_score_fma<128, true>(p, gpv, grid, smem, st)
-                                    : launch_score_fma<128, false>(p, gpv, grid, smem, st);
-        return Y.rope_interleaved ? launch_score_fma<64, true>(p, gpv, grid, smem, st)
-                                  : launch_score_fma<64, false>(p, gpv, grid, smem, st);
-      }
-    }
-    if (Y.head_dim == 128)
-      return Y.rope_interleaved ? launch_score_mma<128, true>(p, grid, smem, st)
-                                : launch_score_mma<128, false>(p, grid, smem, st);
-    return Y.rope_interleaved ? launch_score_mma<64, true>(p, grid, smem, st)
-                              : launch_score_mma<64, false>(p, grid, smem, st);
-  }
-  // max over offsets on the tensor cores: one CTA per (layer, request, virtual head, run of 16-key tiles)
-  if (p.agg_max && (Y.head_dim == 64 || Y.head_dim == 128) && (p.block_stride_bytes % 16) == 0 &&
-      max_agg_smem_bytes(Y.head_dim, num_offsets) <= 220 * 1024 && env_int("TRIATTN_SCORE_MAX_MMA", 1, 0, 1) == 1) {
-    const int nvh = Y.num_kv_heads * ((gp + 3) / 4);
-    const int n_tiles = (p.t_pad + kMmaKeys - 1) / kMmaKeys;
-    p.tiles_per_cta = std::min(n_tiles, 16 * kMaxAggWarps);
-    const int chunks = (n_tiles + p.tiles_per_cta - 1) / p.tiles_per_cta;
-    dim3 grid((unsigned)(nvh * chunks), (unsigned)Y.num_layers, (unsigned)Y.num_reqs);
-    const size_t smem = max_agg_smem_bytes(Y.head_dim, num_offsets);
-#define TRIATTN_LAUNCH(D, IL)                                                                      \
-  {                                                                                                \
-    if (!ensure_dynamic_smem<score_paged_mma_max_kernel<D, IL>>(smem)) return TRIATTN_ERR_CUDA;    \
-    score_paged_mma_max_kernel<D, IL><<<grid, kMaxAggThreads, smem, st>>>(p);                      \
-    return check_launch();                                                                         \
-  }
-    if (Y.head_dim == 128) {
-      if (Y.rope_interleaved) TRIATTN_LAUNCH(128, true) else TRIATTN_LAUNCH(128, false)
-    } else {
-      if (Y.rope_interleaved) TRIATTN_LAUNCH(64, true) else TRIATTN_LAUNCH(64, false)
-    }
-#undef TRIATTN_LAUNCH
-  }
-  dim3 grid((unsigned)((p.t_pad + 127) / 128), (unsigned)Y.num_kv_heads, (unsigned)(Y.num_layers * Y.num_reqs));
-  if ((long long)Y.num_layers * Y.num_reqs > 65535) return TRIATTN_ERR_UNSUPPORTED_SHAPE;
-  score_paged_generic_kernel<<<grid, 128, 0, st>>>(p, Y.head_dim, Y.rope_interleaved);
-  return check_launch();
+int triattn_score_paged_cuda_cores(const triattn_paged_layout* layout, const void* const* k_layer_ptrs,
+                                   const int32_t* block_table, const int32_t* seq_lens, const float* weights,
+                                   int offset_agg, int num_offsets, float* raw_scores, double* moments,
+                                   uint32_t* device_status, void* stream) {
+  StageOpts opt;
+  opt.cuda_core_scorer = true;
+  return score_paged_impl(layout, k_layer_ptrs, block_table, seq_lens, weights, offset_agg, num_offsets, raw_scores,
+                          moments, device_status, static_cast<cudaStream_t>(stream), opt);
 }
 
 int triattn_finalize_scores(const triattn_paged_layout* layout, const float* raw_scores, const double* moments,
                             const int32_t* seq_lens, const int32_t* prefill_lens, int window, int normalize,
-                            int group_reduce, int head_reduce, int layer_reduce, float* mean_std_scratch,
-                            float* scores_out, void* stream) {
-  int rc = validate_layout(layout);
-  if (rc != TRIATTN_OK) return rc;
-  if (!raw_scores || !moments || !seq_lens || !mean_std_scratch || !scores_out) return TRIATTN_ERR_INVALID_ARGUMENT;
-  if (group_reduce != TRIATTN_REDUCE_MAX && group_reduce != TRIATTN_REDUCE_MEAN) return TRIATTN_ERR_INVALID_ARGUMENT;
-  if (head_reduce != TRIATTN_REDUCE_NONE && head_reduce != TRIATTN_REDUCE_MAX) return TRIATTN_ERR_INVALID_ARGUMENT;
-  if (layer_reduce < TRIATTN_REDUCE_NONE || layer_reduce > TRIATTN_REDUCE_MAX) return TRIATTN_ERR_INVALID_ARGUMENT;
-  const triattn_paged_layout& Y = *layout;
-  const int gp = triattn_padded_group(Y.group_size);
-  if (gp == 0) return TRIATTN_ERR_UNSUPPORTED_SHAPE;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int Hq = Y.num_kv_heads * Y.group_size;
-  const int t_pad = Y.max_blocks_per_req * Y.block_size;
-  const int n = Y.num_layers * Y.num_reqs * Hq;
-  moments_to_mean_std_kernel<<<(n + 127) / 128, 128, 0, st>>>(moments, seq_lens, Y.num_layers, Y.num_reqs, Hq, t_pad,
-                                                             mean_std_scratch);
-  FinalizeParams p{};
-  p.raw = raw_scores;
-  p.mean_std = mean_std_scratch;
-  p.seq_lens = seq_lens;
-  p.prefill_lens = prefill_lens;
-  p.out = scores_out;
-  p.L = Y.num_layers;
-  p.B = Y.num_reqs;
-  p.Hkv = Y.num_kv_heads;
-  p.g = Y.group_size;
-  p.t_pad = t_pad;
-  p.window = window;
-  p.normalize = normalize;
-  p.group_reduce = group_reduce;
-  p.head_reduce = head_reduce;
-  p.layer_reduce = layer_reduce;
-  const int Ho = head_reduce != TRIATTN_REDUCE_NONE ? 1 : Y.num_kv_heads;
-  dim3 grid((unsigned)((t_pad + 255) / 256), (unsigned)Ho, (unsigned)Y.num_reqs);
-  p.gp = gp;
-  if (head_reduce == TRIATTN_REDUCE_NONE && Y.group_size <= 8 && (gp == 4 || gp == 8)) {
-#define TRIATTN_FIN(G)                                                                                \
-  case G:                                                                                             \
-    if (layer_reduce == TRIATTN_REDUCE_NONE)                                                          \
-      finalize_scores_fast_kernel<G, TRIATTN_REDUCE_NONE><<<grid, 256, 0, st>>>(p);                   \
-    else if (layer_reduce == TRIATTN_REDUCE_MAX)                                                      \
-      finalize_scores_fast_kernel<G, TRIATTN_REDUCE_MAX><<<grid, 256, 0, st>>>(p);                    \
-    else                                                                                              \
-      finalize_scores_fast_kernel<G, TRIATTN_REDUCE_MEAN><<<grid, 256, 0, st>>>(p);                   \
-    break;
-    switch (Y.group_size) {
-      TRIATTN_FIN(3) TRIATTN_FIN(4) TRIATTN_FIN(5) TRIATTN_FIN(6) TRIATTN_FIN(7) TRIATTN_FIN(8)
-      default: finalize_scores_kernel<<<grid, 256, 0, st>>>(p);
-    }
-#undef TRIATTN_FIN
-  } else {
-    finalize_scores_kernel<<<grid, 256, 0, st>>>(p);
-  }
-  return check_launch();
+                            int group_reduce, int head_reduce, int layer_reduce, float* scores_out, void* stream) {
+  if (validate_layout(layout) != TRIATTN_OK) return validate_layout(layout);
+  return finalize_scores_impl(layout, raw_scores, moments, seq_lens, prefill_lens, window, normalize, group_reduce,
+                              head_reduce, layer_reduce, layout->num_layers, true, true, scores_out,
+                              static_cast<cudaStream_t>(stream), false);
 }
 
-int triattn_select_topk(const float* scores, int num_rows, int64_t row_stride, const int32_t* seq_lens,
-                        const int32_t* keep_counts, int num_reqs, int rows_per_req_inner, int32_t* keep_out,
-                        int keep_pitch, uint32_t* device_status, void* stream) {
+static int select_topk_impl(const float* scores, int num_rows, int64_t row_stride, const int32_t* seq_lens,
+                            const int32_t* keep_counts, int num_reqs, int rows_per_req_inner, int32_t* keep_out,
+                            int keep_pitch, uint32_t* device_status, cudaStream_t st, bool pdl) {
   if (!scores || !seq_lens || !keep_counts || !keep_out) return TRIATTN_ERR_INVALID_ARGUMENT;
   if (num_rows <= 0 || row_stride <= 0 || num_reqs <= 0 || rows_per_req_inner <= 0 || keep_pitch <= 0)
     return TRIATTN_ERR_INVALID_ARGUMENT;
@@ -420,15 +266,21 @@ int triattn_select_topk(const float* scores, int num_rows, int64_t row_stride, c
   p.keep_out = keep_out;
   p.keep_pitch = keep_pitch;
   p.status = device_status;
-  select_topk_kernel<<<num_rows, kSelectThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
-  return check_launch();
+  return launch_kernel(select_topk_kernel, dim3((unsigned)num_rows), dim3(kSelectThreads), 0, st, pdl, p);
+}
+
+int triattn_select_topk(const float* scores, int num_rows, int64_t row_stride, const int32_t* seq_lens,
+                        const int32_t* keep_counts, int num_reqs, int rows_per_req_inner, int32_t* keep_out,
+                        int keep_pitch, uint32_t* device_status, void* stream) {
+  return select_topk_impl(scores, num_rows, row_stride, seq_lens, keep_counts, num_reqs, rows_per_req_inner, keep_out,
+                          keep_pitch, device_status, static_cast<cudaStream_t>(stream), false);
 }
 
 static int compact_common(const triattn_paged_layout* layout, void* const* k_layer_ptrs, void* const* v_layer_ptrs,
                           const int32_t* block_table, const int32_t* seq_lens, const int32_t* keep,
                           int64_t keep_ls, int64_t keep_rs, int64_t keep_hs, const int32_t* keep_counts,
                           void* scratch, long long scratch_stream_bytes, int scratch_rows, bool preserve,
-                          uint32_t* device_status, void* stream) {
+                          uint32_t* device_status, void* stream, bool pdl = false) {
   int rc = validate_layout(layout);
   if (rc != TRIATTN_OK) return rc;
   if (!k_layer_ptrs || !v_layer_ptrs || !block_table || !seq_lens || !keep || !keep_counts)
@@ -467,11 +319,8 @@ static int compact_common(const triattn_paged_layout* layout, void* const* k_lay
   p.scratch_rows = scratch_rows;
   dim3 grid((unsigned)(Y.num_kv_heads * 2), (unsigned)Y.num_layers, (unsigned)Y.num_reqs);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (preserve)
-    compact_paged_kernel<true><<<grid, kCompactThreads, 0, st>>>(p);
-  else
-    compact_paged_kernel<false><<<grid, kCompactThreads, 0, st>>>(p);
-  return check_launch();
+  if (preserve) return launch_kernel(compact_paged_kernel<true>, grid, dim3(kCompactThreads), 0, st, pdl, p);
+  return launch_kernel(compact_paged_kernel<false>, grid, dim3(kCompactThreads), 0, st, pdl, p);
 }
 
 int triattn_compact_paged(const triattn_paged_layout* layout, void* const* k_layer_ptrs, void* const* v_layer_ptrs,
@@ -555,10 +404,64 @@ int triattn_apply_effective_overrides(const int32_t* idx_mapping, const int32_t*
   return check_launch();
 }
 
+// ------------------------------------------------------------------------- one-launch weight prep
+static int prep_weights_fused_impl(const float* q_mean_real, const float* q_mean_imag, const float* q_abs_mean,
+                                   const float* freq_scale_sq, const float* omega, const float* offsets,
+                                   const int32_t* round_start, int num_layers, int num_reqs, int num_q_heads,
+                                   int num_freqs, int num_offsets, int offset_agg, int flags, float* weights_out,
+                                   double* moments_to_clear, cudaStream_t st, bool pdl) {
+  if (!q_mean_real || !q_mean_imag || !q_abs_mean || !freq_scale_sq || !omega || !offsets || !round_start || !weights_out)
+    return TRIATTN_ERR_INVALID_ARGUMENT;
+  if (num_layers <= 0 || num_reqs <= 0 || num_q_heads <= 0 || num_freqs <= 0 || num_offsets <= 0)
+    return TRIATTN_ERR_INVALID_ARGUMENT;
+  if (num_reqs > 65535) return TRIATTN_ERR_UNSUPPORTED_SHAPE;
+  const size_t smem = sizeof(float) * (2 * (size_t)num_offsets * num_freqs + 2 * (size_t)num_freqs);
+  if (smem > 200 * 1024) return TRIATTN_ERR_UNSUPPORTED_SHAPE;
+  if (!ensure_dynamic_smem<prep_weights_fused_kernel>(smem)) return TRIATTN_ERR_CUDA;
+  PrepFusedParams p{};
+  p.q_re = q_mean_real;
+  p.q_im = q_mean_imag;
+  p.q_abs = q_abs_mean;
+  p.fs = freq_scale_sq;
+  p.omega = omega;
+  p.offsets = offsets;
+  p.round_start = round_start;
+  p.weights = weights_out;
+  p.moments = moments_to_clear;
+  p.L = num_layers;
+  p.B = num_reqs;
+  p.Hq = num_q_heads;
+  p.F = num_freqs;
+  p.O = num_offsets;
+  p.agg_max = offset_agg == TRIATTN_OFFSETS_MAX ? 1 : 0;
+  p.flags = flags;
+  // Every CTA re-evaluates its request's O x F trig values, so few CTAs per request would be cheapest, but the
+  // launch should still fill the GPU: about four CTAs per SM in total, at least 4 rows of weights per CTA.
+  const int n_rows = num_layers * num_q_heads;
+  const int want_ctas = std::max(1, (4 * kSMs + num_reqs - 1) / num_reqs);
+  const int chunks = std::max(1, std::min((n_rows + 3) / 4, want_ctas));
+  p.rows_per_cta = (n_rows + chunks - 1) / chunks;
+  dim3 grid((unsigned)((n_rows + p.rows_per_cta - 1) / p.rows_per_cta), (unsigned)num_reqs);
+  return launch_kernel(prep_weights_fused_kernel, grid, dim3(kPrepThreads), smem, st, pdl, p);
+}
+
+int triattn_prep_weights_fused(const float* q_mean_real, const float* q_mean_imag, const float* q_abs_mean,
+                               const float* freq_scale_sq, const float* omega, const float* offsets,
+                               const int32_t* round_start, int num_layers, int num_reqs, int num_q_heads,
+                               int num_freqs, int num_offsets, int offset_agg, int flags, float* weights_out,
+                               double* moments_to_clear, void* stream) {
+  return prep_weights_fused_impl(q_mean_real, q_mean_imag, q_abs_mean, freq_scale_sq, omega, offsets, round_start,
+                                 num_layers, num_reqs, num_q_heads, num_freqs, num_offsets, offset_agg, flags,
+                                 weights_out, moments_to_clear, static_cast<cudaStream_t>(stream), false);
+}
+
 // ------------------------------------------------------------------------- fused step
 namespace {
+// Workspace of the fused step: folded weights and moments of all layers, raw scores of ONE chunk of layers,
+// the final score rows.  The raw scores dominate (4 * Gp bytes per key); a smaller workspace means fewer layers
+// per chunk, down to one.
 struct CompressWs {
-  size_t trig, weights, raw, moments, mean_std, final_scores, total;
+  size_t weights, moments, final_scores, raw, fixed, raw_per_layer;
 };
 CompressWs compress_ws_layout(const triattn_paged_layout& Y, int num_offsets, int offset_agg) {
   CompressWs w{};
@@ -567,19 +470,15 @@ CompressWs compress_ws_layout(const triattn_paged_layout& Y, int num_offsets, in
   const int gp = std::max(1, triattn_padded_group(Y.group_size));
   const size_t t_pad = (size_t)Y.max_blocks_per_req * Y.block_size;
   size_t off = 0;
-  w.trig = off;
-  off += round_up(sizeof(float) * triattn_prep_scratch_floats(Y.num_reqs, F, num_offsets, offset_agg), 256);
   w.weights = off;
   off += round_up(sizeof(float) * (size_t)Y.num_layers * Y.num_reqs * Hq * triattn_weight_rows(offset_agg, num_offsets) * F, 256);
-  w.raw = off;
-  off += round_up(sizeof(float) * (size_t)Y.num_layers * Y.num_reqs * Y.num_kv_heads * t_pad * gp, 256);
   w.moments = off;
   off += round_up(sizeof(double) * 2 * (size_t)Y.num_layers * Y.num_reqs * Hq, 256);
-  w.mean_std = off;
-  off += round_up(sizeof(float) * 2 * (size_t)Y.num_layers * Y.num_reqs * Hq, 256);
   w.final_scores = off;
   off += round_up(sizeof(float) * (size_t)Y.num_reqs * Y.num_kv_heads * t_pad, 256);
-  w.total = off;
+  w.raw = off;
+  w.fixed = off;
+  w.raw_per_layer = round_up(sizeof(float) * (size_t)Y.num_reqs * Y.num_kv_heads * t_pad * gp, 256);
   return w;
 }
 }  // namespace
@@ -588,7 +487,16 @@ size_t triattn_compress_workspace_bytes(const triattn_paged_layout* layout, int 
                                         int keep_pitch) {
   (void)keep_pitch;
   if (validate_layout(layout) != TRIATTN_OK || num_offsets <= 0) return 0;
-  return compress_ws_layout(*layout, num_offsets, offset_agg).total;
+  const CompressWs w = compress_ws_layout(*layout, num_offsets, offset_agg);
+  return w.fixed + w.raw_per_layer * (size_t)layout->num_layers;
+}
+
+size_t triattn_compress_workspace_bytes_min(const triattn_paged_layout* layout, int num_offsets, int offset_agg,
+                                            int keep_pitch) {
+  (void)keep_pitch;
+  if (validate_layout(layout) != TRIATTN_OK || num_offsets <= 0) return 0;
+  const CompressWs w = compress_ws_layout(*layout, num_offsets, offset_agg);
+  return w.fixed + w.raw_per_layer;
 }
 
 int triattn_compress_paged(const triattn_paged_layout* layout, void* const* k_layer_ptrs, void* const* v_layer_ptrs,
@@ -605,32 +513,246 @@ int triattn_compress_paged(const triattn_paged_layout* layout, void* const* k_la
   if (layer_reduce != TRIATTN_REDUCE_MEAN && layer_reduce != TRIATTN_REDUCE_MAX) return TRIATTN_ERR_INVALID_ARGUMENT;
   const triattn_paged_layout& Y = *layout;
   const CompressWs w = compress_ws_layout(Y, num_offsets, offset_agg);
-  if (workspace_bytes < w.total) return TRIATTN_ERR_WORKSPACE_TOO_SMALL;
+  if (workspace_bytes < w.fixed + w.raw_per_layer) return TRIATTN_ERR_WORKSPACE_TOO_SMALL;
+  const int chunk_layers = (int)std::min<size_t>((size_t)Y.num_layers, (workspace_bytes - w.fixed) / w.raw_per_layer);
   unsigned char* ws = static_cast<unsigned char*>(workspace);
-  float* trig = reinterpret_cast<float*>(ws + w.trig);
   float* weights = reinterpret_cast<float*>(ws + w.weights);
   float* raw = reinterpret_cast<float*>(ws + w.raw);
   double* moments = reinterpret_cast<double*>(ws + w.moments);
-  float* mean_std = reinterpret_cast<float*>(ws + w.mean_std);
   float* fin = reinterpret_cast<float*>(ws + w.final_scores);
   const int Hq = Y.num_kv_heads * Y.group_size;
+  const int F = Y.head_dim / 2;
   const int64_t t_pad = (int64_t)Y.max_blocks_per_req * Y.block_size;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
 
-  rc = triattn_prep_weights(q_mean_real, q_mean_imag, q_abs_mean, freq_scale_sq, omega, offsets, round_start,
-                            Y.num_layers, Y.num_reqs, Hq, Y.head_dim / 2, num_offsets, offset_agg, flags, trig,
-                            weights, stream);
+  // prep (also clears the moments) -> per chunk of layers: score -> finalize into the running rows -> top-k ->
+  // compaction.  Every launch after the first is a programmatic dependent of the one before it.
+  rc = prep_weights_fused_impl(q_mean_real, q_mean_imag, q_abs_mean, freq_scale_sq, omega, offsets, round_start,
+                               Y.num_layers, Y.num_reqs, Hq, F, num_offsets, offset_agg, flags, weights, moments, st,
+                               false);
   if (rc != TRIATTN_OK) return rc;
-  rc = triattn_score_paged(layout, reinterpret_cast<const void* const*>(k_layer_ptrs), block_table, seq_lens,
-                           weights, offset_agg, num_offsets, raw, moments, device_status, stream);
+  const size_t w_layer = (size_t)Y.num_reqs * Hq * triattn_weight_rows(offset_agg, num_offsets) * F;
+  const size_t m_layer = (size_t)Y.num_reqs * Hq * 2;
+  StageOpts opt;
+  opt.pdl = true;
+  opt.moments_cleared = true;
+  for (int l0 = 0; l0 < Y.num_layers; l0 += chunk_layers) {
+    triattn_paged_layout C = Y;
+    C.num_layers = std::min(chunk_layers, Y.num_layers - l0);
+    rc = score_paged_impl(&C, reinterpret_cast<const void* const*>(k_layer_ptrs) + l0, block_table, seq_lens,
+                          weights + (size_t)l0 * w_layer, offset_agg, num_offsets, raw, moments + (size_t)l0 * m_layer,
+                          device_status, st, opt);
+    if (rc != TRIATTN_OK) return rc;
+    rc = finalize_scores_impl(&C, raw, moments + (size_t)l0 * m_layer, seq_lens, prefill_lens, window, normalize,
+                              TRIATTN_REDUCE_MAX, TRIATTN_REDUCE_NONE, layer_reduce, Y.num_layers, l0 == 0,
+                              l0 + C.num_layers >= Y.num_layers, fin, st, true);
+    if (rc != TRIATTN_OK) return rc;
+  }
+  rc = select_topk_impl(fin, Y.num_reqs * Y.num_kv_heads, t_pad, seq_lens, keep_counts, Y.num_reqs, Y.num_kv_heads,
+                        keep_out, keep_pitch, device_status, st, true);
   if (rc != TRIATTN_OK) return rc;
-  rc = triattn_finalize_scores(layout, raw, moments, seq_lens, prefill_lens, window, normalize, TRIATTN_REDUCE_MAX,
-                               TRIATTN_REDUCE_NONE, layer_reduce, mean_std, fin, stream);
-  if (rc != TRIATTN_OK) return rc;
-  rc = triattn_select_topk(fin, Y.num_reqs * Y.num_kv_heads, t_pad, seq_lens, keep_counts, Y.num_reqs,
-                           Y.num_kv_heads, keep_out, keep_pitch, device_status, stream);
-  if (rc != TRIATTN_OK) return rc;
-  return triattn_compact_paged(layout, k_layer_ptrs, v_layer_ptrs, block_table, seq_lens, keep_out, 0,
-                               (int64_t)Y.num_kv_heads * keep_pitch, keep_pitch, keep_counts, device_status, stream);
+  return compact_common(layout, k_layer_ptrs, v_layer_ptrs, block_table, seq_lens, keep_out, 0,
+                        (int64_t)Y.num_kv_heads * keep_pitch, keep_pitch, keep_counts, nullptr, 0, 0, false,
+                        device_status, stream, true);
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------- stage implementations
+namespace {
+
+int score_paged_impl(const triattn_paged_layout* layout, const void* const* k_layer_ptrs, const int32_t* block_table,
+                     const int32_t* seq_lens, const float* weights, int offset_agg, int num_offsets,
+                     float* raw_scores, double* moments, uint32_t* device_status, cudaStream_t st,
+                     const StageOpts& opt) {
+  int rc = validate_layout(layout);
+  if (rc != TRIATTN_OK) return rc;
+  if (!k_layer_ptrs || !block_table || !seq_lens || !weights || !raw_scores || !moments)
+    return TRIATTN_ERR_INVALID_ARGUMENT;
+  const triattn_paged_layout& Y = *layout;
+  const int gp = triattn_padded_group(Y.group_size);
+  if (gp == 0) return TRIATTN_ERR_UNSUPPORTED_SHAPE;
+  const int Hq = Y.num_kv_heads * Y.group_size;
+  if (!opt.moments_cleared &&
+      cudaMemsetAsync(moments, 0, sizeof(double) * 2 * (size_t)Y.num_layers * Y.num_reqs * Hq, st) != cudaSuccess)
+    return TRIATTN_ERR_CUDA;
+
+  ScoreParams p{};
+  p.k_ptrs = k_layer_ptrs;
+  p.block_table = block_table;
+  p.seq_lens = seq_lens;
+  p.weights = weights;
+  p.raw = raw_scores;
+  p.moments = moments;
+  p.status = device_status;
+  p.L = Y.num_layers;
+  p.B = Y.num_reqs;
+  p.Hkv = Y.num_kv_heads;
+  p.g = Y.group_size;
+  p.bs = Y.block_size;
+  p.num_blocks = Y.num_blocks;
+  p.max_blocks = Y.max_blocks_per_req;
+  p.t_pad = Y.max_blocks_per_req * Y.block_size;
+  p.block_stride_bytes = (long long)Y.block_stride * 2;
+  p.token_stride = (int)Y.token_stride;
+  p.head_stride = (int)Y.head_stride;
+  p.num_offsets = num_offsets;
+  p.agg_max = offset_agg == TRIATTN_OFFSETS_MAX ? 1 : 0;
+
+  const long long block_bytes = (long long)Y.block_size * Y.num_kv_heads * Y.head_dim * 2;
+  p.gp_total = gp;
+  const bool nhd = Y.head_stride == Y.head_dim && Y.token_stride == (int64_t)Y.num_kv_heads * Y.head_dim;
+  p.nhd = nhd ? 1 : 0;
+  // Streaming kernels: mean aggregation, head_dim 64/128, K region of a block one dense run.
+  const bool streamable = !p.agg_max && (Y.head_dim == 64 || Y.head_dim == 128) && block_is_dense(layout) &&
+                          block_bytes <= 64 * 1024 && (block_bytes % 16) == 0 && (p.block_stride_bytes % 16) == 0;
+  if (streamable) {
+    // cache blocks per pipeline stage: a power of two filling ~32 KB (8 work items of 16 keys for 8 KV heads)
+    int mb = 1;
+    while ((mb * 2) * block_bytes <= 32 * 1024) mb *= 2;
+    const long long stage_bytes = (long long)mb * block_bytes;
+    // two CTAs per SM share ~200 KB of shared memory
+    int stages = (int)std::min<long long>(4, (100 * 1024) / stage_bytes);
+    if (stages < 2) stages = 2;
+    p.block_bytes = (int)block_bytes;
+    p.mb = mb;
+    p.stages = stages;
+    p.block_group = (gp <= 8 && Y.block_size == 16 && Y.num_kv_heads * mb == kScoreConsumerWarps && !opt.cuda_core_scorer)
+                        ? Y.num_kv_heads : 0;
+    const int max_tiles = (Y.max_blocks_per_req + mb - 1) / mb;
+    // Tiles per CTA: every CTA pays a fixed start-up (weight fragments, first copies: about two tiles' worth) and
+    // the CTAs run in waves of 2 per SM, so the launch takes about waves(tpc) * (tpc + 2) tile times; take the
+    // tpc that minimises it.  At least ~64 KB and at most ~2 MB of keys per CTA, and the CTA's block ids must
+    // fit its shared-memory table.
+    const int min_tpc = (int)std::max<long long>(1, (64 * 1024) / stage_bytes);
+    int max_tpc = (int)std::max<long long>(min_tpc, (2 * 1024 * 1024) / stage_bytes);
+    max_tpc = std::max(1, std::min(max_tpc, kMaxPrefetchedBlocks / mb));
+    const int lo_tpc = std::min(min_tpc, max_tpc);
+    int tpc = lo_tpc;
+    {
+      const long long slots = (long long)kSMs * 2;
+      const long long lb = (long long)Y.num_layers * Y.num_reqs;
+      long long best = -1;
+      for (int c = lo_tpc; c <= std::min(max_tpc, max_tiles); ++c) {
+        const long long per_lb = (max_tiles + c - 1) / c;
+        const int share = (int)((max_tiles + per_lb - 1) / per_lb);  // equal shares for the CTAs of one (layer, request)
+        const long long waves = (per_lb * lb + slots - 1) / slots;
+        const long long cost = waves * (share + 2);
+        if (best < 0 || cost < best) {
+          best = cost;
+          tpc = share;
+        }
+      }
+    }
+    p.tiles_per_cta = tpc;
+    dim3 grid((unsigned)((max_tiles + tpc - 1) / tpc), (unsigned)Y.num_layers, (unsigned)Y.num_reqs);
+    const size_t smem = (size_t)stages * stage_bytes;
+    if (opt.cuda_core_scorer) {
+      // the CUDA-core kernel works on batches of 16/gpv tokens and keeps a table of work items per stage
+      const int gpv = std::min(gp, 4), nsub = gp / gpv, nt = kLPK / gpv;
+      const long long stage_tok = (long long)mb * Y.block_size;
+      const long long n_items = nhd ? (long long)Y.num_kv_heads * nsub * (stage_tok / nt)
+                                    : (long long)mb * Y.num_kv_heads * nsub * (Y.block_size / nt);
+      const bool ok = (nhd ? (stage_tok % nt) == 0 : (Y.block_size % nt) == 0) && n_items > 0 && n_items <= kMaxScoreItems;
+      if (!ok) return TRIATTN_ERR_UNSUPPORTED_SHAPE;
+      if (Y.head_dim == 128)
+        return Y.rope_interleaved ? launch_score_fma<128, true>(p, gpv, grid, smem, st, opt.pdl)
+                                  : launch_score_fma<128, false>(p, gpv, grid, smem, st, opt.pdl);
+      return Y.rope_interleaved ? launch_score_fma<64, true>(p, gpv, grid, smem, st, opt.pdl)
+                                : launch_score_fma<64, false>(p, gpv, grid, smem, st, opt.pdl);
+    }
+    if (Y.head_dim == 128)
+      return Y.rope_interleaved ? launch_score_mma<128, true>(p, grid, smem, st, opt.pdl)
+                                : launch_score_mma<128, false>(p, grid, smem, st, opt.pdl);
+    return Y.rope_interleaved ? launch_score_mma<64, true>(p, grid, smem, st, opt.pdl)
+                              : launch_score_mma<64, false>(p, grid, smem, st, opt.pdl);
+  }
+  if (opt.cuda_core_scorer) return TRIATTN_ERR_UNSUPPORTED_SHAPE;
+  // max over offsets on the tensor cores: one CTA per (layer, request, virtual head, run of 16-key tiles)
+  if (p.agg_max && (Y.head_dim == 64 || Y.head_dim == 128) && (p.block_stride_bytes % 16) == 0 &&
+      max_agg_smem_bytes(Y.head_dim, num_offsets) <= 220 * 1024) {
+    const int nvh = Y.num_kv_heads * ((gp + 3) / 4);
+    const int n_tiles = (p.t_pad + kMmaKeys - 1) / kMmaKeys;
+    p.tiles_per_cta = std::min(n_tiles, 16 * kMaxAggWarps);
+    const int chunks = (n_tiles + p.tiles_per_cta - 1) / p.tiles_per_cta;
+    dim3 grid((unsigned)(nvh * chunks), (unsigned)Y.num_layers, (unsigned)Y.num_reqs);
+    const size_t smem = max_agg_smem_bytes(Y.head_dim, num_offsets);
+#define TRIATTN_LAUNCH(D, IL)                                                                      \
+  {                                                                                                \
+    if (!ensure_dynamic_smem<score_paged_mma_max_kernel<D, IL>>(smem)) return TRIATTN_ERR_CUDA;    \
+    return launch_kernel(score_paged_mma_max_kernel<D, IL>, grid, dim3(kMaxAggThreads), smem, st, opt.pdl, p); \
+  }
+    if (Y.head_dim == 128) {
+      if (Y.rope_interleaved) TRIATTN_LAUNCH(128, true) else TRIATTN_LAUNCH(128, false)
+    } else {
+      if (Y.rope_interleaved) TRIATTN_LAUNCH(64, true) else TRIATTN_LAUNCH(64, false)
+    }
+#undef TRIATTN_LAUNCH
+  }
+  dim3 grid((unsigned)((p.t_pad + 127) / 128), (unsigned)Y.num_kv_heads, (unsigned)(Y.num_layers * Y.num_reqs));
+  if ((long long)Y.num_layers * Y.num_reqs > 65535) return TRIATTN_ERR_UNSUPPORTED_SHAPE;
+  return launch_kernel(score_paged_generic_kernel, grid, dim3(128), 0, st, opt.pdl, p, (int)Y.head_dim,
+                       (int)Y.rope_interleaved);
+}
+
+int finalize_scores_impl(const triattn_paged_layout* layout, const float* raw_scores, const double* moments,
+                         const int32_t* seq_lens, const int32_t* prefill_lens, int window, int normalize,
+                         int group_reduce, int head_reduce, int layer_reduce, int l_total, bool first_chunk,
+                         bool last_chunk, float* scores_out, cudaStream_t st, bool pdl) {
+  if (!raw_scores || !moments || !seq_lens || !scores_out) return TRIATTN_ERR_INVALID_ARGUMENT;
+  if (group_reduce != TRIATTN_REDUCE_MAX && group_reduce != TRIATTN_REDUCE_MEAN) return TRIATTN_ERR_INVALID_ARGUMENT;
+  if (head_reduce != TRIATTN_REDUCE_NONE && head_reduce != TRIATTN_REDUCE_MAX) return TRIATTN_ERR_INVALID_ARGUMENT;
+  if (layer_reduce < TRIATTN_REDUCE_NONE || layer_reduce > TRIATTN_REDUCE_MAX) return TRIATTN_ERR_INVALID_ARGUMENT;
+  const triattn_paged_layout& Y = *layout;
+  const int gp = triattn_padded_group(Y.group_size);
+  if (gp == 0) return TRIATTN_ERR_UNSUPPORTED_SHAPE;
+  const int t_pad = Y.max_blocks_per_req * Y.block_size;
+  FinalizeParams p{};
+  p.raw = raw_scores;
+  p.moments = moments;
+  p.seq_lens = seq_lens;
+  p.prefill_lens = prefill_lens;
+  p.out = scores_out;
+  p.L = Y.num_layers;
+  p.B = Y.num_reqs;
+  p.Hkv = Y.num_kv_heads;
+  p.g = Y.group_size;
+  p.t_pad = t_pad;
+  p.window = window;
+  p.normalize = normalize;
+  p.group_reduce = group_reduce;
+  p.head_reduce = head_reduce;
+  p.layer_reduce = layer_reduce;
+  p.l_total = l_total;
+  p.first_chunk = first_chunk ? 1 : 0;
+  p.last_chunk = last_chunk ? 1 : 0;
+  p.gp = gp;
+  const int Ho = head_reduce != TRIATTN_REDUCE_NONE ? 1 : Y.num_kv_heads;
+  dim3 grid((unsigned)((t_pad + 255) / 256), (unsigned)Ho, (unsigned)Y.num_reqs);
+  // (mean, 1/std) of the rows a CTA normalises with live in its shared memory
+  const size_t heads_per_cta = (size_t)(head_reduce != TRIATTN_REDUCE_NONE ? Y.num_kv_heads : 1) * Y.group_size;
+  const size_t smem = sizeof(float2) * (size_t)Y.num_layers * heads_per_cta;
+  if (smem > 200 * 1024) return TRIATTN_ERR_UNSUPPORTED_SHAPE;
+  if (head_reduce == TRIATTN_REDUCE_NONE && Y.group_size <= 8 && (gp == 4 || gp == 8)) {
+#define TRIATTN_FIN_LR(G, LR)                                                                         \
+  {                                                                                                   \
+    if (!ensure_dynamic_smem<finalize_scores_fast_kernel<G, LR>>(smem)) return TRIATTN_ERR_CUDA;      \
+    return launch_kernel(finalize_scores_fast_kernel<G, LR>, grid, dim3(256), smem, st, pdl, p);      \
+  }
+#define TRIATTN_FIN(G)                                                                                \
+  case G:                                                                                             \
+    if (layer_reduce == TRIATTN_REDUCE_NONE) TRIATTN_FIN_LR(G, TRIATTN_REDUCE_NONE)                   \
+    if (layer_reduce == TRIATTN_REDUCE_MAX) TRIATTN_FIN_LR(G, TRIATTN_REDUCE_MAX)                     \
+    TRIATTN_FIN_LR(G, TRIATTN_REDUCE_MEAN)
+    switch (Y.group_size) {
+      TRIATTN_FIN(3) TRIATTN_FIN(4) TRIATTN_FIN(5) TRIATTN_FIN(6) TRIATTN_FIN(7) TRIATTN_FIN(8)
+      default: break;
+    }
+#undef TRIATTN_FIN
+#undef TRIATTN_FIN_LR
+  }
+  if (!ensure_dynamic_smem<finalize_scores_kernel>(smem)) return TRIATTN_ERR_CUDA;
+  return launch_kernel(finalize_scores_kernel, grid, dim3(256), smem, st, pdl, p);
+}
+
+}  // namespace

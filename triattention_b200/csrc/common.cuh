@@ -77,9 +77,17 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity
 }
 // Bounded wait: each poll may suspend the thread in hardware for up to kWaitSuspendNs (so a wait that is
 // satisfied within that time costs one instruction); after kWaitLimit polls it gives up and reports failure
-// instead of spinning forever (worst case about kWaitLimit * kWaitSuspendNs = 1 s).
+// instead of spinning forever (worst case about kWaitLimit * kWaitSuspendNs = 1 s).  A build with
+// TRIATTN_TEST_SHORT_WAIT (tests only) gives up after about a millisecond and makes every barrier expect
+// kTestExtraTxBytes more than is ever copied, so that the wait runs out after all real copies have landed.
 constexpr uint32_t kWaitSuspendNs = 1u << 14;
+#ifdef TRIATTN_TEST_SHORT_WAIT
+constexpr uint32_t kWaitLimit = 1u << 6;
+constexpr uint32_t kTestExtraTxBytes = 16u;
+#else
 constexpr uint32_t kWaitLimit = 1u << 16;
+constexpr uint32_t kTestExtraTxBytes = 0u;
+#endif
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
   if (mbar_try_wait_hint(bar, parity, kWaitSuspendNs)) return true;
   for (uint32_t i = 1; i < kWaitLimit; ++i) {
@@ -87,6 +95,34 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
   }
   return false;
 }
+// Same, but also gives up as soon as `*abort_flag` (shared memory) is non-zero: once one warp of a CTA has
+// timed out the stages it would have released are never refilled, and the others need not wait a second each.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, const volatile int* abort_flag) {
+  if (mbar_try_wait_hint(bar, parity, kWaitSuspendNs)) return true;
+  for (uint32_t i = 1; i < kWaitLimit; ++i) {
+    if (*abort_flag != 0) return false;
+    if (mbar_try_wait_hint(bar, parity, kWaitSuspendNs)) return true;
+  }
+  return false;
+}
+// Release/acquire counter in shared memory.  A warp that has finished reading a buffer calls __syncwarp() and
+// then one lane adds 1 with acq_rel semantics: the release half publishes the warp's reads, the acquire half
+// makes the reads of every warp that added before visible-as-done to the adder, so the warp whose add completes
+// the count may hand the buffer back to the async proxy (fence.proxy.async, then the bulk copy).
+__device__ __forceinline__ unsigned atom_add_acq_rel_shared(unsigned* counter, unsigned v) {
+  unsigned old;
+  asm volatile("atom.acq_rel.cta.shared::cta.add.u32 %0, [%1], %2;" : "=r"(old) : "r"(smem_u32(counter)), "r"(v) : "memory");
+  return old;
+}
+
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with the programmatic-stream-serialization attribute may start while its predecessor in
+// the stream is still running; it must call grid_dependency_wait() before it touches anything the predecessor
+// wrote (the wait returns once the predecessor has completed and its memory is visible).  A predecessor calls
+// trigger_dependents() once its CTA no longer needs the SM resources the successor competes for.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void trigger_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // 1-D bulk copy global -> this CTA's shared memory, completion counted in bytes on `bar`.
 // Both addresses 16-byte aligned, bytes a multiple of 16.  No multicast.
 __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {

@@ -56,6 +56,8 @@ __device__ __forceinline__ uint32_t slot_off16(const CompactParams& p, const int
 
 template <bool PRESERVE>
 __global__ void __launch_bounds__(kCompactThreads) compact_paged_kernel(const __grid_constant__ CompactParams p) {
+  grid_dependency_wait();  // no global access before the preceding kernel of the stream has completed
+  trigger_dependents();
   const int which = blockIdx.x & 1;  // 0: K, 1: V
   const int head = blockIdx.x >> 1;
   const int l = blockIdx.y, b = blockIdx.z;

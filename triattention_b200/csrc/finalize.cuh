@@ -6,56 +6,64 @@
 
 namespace triattn {
 
-// mean_std[l][b][h] = (mean, 1/std_safe) from (sum, sumsq): mean = S1/n, var = (S2 - n*mean^2)/(n-1)
-// clamped at 0, std < 1e-8 -> 1 (streaming formula of the reference selector), evaluated in double.
-__global__ void moments_to_mean_std_kernel(const double* __restrict__ moments, const int32_t* __restrict__ seq_lens,
-                                           int L, int B, int Hq, int t_pad, float* __restrict__ mean_std) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= L * B * Hq) return;
-  const int b = (i / Hq) % B;
-  const int n = min(seq_lens[b], t_pad);
-  const double s1 = moments[2 * (size_t)i], s2 = moments[2 * (size_t)i + 1];
+// (mean, 1/std_safe) of one (layer, request, query head) row from its (sum, sum of squares): mean = S1/n,
+// var = (S2 - n*mean^2)/(n-1) clamped at 0, std < 1e-8 -> 1 (the streaming formula of the reference selector,
+// selector_hf.py:896-913), evaluated in double; the finalize kernels multiply by the reciprocal.
+__device__ __forceinline__ float2 mean_rstd_from_moments(const double* __restrict__ m, int n) {
+  const double s1 = m[0], s2 = m[1];
   double mean = 0.0, var = 0.0;
   if (n > 0) mean = s1 / (double)n;
   if (n > 1) var = (s2 - (double)n * mean * mean) / (double)(n - 1);
   if (var < 0.0) var = 0.0;
   float sd = (float)sqrt(var);
   if (sd < 1e-8f) sd = 1.0f;
-  mean_std[2 * (size_t)i] = (float)mean;
-  mean_std[2 * (size_t)i + 1] = 1.0f / sd;  // the finalize kernel multiplies by the reciprocal
+  return make_float2((float)mean, 1.0f / sd);
 }
 
-#ifndef TRIATTN_FIN_UNROLL
-#define TRIATTN_FIN_UNROLL 4
-#endif
-constexpr int kFinalizeUnroll = TRIATTN_FIN_UNROLL;
+constexpr int kFinalizeUnroll = 4;
 
 struct FinalizeParams {
   const float* raw;        // [L, B, Hkv, t_pad, gp]
-  const float* mean_std;   // [L, B, Hq, 2]: (mean, 1/std)
+  const double* moments;   // [L, B, Hq, 2]: (sum, sum of squares) from the scorer
   const int32_t* seq_lens;
   const int32_t* prefill_lens;  // may be null
   float* out;              // [Lo, B, Ho, t_pad]
   int L, B, Hkv, g, gp, t_pad;
   int window, normalize, group_reduce, head_reduce, layer_reduce;
+  // A step may be cut into chunks of layers (raw scores of one chunk at a time): L counts the layers of this
+  // call, l_total those of the whole step.  With a layer reduction, every call but the first continues from
+  // the value already in `out` and only the last one divides the mean.
+  int l_total, first_chunk, last_chunk;
 };
 
-// one thread per (request, output head, token); gp = query-head slots per KV head in the raw layout
+// one thread per (request, output head, token); gp = query-head slots per KV head in the raw layout.
+// Dynamic shared memory: (mean, 1/std) of the L x (heads this CTA reduces) rows it normalises with.
 __global__ void __launch_bounds__(256) finalize_scores_kernel(const __grid_constant__ FinalizeParams p) {
+  extern __shared__ float2 s_ms[];
+  grid_dependency_wait();
+  trigger_dependents();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   const int ho = blockIdx.y, b = blockIdx.z;
   const int seq_len = min(p.seq_lens[b], p.t_pad);
-  if (t >= seq_len) return;
   const int gp = p.gp;
   const int Hq = p.Hkv * p.g;
   const int Ho = p.head_reduce != TRIATTN_REDUCE_NONE ? 1 : p.Hkv;
+  const int h_begin = p.head_reduce != TRIATTN_REDUCE_NONE ? 0 : ho;
+  const int h_end = p.head_reduce != TRIATTN_REDUCE_NONE ? p.Hkv : ho + 1;
+  const int nh = (h_end - h_begin) * p.g;  // query heads this CTA reads
+  if (blockIdx.x * blockDim.x >= seq_len) return;  // whole CTA beyond the request
+  for (int i = threadIdx.x; i < p.L * nh; i += blockDim.x) {
+    const int l = i / nh, hq = h_begin * p.g + (i - l * nh);
+    s_ms[i] = mean_rstd_from_moments(p.moments + (((size_t)l * p.B + b) * Hq + hq) * 2, seq_len);
+  }
+  __syncthreads();
+  if (t >= seq_len) return;
   const int recent = p.window > 0 ? min(p.window, seq_len) : 0;
   bool guarded = recent > 0 && t >= seq_len - recent;
   if (p.prefill_lens != nullptr && t < p.prefill_lens[b]) guarded = true;
-  const int h_begin = p.head_reduce != TRIATTN_REDUCE_NONE ? 0 : ho;
-  const int h_end = p.head_reduce != TRIATTN_REDUCE_NONE ? p.Hkv : ho + 1;
   const bool vec4 = (gp & 3) == 0;
-  float acc = 0.f;
+  float* out_red = p.out + ((size_t)b * Ho + ho) * (size_t)p.t_pad + t;
+  float acc = (p.layer_reduce != TRIATTN_REDUCE_NONE && !p.first_chunk) ? *out_red : 0.f;
 #pragma unroll(kFinalizeUnroll)
   for (int l = 0; l < p.L; ++l) {
     float lv = -INFINITY;
@@ -65,7 +73,7 @@ __global__ void __launch_bounds__(256) finalize_scores_kernel(const __grid_const
         gv = INFINITY;
       } else {
         const float* r = p.raw + ((((size_t)l * p.B + b) * p.Hkv + kvh) * (size_t)p.t_pad + t) * gp;
-        const float* ms = p.mean_std + (((size_t)l * p.B + b) * Hq + (size_t)kvh * p.g) * 2;
+        const float2* ms = s_ms + (size_t)l * nh + (size_t)(kvh - h_begin) * p.g;
         float mx = -INFINITY, sum = 0.f;
         for (int j0 = 0; j0 < p.g; j0 += 4) {
           float s[4];
@@ -80,7 +88,7 @@ __global__ void __launch_bounds__(256) finalize_scores_kernel(const __grid_const
           for (int j = 0; j < 4; ++j) {
             if (j0 + j < p.g) {
               float z = s[j];
-              if (p.normalize) z = __fmul_rn(__fsub_rn(z, __ldg(ms + 2 * (j0 + j))), __ldg(ms + 2 * (j0 + j) + 1));
+              if (p.normalize) z = __fmul_rn(__fsub_rn(z, ms[j0 + j].x), ms[j0 + j].y);
               mx = fmaxf(mx, z);
               sum = __fadd_rn(sum, z);
             }
@@ -90,16 +98,17 @@ __global__ void __launch_bounds__(256) finalize_scores_kernel(const __grid_const
       }
       lv = fmaxf(lv, gv);  // single head unless head_reduce == MAX
     }
+    const bool first = l == 0 && p.first_chunk;
     if (p.layer_reduce == TRIATTN_REDUCE_NONE) {
       p.out[(((size_t)l * p.B + b) * Ho + ho) * (size_t)p.t_pad + t] = lv;
     } else if (p.layer_reduce == TRIATTN_REDUCE_MAX) {
-      acc = l == 0 ? lv : fmaxf(acc, lv);
+      acc = first ? lv : fmaxf(acc, lv);
     } else {
-      acc = l == 0 ? lv : __fadd_rn(acc, lv);
+      acc = first ? lv : __fadd_rn(acc, lv);
     }
   }
-  if (p.layer_reduce == TRIATTN_REDUCE_MEAN) acc = __fdiv_rn(acc, (float)p.L);
-  if (p.layer_reduce != TRIATTN_REDUCE_NONE) p.out[((size_t)b * Ho + ho) * (size_t)p.t_pad + t] = acc;
+  if (p.layer_reduce == TRIATTN_REDUCE_MEAN && p.last_chunk) acc = __fdiv_rn(acc, (float)p.l_total);
+  if (p.layer_reduce != TRIATTN_REDUCE_NONE) *out_red = acc;
 }
 
 // Fast path for one KV head per output row (head_reduce == NONE): group size G and the layer reduction are
@@ -111,11 +120,23 @@ constexpr int kFinalizePrefetch = 6;
 template <int G, int LR>
 __global__ void __launch_bounds__(256) finalize_scores_fast_kernel(const __grid_constant__ FinalizeParams p) {
   constexpr int NQ = (G + 3) / 4;  // float4 loads per layer; the raw layout has 4*NQ slots per KV head
+  extern __shared__ float2 s_ms[];  // [L][G]: (mean, 1/std) of this CTA's query heads
+  grid_dependency_wait();
+  trigger_dependents();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   const int kvh = blockIdx.y, b = blockIdx.z;
   const int seq_len = min(p.seq_lens[b], p.t_pad);
-  if (t >= seq_len) return;
+  if (blockIdx.x * blockDim.x >= seq_len) return;  // whole CTA beyond the request
   const int Hq = p.Hkv * G;
+  const bool normalize = p.normalize != 0, group_mean = p.group_reduce == TRIATTN_REDUCE_MEAN;
+  for (int i = threadIdx.x; i < p.L * G; i += blockDim.x) {
+    const int l = i / G, j = i - l * G;
+    float2 m = mean_rstd_from_moments(p.moments + (((size_t)l * p.B + b) * Hq + (size_t)kvh * G + j) * 2, seq_len);
+    if (!normalize) m = make_float2(0.f, 1.f);  // (s - 0) * 1 == s exactly
+    s_ms[i] = m;
+  }
+  __syncthreads();
+  if (t >= seq_len) return;
   const int recent = p.window > 0 ? min(p.window, seq_len) : 0;
   bool guarded = recent > 0 && t >= seq_len - recent;
   if (p.prefill_lens != nullptr && t < p.prefill_lens[b]) guarded = true;
@@ -132,32 +153,30 @@ __global__ void __launch_bounds__(256) finalize_scores_fast_kernel(const __grid_
   }
   const size_t raw_layer_stride = (size_t)p.B * p.Hkv * (size_t)p.t_pad * NQ;  // in float4
   const float4* r = reinterpret_cast<const float4*>(p.raw) + (((size_t)b * p.Hkv + kvh) * (size_t)p.t_pad + t) * NQ;
-  const float2* ms = reinterpret_cast<const float2*>(p.mean_std) + ((size_t)b * Hq + (size_t)kvh * G);
-  const size_t ms_layer_stride = (size_t)p.B * Hq;  // in float2
-  const bool normalize = p.normalize != 0, group_mean = p.group_reduce == TRIATTN_REDUCE_MEAN;
-  float acc = 0.f;
+  const bool first_chunk = p.first_chunk != 0;
+  float acc = (LR != TRIATTN_REDUCE_NONE && !first_chunk) ? *out : 0.f;
 
   // z-normalise, reduce over the G query heads; then fold layer l into the accumulator / the output
   auto layer = [&](const float4 (&q)[NQ], int l) {
-    const float2* msl = ms + (size_t)l * ms_layer_stride;
+    const float2* msl = s_ms + (size_t)l * G;
     float mx = -INFINITY, sum = 0.f;
 #pragma unroll
     for (int j = 0; j < G; ++j) {
       const float4 v = q[j >> 2];
       const float sj = (j & 3) == 0 ? v.x : (j & 3) == 1 ? v.y : (j & 3) == 2 ? v.z : v.w;
-      float2 m = __ldg(msl + j);
-      if (!normalize) m = make_float2(0.f, 1.f);  // (s - 0) * 1 == s exactly
+      const float2 m = msl[j];
       const float z = __fmul_rn(__fsub_rn(sj, m.x), m.y);
       mx = fmaxf(mx, z);
       sum = __fadd_rn(sum, z);
     }
     const float lv = group_mean ? __fdiv_rn(sum, (float)G) : mx;
+    const bool first = l == 0 && first_chunk;
     if (LR == TRIATTN_REDUCE_NONE) {
       out[(size_t)l * out_layer_stride] = lv;
     } else if (LR == TRIATTN_REDUCE_MAX) {
-      acc = l == 0 ? lv : fmaxf(acc, lv);
+      acc = first ? lv : fmaxf(acc, lv);
     } else {
-      acc = l == 0 ? lv : __fadd_rn(acc, lv);
+      acc = first ? lv : __fadd_rn(acc, lv);
     }
   };
 
@@ -177,7 +196,7 @@ __global__ void __launch_bounds__(256) finalize_scores_fast_kernel(const __grid_
     for (int n = 0; n < NQ; ++n) q[n] = r[(size_t)l0 * raw_layer_stride + n];
     layer(q, l0);
   }
-  if (LR == TRIATTN_REDUCE_MEAN) acc = __fdiv_rn(acc, (float)p.L);
+  if (LR == TRIATTN_REDUCE_MEAN && p.last_chunk) acc = __fdiv_rn(acc, (float)p.l_total);
   if (LR != TRIATTN_REDUCE_NONE) *out = acc;
 }
 

@@ -41,6 +41,8 @@ constexpr int kMaxPrefetchedBlocks = 1024;  // block ids of a CTA's tiles kept i
 // (token, KV head); K is read straight from global memory (cache resident between passes).
 // Weight rows: MEAN {w_re, w_im, w_mag}; MAX {w_re[o]..., w_im[o]..., w_mag}.
 __global__ void score_paged_generic_kernel(const __grid_constant__ ScoreParams p, int D, int interleaved) {
+  grid_dependency_wait();  // no global access before the preceding kernel of the stream has completed
+  trigger_dependents();
   const int GP = p.gp_total;
   const int F = D / 2;
   const int l = blockIdx.z / p.B, b = blockIdx.z % p.B;

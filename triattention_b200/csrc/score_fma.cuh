@@ -23,9 +23,7 @@ namespace triattn {
 
 constexpr int kLPK = 16;  // lanes per key
 constexpr int kScoreConsumerThreads = kScoreConsumerWarps * 32;
-#ifndef TRIATTN_SCORE_MIN_CTAS
-#define TRIATTN_SCORE_MIN_CTAS 2
-#endif
+constexpr int kScoreFmaMinCtas = 2;  // CTAs per SM the register budget is held to
 
 // One (virtual head, token-batch) work item of a pipeline stage; the table is identical for every stage.
 // A KV head with g > 4 query heads is split into ceil(g/4) virtual heads of <= 4 query heads that read
@@ -40,7 +38,7 @@ constexpr int kMaxScoreItems = 256;
 
 // GP = query-head slots per virtual head (1, 2 or 4).  p.gp_total = slots per KV head in the raw layout.
 template <int D, int GP, bool INTERLEAVED>
-__global__ void __launch_bounds__(kScoreThreadsWS, TRIATTN_SCORE_MIN_CTAS)
+__global__ void __launch_bounds__(kScoreThreadsWS, kScoreFmaMinCtas)
 score_paged_mean_kernel(const __grid_constant__ ScoreParams p) {
   constexpr int F = D / 2;
   constexpr int FPT = F / kLPK;  // frequencies per lane: 4 (D=128) or 2 (D=64)
@@ -54,12 +52,15 @@ score_paged_mean_kernel(const __grid_constant__ ScoreParams p) {
   __shared__ __align__(16) ScoreItem s_items[kMaxScoreItems];
   __shared__ __align__(8) uint64_t full_bar[kMaxStages];
   __shared__ unsigned int s_released[kMaxStages];  // warps that released each stage so far (monotonic)
+  __shared__ unsigned int s_issued[kMaxStages];    // copies armed so far, per stage barrier
   __shared__ int s_bt[kMaxPrefetchedBlocks];  // this CTA's slice of the block table
   __shared__ int s_err;
 
   const int tid = threadIdx.x;
   const int l = blockIdx.y, b = blockIdx.z;
 
+  grid_dependency_wait();  // no global access before the preceding kernel of the stream has completed
+  trigger_dependents();
   int seq_len = p.seq_lens[b];
   if (seq_len > p.t_pad) {
     if (tid == 0) flag_status(p.status, TRIATTN_DEV_BAD_LENGTH);
@@ -86,6 +87,7 @@ score_paged_mean_kernel(const __grid_constant__ ScoreParams p) {
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(smem_u32(&full_bar[s]), 1);
       s_released[s] = 0u;
+      s_issued[s] = 0u;
     }
     mbar_fence_init();
     s_err = 0;
@@ -127,7 +129,10 @@ score_paged_mean_kernel(const __grid_constant__ ScoreParams p) {
     const uint32_t bar = smem_u32(&full_bar[stage]);
     const int blk0 = (tile0 + it) * p.mb;
     const int nb = min(p.mb, nblk - blk0);
-    if (lane_id == 0) mbar_arrive_expect_tx(bar, (uint32_t)(nb * p.block_bytes));
+    if (lane_id == 0) {
+      mbar_arrive_expect_tx(bar, (uint32_t)(nb * p.block_bytes) + kTestExtraTxBytes);
+      s_issued[stage] += 1u;  // one issuer at a time: the issuers of a stage are ordered by its release counter
+    }
     __syncwarp();
     for (int j = lane_id; j < nb; j += 32) {
       int blk;
@@ -342,10 +347,12 @@ score_paged_mean_kernel(const __grid_constant__ ScoreParams p) {
   unsigned release_target = (unsigned)kScoreConsumerWarps;
   for (int it = 0; it < my_tiles; ++it) {
     // warp-uniform outcome, so that the shuffles below never see a split warp
-    const bool ready = __all_sync(kFull, mbar_wait_bounded(smem_u32(&full_bar[stage]), parity));
+    const bool ready = __all_sync(kFull, mbar_wait_bounded(smem_u32(&full_bar[stage]), parity, &s_err));
     if (!ready) {
-      s_err = 1;
-      if (lane == 0) flag_status(p.status, TRIATTN_DEV_WAIT_TIMEOUT);
+      if (lane == 0) {
+        if (s_err == 0) flag_status(p.status, TRIATTN_DEV_WAIT_TIMEOUT);
+        s_err = 1;
+      }
       break;
     }
     const unsigned tile_off = (unsigned)(stage * stage_bytes);
@@ -364,20 +371,19 @@ score_paged_mean_kernel(const __grid_constant__ ScoreParams p) {
         process_item(tile_off, s_items[live ? item : 0], tile_tok0, live, std::true_type{});
       }
     }
-    // release the stage: all lanes of this warp have consumed their shared-memory reads.  The warp whose
-    // release is the last of the 8 refills the stage with the tile `stages` ahead - nobody waits for it.
+    // Release the stage.  __syncwarp orders the warp's shared-memory reads before lane 0's acq_rel add; its
+    // acquire half covers the reads of the warps that added earlier.  The warp whose add is the last of the 8
+    // refills the stage with the tile `stages` ahead - nobody waits for it.
     __syncwarp();
     unsigned refill = 0u;
     if (lane == 0) {
-      // No memory fence: every shared-memory value this warp read from the stage has already been consumed by
-      // arithmetic (a fence here would also wait for the warp's outstanding global stores of raw scores).
-      const unsigned int done = atomicAdd(&s_released[stage], 1u) + 1u;
-      if (done == release_target && it + p.stages < my_tiles) {
-        fence_proxy_async();  // generic-proxy reads of the stage before the async-proxy refill
-        refill = 1u;
-      }
+      const unsigned int done = atom_add_acq_rel_shared(&s_released[stage], 1u) + 1u;
+      if (done == release_target && it + p.stages < my_tiles) refill = 1u;
     }
-    if (__shfl_sync(kFull, refill, 0)) issue(it + p.stages, stage, lane);
+    if (__shfl_sync(kFull, refill, 0)) {
+      fence_proxy_async();  // generic-proxy reads of the stage before this lane's async-proxy refill copies
+      issue(it + p.stages, stage, lane);
+    }
     if (++stage == p.stages) {
       stage = 0;
       parity ^= 1u;
@@ -385,6 +391,13 @@ score_paged_mean_kernel(const __grid_constant__ ScoreParams p) {
     }
   }
   flush_moments();
+  // No thread leaves while a copy may still be on its way into this CTA's shared memory: after a timeout
+  // (and only then) one lane per stage waits once more, bounded, for every copy that was armed.
+  __syncthreads();
+  if (s_err != 0 && tid < p.stages) {
+    const unsigned n = s_issued[tid];
+    if (n > 0u) mbar_wait_bounded(smem_u32(&full_bar[tid]), (n - 1u) & 1u);
+  }
 }
 
 }  // namespace triattn

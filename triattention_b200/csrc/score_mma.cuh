@@ -24,9 +24,7 @@
 
 namespace triattn {
 
-#ifndef TRIATTN_SCORE_MMA_MIN_CTAS
-#define TRIATTN_SCORE_MMA_MIN_CTAS 2
-#endif
+constexpr int kScoreMmaMinCtas = 2;  // CTAs per SM the register budget is held to
 
 constexpr int kMmaKeys = 16;  // keys per MMA tile and work item
 
@@ -66,7 +64,7 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
 // NT = column tiles of 4 query heads per virtual head (1: g <= 4, 2: g <= 8; larger groups are split into
 // virtual heads of 8 that read the same K rows).
 template <int D, bool INTERLEAVED, int NT>
-__global__ void __launch_bounds__(kScoreThreadsWS, TRIATTN_SCORE_MMA_MIN_CTAS)
+__global__ void __launch_bounds__(kScoreThreadsWS, kScoreMmaMinCtas)
 score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
   constexpr int F = D / 2;
   constexpr int NQ = D / 32;  // 16-byte chunks per key and thread: chunk index lane%4 + 4q
@@ -78,12 +76,16 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
   __shared__ __align__(8) uint64_t blk_bar[kMaxStages][kScoreConsumerWarps];  // block-group mode: one per block
   __shared__ unsigned int s_blk_released[kMaxStages][kScoreConsumerWarps];
   __shared__ unsigned int s_released[kMaxStages];
+  __shared__ unsigned int s_blk_issued[kMaxStages][kScoreConsumerWarps];  // copies armed so far, per barrier
+  __shared__ unsigned int s_issued[kMaxStages];
   __shared__ int s_bt[kMaxPrefetchedBlocks];
   __shared__ int s_err;
 
   const int tid = threadIdx.x;
   const int l = blockIdx.y, b = blockIdx.z;
 
+  grid_dependency_wait();  // no global access before the preceding kernel of the stream has completed
+  trigger_dependents();
   int seq_len = p.seq_lens[b];
   if (seq_len > p.t_pad) {
     if (tid == 0) flag_status(p.status, TRIATTN_DEV_BAD_LENGTH);
@@ -106,9 +108,11 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(smem_u32(&full_bar[s]), 1);
       s_released[s] = 0u;
+      s_issued[s] = 0u;
       for (int w = 0; w < kScoreConsumerWarps; ++w) {
         mbar_init(smem_u32(&blk_bar[s][w]), 1);
         s_blk_released[s][w] = 0u;
+        s_blk_issued[s][w] = 0u;
       }
     }
     mbar_fence_init();
@@ -135,7 +139,10 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
     const uint32_t bar = smem_u32(&full_bar[stage]);
     const int blk0 = (tile0 + it) * p.mb;
     const int nb = min(p.mb, nblk - blk0);
-    if (lane_id == 0) mbar_arrive_expect_tx(bar, (uint32_t)(nb * p.block_bytes));
+    if (lane_id == 0) {
+      mbar_arrive_expect_tx(bar, (uint32_t)(nb * p.block_bytes) + kTestExtraTxBytes);
+      s_issued[stage] += 1u;  // one issuer at a time: the issuers of a stage are ordered by its release counter
+    }
     __syncwarp();
     for (int j = lane_id; j < nb; j += 32) {
       int blk;
@@ -170,7 +177,8 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
       }
     }
     const uint32_t bar = smem_u32(&blk_bar[stage][j]);
-    mbar_arrive_expect_tx(bar, (uint32_t)p.block_bytes);
+    mbar_arrive_expect_tx(bar, (uint32_t)p.block_bytes + kTestExtraTxBytes);
+    s_blk_issued[stage][j] += 1u;
     bulk_copy_g2s(smem_u32(smem_tiles + (size_t)stage * stage_bytes + (size_t)j * p.block_bytes),
                   kbase + (long long)blk * p.block_stride_bytes, (uint32_t)p.block_bytes, bar);
   };
@@ -413,18 +421,22 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
     unsigned target = (unsigned)G;
     for (int it = 0; it < my_tiles; ++it) {
       if ((tile0 + it) * p.mb + j >= nblk) break;  // this warp's block of the tile (and of all later tiles) does not exist
-      const bool ready = __all_sync(kFull, mbar_wait_bounded(smem_u32(&blk_bar[stage][j]), parity));
+      const bool ready = __all_sync(kFull, mbar_wait_bounded(smem_u32(&blk_bar[stage][j]), parity, &s_err));
       if (!ready) {
-        s_err = 1;
-        if (lane == 0) flag_status(p.status, TRIATTN_DEV_WAIT_TIMEOUT);
+        if (lane == 0) {
+          if (s_err == 0) flag_status(p.status, TRIATTN_DEV_WAIT_TIMEOUT);
+          s_err = 1;
+        }
         break;
       }
       const int stage_tok0 = (tile0 + it) * stage_tokens;
       const int tok_end = min(seq_len - stage_tok0, stage_tokens);
       compute_item(smem_base + (uint32_t)(stage * stage_bytes), j, kvh, stage_tok0, (j + 1) * kMmaKeys <= tok_end);
+      // Hand the block back: __syncwarp orders the warp's shared-memory reads before lane 0's acq_rel add, whose
+      // acquire half covers the reads of the warps that added earlier; the warp completing the count refills.
       __syncwarp();
       if (lane == 0) {
-        const unsigned done = G == 1 ? target : atomicAdd(&s_blk_released[stage][j], 1u) + 1u;
+        const unsigned done = G == 1 ? target : atom_add_acq_rel_shared(&s_blk_released[stage][j], 1u) + 1u;
         if (done == target && it + p.stages < my_tiles) {
           fence_proxy_async();  // generic-proxy reads of the block before the async-proxy refill
           issue_block(it + p.stages, stage, j);
@@ -436,55 +448,71 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
         target += (unsigned)G;
       }
     }
-    flush_moments();
-    return;
-  }
-  unsigned release_target = (unsigned)kScoreConsumerWarps;
-  for (int it = 0; it < my_tiles; ++it) {
-    const bool ready = __all_sync(kFull, mbar_wait_bounded(smem_u32(&full_bar[stage]), parity));
-    if (!ready) {
-      s_err = 1;
-      if (lane == 0) flag_status(p.status, TRIATTN_DEV_WAIT_TIMEOUT);
-      break;
-    }
-    const uint32_t stage_addr = smem_base + (uint32_t)(stage * stage_bytes);
-    const int stage_tok0 = (tile0 + it) * stage_tokens;
-    const int tok_end = min(seq_len - stage_tok0, stage_tokens);  // keys of this stage that exist
-    if (fixed) {
-      for (int tt = tt_first; tt * kMmaKeys < tok_end; tt += tt_step)
-        compute_item(stage_addr, tt, fixed_kvh, stage_tok0, (tt + 1) * kMmaKeys <= tok_end);
-    } else {
-      for (int sl = 0; sl < slots; ++sl) {
-        const int item = wid + sl * kScoreConsumerWarps;  // warp-uniform
-        if (item >= n_items) break;
-        const int vh = item % nvh, tt = item / nvh;
-        if (tt * kMmaKeys >= tok_end) break;  // items are ordered by token
-        if (vh != cur_vh) {
-          flush_moments();
-          load_weights(vh);
-          cur_vh = vh;
+  } else {
+    unsigned release_target = (unsigned)kScoreConsumerWarps;
+    for (int it = 0; it < my_tiles; ++it) {
+      const bool ready = __all_sync(kFull, mbar_wait_bounded(smem_u32(&full_bar[stage]), parity, &s_err));
+      if (!ready) {
+        if (lane == 0) {
+          if (s_err == 0) flag_status(p.status, TRIATTN_DEV_WAIT_TIMEOUT);
+          s_err = 1;
         }
-        compute_item(stage_addr, tt, vh / nsub, stage_tok0, (tt + 1) * kMmaKeys <= tok_end);
+        break;
       }
-    }
-    // release the stage; the warp whose release is the last of the 8 refills it with the tile `stages` ahead
-    __syncwarp();
-    unsigned refill = 0u;
-    if (lane == 0) {
-      const unsigned int done = atomicAdd(&s_released[stage], 1u) + 1u;
-      if (done == release_target && it + p.stages < my_tiles) {
-        fence_proxy_async();
-        refill = 1u;
+      const uint32_t stage_addr = smem_base + (uint32_t)(stage * stage_bytes);
+      const int stage_tok0 = (tile0 + it) * stage_tokens;
+      const int tok_end = min(seq_len - stage_tok0, stage_tokens);  // keys of this stage that exist
+      if (fixed) {
+        for (int tt = tt_first; tt * kMmaKeys < tok_end; tt += tt_step)
+          compute_item(stage_addr, tt, fixed_kvh, stage_tok0, (tt + 1) * kMmaKeys <= tok_end);
+      } else {
+        for (int sl = 0; sl < slots; ++sl) {
+          const int item = wid + sl * kScoreConsumerWarps;  // warp-uniform
+          if (item >= n_items) break;
+          const int vh = item % nvh, tt = item / nvh;
+          if (tt * kMmaKeys >= tok_end) break;  // items are ordered by token
+          if (vh != cur_vh) {
+            flush_moments();
+            load_weights(vh);
+            cur_vh = vh;
+          }
+          compute_item(stage_addr, tt, vh / nsub, stage_tok0, (tt + 1) * kMmaKeys <= tok_end);
+        }
       }
-    }
-    if (__shfl_sync(kFull, refill, 0)) issue(it + p.stages, stage, lane);
-    if (++stage == p.stages) {
-      stage = 0;
-      parity ^= 1u;
-      release_target += (unsigned)kScoreConsumerWarps;
+      // release the stage; the warp whose release is the last of the 8 refills it with the tile `stages` ahead
+      __syncwarp();
+      unsigned refill = 0u;
+      if (lane == 0) {
+        const unsigned int done = atom_add_acq_rel_shared(&s_released[stage], 1u) + 1u;
+        if (done == release_target && it + p.stages < my_tiles) refill = 1u;
+      }
+      if (__shfl_sync(kFull, refill, 0)) {
+        fence_proxy_async();  // every lane issues copies: each orders the (acquired) generic reads before its own
+        issue(it + p.stages, stage, lane);
+      }
+      if (++stage == p.stages) {
+        stage = 0;
+        parity ^= 1u;
+        release_target += (unsigned)kScoreConsumerWarps;
+      }
     }
   }
   flush_moments();
+  // No thread leaves while a copy may still be on its way into this CTA's shared memory: after a timeout
+  // (and only then) the first warp waits once more, bounded, for every copy that was armed.
+  __syncthreads();
+  if (s_err != 0 && tid < 32) {
+    if (p.block_group > 0) {
+      for (int i = tid; i < p.stages * kScoreConsumerWarps; i += 32) {
+        const int s = i / kScoreConsumerWarps, w = i - s * kScoreConsumerWarps;
+        const unsigned n = s_blk_issued[s][w];
+        if (n > 0u) mbar_wait_bounded(smem_u32(&blk_bar[s][w]), (n - 1u) & 1u);
+      }
+    } else if (tid < p.stages) {
+      const unsigned n = s_issued[tid];
+      if (n > 0u) mbar_wait_bounded(smem_u32(&full_bar[tid]), (n - 1u) & 1u);
+    }
+  }
 }
 
 }  // namespace triattn

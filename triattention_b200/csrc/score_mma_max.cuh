@@ -23,10 +23,7 @@ namespace triattn {
 
 constexpr int kMaxAggWarps = 12;
 constexpr int kMaxAggThreads = kMaxAggWarps * 32;
-#ifndef MAXAGG_OFFSETS
-#define MAXAGG_OFFSETS 1
-#endif
-constexpr int kMaxAggOffsets = MAXAGG_OFFSETS;  // offsets a warp works on at once
+constexpr int kMaxAggOffsets = 1;  // offsets a warp works on at once
 constexpr int kMaxAggTiles = 2;   // 16-key tiles a warp works on at once (independent accumulator chains)
 constexpr int kMaxAggSlots = kMaxAggTiles;  // ring slots per warp: the tiles move to registers, then the slots refill
 
@@ -62,6 +59,8 @@ __global__ void __launch_bounds__(kMaxAggThreads, 1) score_paged_mma_max_kernel(
 
   const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
   const int l = blockIdx.y, b = blockIdx.z;
+  grid_dependency_wait();  // no global access before the preceding kernel of the stream has completed
+  trigger_dependents();
   const int nsub = (p.gp_total + GP - 1) / GP;
   const int nvh = p.Hkv * nsub;
   const int vh = blockIdx.x % nvh, chunk = blockIdx.x / nvh;
@@ -134,12 +133,16 @@ __global__ void __launch_bounds__(kMaxAggThreads, 1) score_paged_mma_max_kernel(
   unsigned char* my_ring = s_ring + (size_t)wid * kMaxAggSlots * SLOT_BYTES;
   constexpr unsigned kFull = 0xffffffffu;
 
+  unsigned armed[kMaxAggTiles];  // copies armed so far on each of this warp's barriers (warp-uniform)
+#pragma unroll
+  for (int t = 0; t < kMaxAggTiles; ++t) armed[t] = 0u;
   // fetch the 16 rows of this warp's tile `i` (tile index within the CTA's range): lane r copies row r
   auto fetch = [&](int i, int slot) {
+    armed[slot] += 1u;
     const int tok0 = (tile0 + i) * kMmaKeys;
     const int rows = min(kMmaKeys, seq_len - tok0);
     const uint32_t bar = smem_u32(&bars[wid][slot]);
-    if (lane == 0) mbar_arrive_expect_tx(bar, (uint32_t)(rows * ROW_BYTES));
+    if (lane == 0) mbar_arrive_expect_tx(bar, (uint32_t)(rows * ROW_BYTES) + kTestExtraTxBytes);
     __syncwarp();
     if (lane < rows) {
       const int t = tok0 + lane;
@@ -158,7 +161,9 @@ __global__ void __launch_bounds__(kMaxAggThreads, 1) score_paged_mma_max_kernel(
   // this warp's tiles: wid, wid + W, ... of the CTA's range, taken kMaxAggTiles at a time: the weight fragments
   // of an offset are loaded from shared memory once and used for all of them
   const int n_mine = my_tiles > wid ? (my_tiles - wid + kMaxAggWarps - 1) / kMaxAggWarps : 0;
-  for (int i = 0; i < min(kMaxAggTiles, n_mine); ++i) fetch(wid + i * kMaxAggWarps, i);
+#pragma unroll
+  for (int i = 0; i < kMaxAggTiles; ++i)
+    if (i < n_mine) fetch(wid + i * kMaxAggWarps, i);
 
   auto split_pair = [&](float m0, float m1, uint32_t& hi, uint32_t& lo) {
     const uint32_t u0 = __float_as_uint(m0), u1 = __float_as_uint(m1);
@@ -246,8 +251,7 @@ __global__ void __launch_bounds__(kMaxAggThreads, 1) score_paged_mma_max_kernel(
     // every shared-memory value of the slots is in registers: refill them with the next tiles of this warp
     __syncwarp();
     if (i + kMaxAggTiles < n_mine) {
-      if (lane == 0) fence_proxy_async();
-      __syncwarp();
+      fence_proxy_async();  // every lane copies a row: each orders the warp's (synchronised) reads before its own copy
 #pragma unroll
       for (int t = 0; t < kMaxAggTiles; ++t)
         if (i + kMaxAggTiles + t < n_mine) fetch(wid + (i + kMaxAggTiles + t) * kMaxAggWarps, t);
@@ -313,6 +317,13 @@ __global__ void __launch_bounds__(kMaxAggThreads, 1) score_paged_mma_max_kernel(
         }
       }
     }
+  }
+  if (failed) {
+    // a wait ran out: before leaving, wait once more (bounded) for every copy this warp armed, so that no copy
+    // is still on its way into the CTA's shared memory when the CTA retires
+#pragma unroll
+    for (int t = 0; t < kMaxAggTiles; ++t)
+      if (armed[t] > 0u) mbar_wait_bounded(smem_u32(&bars[wid][t]), (armed[t] - 1u) & 1u);
   }
   // moments of query slot rt over this warp's keys
 #pragma unroll

@@ -72,6 +72,8 @@ __global__ void __launch_bounds__(kSelectThreads) select_topk_kernel(const __gri
   __shared__ unsigned int s_prefix, s_remaining;
   __shared__ unsigned int warp_tot[32];
 
+  grid_dependency_wait();  // no global access before the preceding kernel of the stream has completed
+  trigger_dependents();
   const int row = blockIdx.x;
   const int b = (row / p.rows_inner) % p.num_reqs;
   // a length beyond the row (bad metadata) is clamped and reported, like the scorer and the compaction do

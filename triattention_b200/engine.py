@@ -59,6 +59,10 @@ class PagedCompressor:
     # has been seen twice: a decode loop compresses the same shapes over and over, and the dozen launches of a
     # small step cost more on the host than on the device.
     use_cuda_graph: bool = False
+    # Upper bound on the scratch the step may hold (None: enough to score all layers in one launch).  A worker
+    # whose HBM went to the KV pool can cap it; the step is then cut into chunks of as many layers as fit (at
+    # least one) and the results stay bit-identical.
+    max_workspace_bytes: Optional[int] = None
     _workspace: Optional[torch.Tensor] = field(default=None, repr=False)
     _staging: Optional[torch.Tensor] = field(default=None, repr=False)
     _dev_meta: Optional[torch.Tensor] = field(default=None, repr=False)
@@ -115,6 +119,9 @@ class PagedCompressor:
         layout = view.layout(B, g, max_blocks, rope_interleaved=self.stats.rope_interleaved)
         O = int(self.stats.offsets.numel())
         ws_bytes = ops.compress_workspace_bytes(layout, O, self.offset_agg, keep_pitch)
+        if self.max_workspace_bytes is not None:
+            ws_bytes = min(ws_bytes, max(int(self.max_workspace_bytes),
+                                         ops.compress_workspace_bytes_min(layout, O, self.offset_agg, keep_pitch)))
         keep_bytes = B * view.num_kv_heads * keep_pitch * 4
         # one staging buffer: block table rows, then seq_lens, round_start, keep_counts, prefill_lens, status
         n_ints = B * max_blocks + 4 * B + 4
@@ -151,7 +158,7 @@ class PagedCompressor:
             dm.copy_(st, non_blocking=True)
             ops.compress_paged(
                 view, layout, self.stats, bt, d_seq, d_rs, d_pre, d_kc, keep_pitch, self.window, self.normalize,
-                self.offset_agg, self.flags, self.layer_reduce, workspace=ws, keep_out=keep, status=d_status)
+                self.offset_agg, self.flags, self.layer_reduce, workspace=ws[:ws_bytes], keep_out=keep, status=d_status)
             self._status_host.copy_(d_status, non_blocking=True)
 
         if not self.use_cuda_graph:
@@ -161,7 +168,7 @@ class PagedCompressor:
             sp = self.stats
             key = (int(view.k_ptrs.data_ptr()), int(view.v_ptrs.data_ptr()), view.num_layers, view.num_blocks,
                    view.block_stride, view.token_stride, view.head_stride, B, max_blocks, keep_pitch,
-                   prefill_lens is not None, int(st.data_ptr()), int(ws.data_ptr()),
+                   prefill_lens is not None, int(st.data_ptr()), int(ws.data_ptr()), int(ws_bytes),
                    int(sp.q_mean_real.data_ptr()), int(sp.q_mean_imag.data_ptr()), int(sp.q_abs_mean.data_ptr()),
                    int(sp.freq_scale_sq.data_ptr()), int(sp.omega.data_ptr()), int(sp.offsets.data_ptr()),
                    bool(sp.rope_interleaved), int(self.window), bool(self.normalize), int(self.offset_agg),

@@ -200,11 +200,30 @@ def prep_weights(stats: DeviceStats, round_start: torch.Tensor, offset_agg: int 
     return out
 
 
+def prep_weights_fused(stats: DeviceStats, round_start: torch.Tensor, offset_agg: int = _native.OFFSETS_MEAN,
+                       flags: int = 0, moments_to_clear: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``triattn_prep_weights`` in one launch, no scratch (``triattn_prep_weights_fused``); optionally zeroes
+    the ``[L, B, Hq, 2]`` fp64 moments array the scorer accumulates into."""
+    lib = _native.load()
+    _require_cuda(stats.q_mean_real, "stats")
+    dev = stats.q_mean_real.device
+    rs = _i32(round_start, dev)
+    L, Hq, F = stats.num_layers, stats.num_heads, stats.num_freqs
+    B, O = int(rs.numel()), int(stats.offsets.numel())
+    out = torch.empty((L, B, Hq, lib.triattn_weight_rows(offset_agg, O), F), dtype=torch.float32, device=dev)
+    _native.check(lib.triattn_prep_weights_fused(
+        _ptr(stats.q_mean_real), _ptr(stats.q_mean_imag), _ptr(stats.q_abs_mean), _ptr(stats.freq_scale_sq),
+        _ptr(stats.omega), _ptr(stats.offsets), _ptr(rs), L, B, Hq, F, O, offset_agg, flags, _ptr(out),
+        _ptr(moments_to_clear), _stream()), "prep_weights_fused")
+    return out
+
+
 def score_paged(view: PagedCacheView, layout: PagedLayout, block_table: torch.Tensor, seq_lens: torch.Tensor,
                 weights: torch.Tensor, offset_agg: int = _native.OFFSETS_MEAN, num_offsets: int = 17,
                 status: Optional[torch.Tensor] = None, raw: Optional[torch.Tensor] = None,
-                moments: Optional[torch.Tensor] = None):
-    """Raw scores ``[L, B, Hkv, t_pad, Gp]`` fp32 and moments ``[L, B, Hq, 2]`` fp64 (``triattn_score_paged``)."""
+                moments: Optional[torch.Tensor] = None, cuda_cores: bool = False):
+    """Raw scores ``[L, B, Hkv, t_pad, Gp]`` fp32 and moments ``[L, B, Hq, 2]`` fp64 (``triattn_score_paged``;
+    ``cuda_cores=True`` calls the all-fp32 cross-check ``triattn_score_paged_cuda_cores``)."""
     lib = _native.load()
     gp = lib.triattn_padded_group(layout.group_size)
     if gp == 0:
@@ -216,7 +235,8 @@ def score_paged(view: PagedCacheView, layout: PagedLayout, block_table: torch.Te
         raw = torch.empty((L, B, Hkv, t_pad, gp), dtype=torch.float32, device=dev)
     if moments is None:
         moments = torch.empty((L, B, Hkv * layout.group_size, 2), dtype=torch.float64, device=dev)
-    _native.check(lib.triattn_score_paged(
+    fn = lib.triattn_score_paged_cuda_cores if cuda_cores else lib.triattn_score_paged
+    _native.check(fn(
         ctypes.byref(layout), _ptr(view.k_ptrs), _ptr(block_table), _ptr(seq_lens), _ptr(weights),
         offset_agg, num_offsets, _ptr(raw), _ptr(moments), _ptr(status), _stream()), "score_paged")
     return raw, moments
@@ -237,10 +257,9 @@ def finalize_scores(layout: PagedLayout, raw: torch.Tensor, moments: torch.Tenso
     Ho = Hkv if head_reduce == _native.REDUCE_NONE else 1
     dev = raw.device
     out = torch.full((Lo, B, Ho, t_pad), float("-inf"), dtype=torch.float32, device=dev)
-    ms = torch.empty((L, B, Hkv * layout.group_size, 2), dtype=torch.float32, device=dev)
     _native.check(lib.triattn_finalize_scores(
         ctypes.byref(layout), _ptr(raw), _ptr(moments), _ptr(seq_lens), _ptr(prefill_lens), int(window),
-        1 if normalize else 0, group_reduce, head_reduce, layer_reduce, _ptr(ms), _ptr(out), _stream()),
+        1 if normalize else 0, group_reduce, head_reduce, layer_reduce, _ptr(out), _stream()),
         "finalize_scores")
     return out
 
@@ -284,7 +303,13 @@ def compact_paged(view: PagedCacheView, layout: PagedLayout, block_table: torch.
 
 
 def compress_workspace_bytes(layout: PagedLayout, num_offsets: int, offset_agg: int, keep_pitch: int) -> int:
+    """Workspace with which the fused step scores all layers in one launch."""
     return int(_native.load().triattn_compress_workspace_bytes(ctypes.byref(layout), num_offsets, offset_agg, keep_pitch))
+
+
+def compress_workspace_bytes_min(layout: PagedLayout, num_offsets: int, offset_agg: int, keep_pitch: int) -> int:
+    """Smallest workspace the fused step accepts (raw scores of one layer at a time)."""
+    return int(_native.load().triattn_compress_workspace_bytes_min(ctypes.byref(layout), num_offsets, offset_agg, keep_pitch))
 
 
 def compress_paged(view: PagedCacheView, layout: PagedLayout, stats: DeviceStats, block_table: torch.Tensor,
@@ -296,9 +321,9 @@ def compress_paged(view: PagedCacheView, layout: PagedLayout, stats: DeviceStats
     """The fused default-mode step (``triattn_compress_paged``); returns keep ``[B, Hkv, keep_pitch]`` int32."""
     lib = _native.load()
     O = int(stats.offsets.numel())
-    need = compress_workspace_bytes(layout, O, offset_agg, keep_pitch)
-    if workspace is None or workspace.numel() < need:
-        workspace = torch.empty(need, dtype=torch.uint8, device=view.device)
+    if workspace is None:
+        workspace = torch.empty(compress_workspace_bytes(layout, O, offset_agg, keep_pitch), dtype=torch.uint8,
+                                device=view.device)
     if keep_out is None:
         keep_out = torch.empty((layout.num_reqs, layout.num_kv_heads, keep_pitch), dtype=torch.int32, device=view.device)
     _native.check(lib.triattn_compress_paged(
