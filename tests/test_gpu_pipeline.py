@@ -281,3 +281,27 @@ def test_reference_outputs_with_shipped_statistics(manifest):
     caches, block_ids = build_stats_case(p, inv)
     _device_keep_vs_reference(stats, caches, block_ids, p, torch.from_numpy(z["gpt_oss_yarn/keep"]).long(),
                               p["cache_out_sha256"], range(p["num_layers"]))
+
+
+@pytest.mark.parametrize("g,hkv", [(4, 8), (8, 2)])
+def test_results_do_not_depend_on_the_batch(g, hkv):
+    """A request gives bit-identical keep sets and caches whether it is compressed alone or next to other requests
+    (the moments are accumulated so that they do not depend on how the keys were split over CTAs)."""
+    L, D = 3, 128
+    lens, budget, window = [2176, 9000, 5000, 2176, 300], [2048, 2048, 1024, 2048, 128], 128
+    stats, caches, ids, _ = _build_case(L, hkv * g, hkv, D, lens, seed=4242 + g)
+    ds = device_stats(stats, oracle.geometric_offsets())
+    starts = [t + 17 for t in lens]
+    batch = [c.to(DEV) for c in caches]
+    res = engine.PagedCompressor(ds, window=window).compress(ops.PagedCacheView.from_layers(batch, kv_axis=0), ids, lens,
+                                                             starts, budget)
+    assert res.device_status == 0
+    keep_b = res.keep.clone()
+    solo = [c.to(DEV) for c in caches]
+    view = ops.PagedCacheView.from_layers(solo, kv_axis=0)
+    comp = engine.PagedCompressor(ds, window=window)
+    for b in range(len(lens)):
+        r = comp.compress(view, [ids[b]], [lens[b]], [starts[b]], [budget[b]])
+        assert r.device_status == 0
+        assert torch.equal(r.keep[0, :, :budget[b]], keep_b[b, :, :budget[b]]), b
+    assert all(torch.equal(a, b) for a, b in zip(batch, solo))

@@ -36,6 +36,36 @@ __device__ __forceinline__ float sqrt_approx(float x) {
 __device__ __forceinline__ float2 bf16x2_to_float2(uint32_t w) {
   return make_float2(__uint_as_float(__byte_perm(w, 0u, 0x1044u)), __uint_as_float(__byte_perm(w, 0u, 0x3244u)));
 }
+// |k|^2 of two frequencies at once: `re` and `im` hold the bf16 pairs (re_f, re_f') and (im_f, im_f').
+// fma.rn.f32.bf16 multiplies two bf16 values exactly and accumulates in fp32, so the pairs need no unpacking
+// (re*re is rounded once, im*im is fused into it - the same two roundings as an fp32 mul followed by an fma).
+__device__ __forceinline__ float2 sq_mag_bf16x2(uint32_t re, uint32_t im) {
+  float2 m;
+  asm("{\n\t.reg .b16 rl, rh, il, ih;\n\t"
+      "mov.b32 {rl, rh}, %2;\n\tmov.b32 {il, ih}, %3;\n\t"
+      "fma.rn.f32.bf16 %0, rl, rl, 0f00000000;\n\tfma.rn.f32.bf16 %0, il, il, %0;\n\t"
+      "fma.rn.f32.bf16 %1, rh, rh, 0f00000000;\n\tfma.rn.f32.bf16 %1, ih, ih, %1;\n\t}"
+      : "=f"(m.x), "=f"(m.y)
+      : "r"(re), "r"(im));
+  return m;
+}
+// |k|^2 of ONE frequency whose (re, im) sit in the two halves of `w` (interleaved RoPE layout).
+__device__ __forceinline__ float sq_mag_bf16_pair(uint32_t w) {
+  float m;
+  asm("{\n\t.reg .b16 r, i;\n\t"
+      "mov.b32 {r, i}, %1;\n\t"
+      "fma.rn.f32.bf16 %0, r, r, 0f00000000;\n\tfma.rn.f32.bf16 %0, i, i, %0;\n\t}"
+      : "=f"(m)
+      : "r"(w));
+  return m;
+}
+__device__ __forceinline__ float2 fsub2(float2 a, float2 b) {
+  float2 d;
+  asm("sub.rn.f32x2 %0, %1, %2;"
+      : "=l"(reinterpret_cast<uint64_t&>(d))
+      : "l"(reinterpret_cast<uint64_t&>(a)), "l"(reinterpret_cast<uint64_t&>(b)));
+  return d;
+}
 __device__ __forceinline__ float bf16_to_float(uint16_t h) { return __uint_as_float(((uint32_t)h) << 16); }
 
 // ---------------------------------------------------------------- mbarrier + bulk copy
@@ -105,14 +135,39 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   }
   return false;
 }
-// Release/acquire counter in shared memory.  A warp that has finished reading a buffer calls __syncwarp() and
-// then one lane adds 1 with acq_rel semantics: the release half publishes the warp's reads, the acquire half
-// makes the reads of every warp that added before visible-as-done to the adder, so the warp whose add completes
-// the count may hand the buffer back to the async proxy (fence.proxy.async, then the bulk copy).
-__device__ __forceinline__ unsigned atom_add_acq_rel_shared(unsigned* counter, unsigned v) {
-  unsigned old;
-  asm volatile("atom.acq_rel.cta.shared::cta.add.u32 %0, [%1], %2;" : "=r"(old) : "r"(smem_u32(counter)), "r"(v) : "memory");
-  return old;
+// "Last reader refills": the warps that read a shared-memory buffer count themselves out on an mbarrier whose
+// expected count is the number of reader warps.  A warp that is done calls __syncwarp() (orders its lanes' reads
+// before lane 0) and lane 0 arrives with release semantics.  The state an arrive returns describes the barrier
+// BEFORE that arrive, so a pending count of 1 means this arrive completed the phase: that warp is the last
+// reader.  Its test_wait on the completed phase (acquire) then orders every reader's loads before what follows:
+// fence.proxy.async and the bulk copy that overwrites the buffer.  The barrier re-arms itself for the next round.
+__device__ __forceinline__ uint64_t mbar_arrive_release(uint32_t bar) {
+  uint64_t state;
+  asm volatile("mbarrier.arrive.release.cta.shared::cta.b64 %0, [%1];" : "=l"(state) : "r"(bar) : "memory");
+  return state;
+}
+__device__ __forceinline__ uint32_t mbar_pending_count(uint64_t state) {
+  uint32_t n;
+  asm volatile("mbarrier.pending_count.b64 %0, %1;" : "=r"(n) : "l"(state));
+  return n;
+}
+__device__ __forceinline__ bool mbar_test_wait_acquire(uint32_t bar, uint64_t state) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.acquire.cta.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "l"(state)
+      : "memory");
+  return ok != 0;
+}
+// true for exactly one caller per round: the reader whose arrive was the last of the round
+__device__ __forceinline__ bool release_and_check_last(uint32_t empty_bar) {
+  const uint64_t state = mbar_arrive_release(empty_bar);
+  if (mbar_pending_count(state) != 1u) return false;
+  mbar_test_wait_acquire(empty_bar, state);  // the phase this arrive completed: acquires the other readers' releases
+  return true;
 }
 
 // ---------------------------------------------------------------- programmatic dependent launch

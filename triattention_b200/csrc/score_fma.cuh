@@ -51,7 +51,7 @@ score_paged_mean_kernel(const __grid_constant__ ScoreParams p) {
   extern __shared__ __align__(128) unsigned char smem_tiles[];
   __shared__ __align__(16) ScoreItem s_items[kMaxScoreItems];
   __shared__ __align__(8) uint64_t full_bar[kMaxStages];
-  __shared__ unsigned int s_released[kMaxStages];  // warps that released each stage so far (monotonic)
+  __shared__ __align__(8) uint64_t empty_bar[kMaxStages];  // reader warps done with each stage
   __shared__ unsigned int s_issued[kMaxStages];    // copies armed so far, per stage barrier
   __shared__ int s_bt[kMaxPrefetchedBlocks];  // this CTA's slice of the block table
   __shared__ int s_err;
@@ -86,7 +86,7 @@ score_paged_mean_kernel(const __grid_constant__ ScoreParams p) {
   if (tid == 0) {
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(smem_u32(&full_bar[s]), 1);
-      s_released[s] = 0u;
+      mbar_init(smem_u32(&empty_bar[s]), kScoreConsumerWarps);
       s_issued[s] = 0u;
     }
     mbar_fence_init();
@@ -131,7 +131,7 @@ score_paged_mean_kernel(const __grid_constant__ ScoreParams p) {
     const int nb = min(p.mb, nblk - blk0);
     if (lane_id == 0) {
       mbar_arrive_expect_tx(bar, (uint32_t)(nb * p.block_bytes) + kTestExtraTxBytes);
-      s_issued[stage] += 1u;  // one issuer at a time: the issuers of a stage are ordered by its release counter
+      s_issued[stage] += 1u;  // one issuer at a time: the issuers of a stage are ordered by its reader barrier
     }
     __syncwarp();
     for (int j = lane_id; j < nb; j += 32) {
@@ -344,7 +344,6 @@ score_paged_mean_kernel(const __grid_constant__ ScoreParams p) {
   }
   int stage = 0;
   uint32_t parity = 0;
-  unsigned release_target = (unsigned)kScoreConsumerWarps;
   for (int it = 0; it < my_tiles; ++it) {
     // warp-uniform outcome, so that the shuffles below never see a split warp
     const bool ready = __all_sync(kFull, mbar_wait_bounded(smem_u32(&full_bar[stage]), parity, &s_err));
@@ -371,15 +370,11 @@ score_paged_mean_kernel(const __grid_constant__ ScoreParams p) {
         process_item(tile_off, s_items[live ? item : 0], tile_tok0, live, std::true_type{});
       }
     }
-    // Release the stage.  __syncwarp orders the warp's shared-memory reads before lane 0's acq_rel add; its
-    // acquire half covers the reads of the warps that added earlier.  The warp whose add is the last of the 8
-    // refills the stage with the tile `stages` ahead - nobody waits for it.
+    // Release the stage: the warp whose release is the last of the 8 refills it with the tile `stages` ahead -
+    // nobody waits for it.
     __syncwarp();
     unsigned refill = 0u;
-    if (lane == 0) {
-      const unsigned int done = atom_add_acq_rel_shared(&s_released[stage], 1u) + 1u;
-      if (done == release_target && it + p.stages < my_tiles) refill = 1u;
-    }
+    if (lane == 0 && release_and_check_last(smem_u32(&empty_bar[stage])) && it + p.stages < my_tiles) refill = 1u;
     if (__shfl_sync(kFull, refill, 0)) {
       fence_proxy_async();  // generic-proxy reads of the stage before this lane's async-proxy refill copies
       issue(it + p.stages, stage, lane);
@@ -387,7 +382,6 @@ score_paged_mean_kernel(const __grid_constant__ ScoreParams p) {
     if (++stage == p.stages) {
       stage = 0;
       parity ^= 1u;
-      release_target += (unsigned)kScoreConsumerWarps;
     }
   }
   flush_moments();

@@ -2,9 +2,14 @@
 //
 // With the offsets folded into per-frequency weights the score of a key for the query heads of its KV head is
 // a small matrix product: [16 keys x 3F] x [3F x heads], where the 3F entries are re(k), im(k) and |k|.
-//   * Keys are the A operand (M = 16 keys per MMA), weights the B operand: the 8 output columns of an MMA are
-//     4 query heads x {high, low} part of the fp32 weight (column n = 2*head + part; bf16 high part and bf16 of
-//     the remainder, accurate to ~2^-17).  A KV head with 5..8 query heads uses two such column tiles.
+//   * g <= 4: keys are the A operand (M = 16 keys per MMA), weights the B operand: the 8 output columns of an
+//     MMA are 4 query heads x {high, low} part of the fp32 weight (column n = 2*head + part; bf16 high part and
+//     bf16 of the remainder, accurate to ~2^-17).
+//   * 5 <= g <= 8 (per virtual head of 8): the product is transposed.  The weights are the A operand - M = 16
+//     rows = 8 query heads x {high, low} part, loop-invariant registers - and 8 keys are the B operand, whose
+//     two registers per thread are adjacent words of ONE 16-byte shared-memory load of one key row, so no
+//     register is moved between the load and the MMA (with keys as the A operand every A quad interleaves the
+//     words of two loads, which cost 57 moves per 16 keys and made this shape issue-bound).
 //   * re / im are the cached bf16 values themselves, so they go from shared memory into the MMA unchanged.
 //   * |k| = sqrt(re^2 + im^2) is computed in fp32 on the CUDA cores and split into a bf16 high part (by
 //     truncation) and the bf16 of the exact remainder; both parts extend the K dimension of the magnitude MMAs.
@@ -74,8 +79,8 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
   extern __shared__ __align__(128) unsigned char smem_tiles[];
   __shared__ __align__(8) uint64_t full_bar[kMaxStages];
   __shared__ __align__(8) uint64_t blk_bar[kMaxStages][kScoreConsumerWarps];  // block-group mode: one per block
-  __shared__ unsigned int s_blk_released[kMaxStages][kScoreConsumerWarps];
-  __shared__ unsigned int s_released[kMaxStages];
+  __shared__ __align__(8) uint64_t empty_bar[kMaxStages];                           // readers done, per stage
+  __shared__ __align__(8) uint64_t blk_empty_bar[kMaxStages][kScoreConsumerWarps];  // readers done, per block
   __shared__ unsigned int s_blk_issued[kMaxStages][kScoreConsumerWarps];  // copies armed so far, per barrier
   __shared__ unsigned int s_issued[kMaxStages];
   __shared__ int s_bt[kMaxPrefetchedBlocks];
@@ -107,11 +112,11 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
   if (tid == 0) {
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(smem_u32(&full_bar[s]), 1);
-      s_released[s] = 0u;
+      mbar_init(smem_u32(&empty_bar[s]), kScoreConsumerWarps);
       s_issued[s] = 0u;
       for (int w = 0; w < kScoreConsumerWarps; ++w) {
         mbar_init(smem_u32(&blk_bar[s][w]), 1);
-        s_blk_released[s][w] = 0u;
+        mbar_init(smem_u32(&blk_empty_bar[s][w]), (uint32_t)max(p.block_group, 1));
         s_blk_issued[s][w] = 0u;
       }
     }
@@ -141,7 +146,7 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
     const int nb = min(p.mb, nblk - blk0);
     if (lane_id == 0) {
       mbar_arrive_expect_tx(bar, (uint32_t)(nb * p.block_bytes) + kTestExtraTxBytes);
-      s_issued[stage] += 1u;  // one issuer at a time: the issuers of a stage are ordered by its release counter
+      s_issued[stage] += 1u;  // one issuer at a time: the issuers of a stage are ordered by its reader barrier
     }
     __syncwarp();
     for (int j = lane_id; j < nb; j += 32) {
@@ -203,16 +208,38 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
   // weight fragments (B operands) of the current virtual head, permuted to the chunk order of the loads
   uint32_t bri[NT][NQ][2][2];  // re/im: [column tile][chunk][half of the chunk][b0, b1]
   uint32_t bmg[NT][NQ][2];     // magnitude: [column tile][4 consecutive frequencies][b0, b1]
+  // transposed form (NT == 2): A fragments of query head rg, rows rg (high part) and rg + 8 (low part)
+  uint32_t ari[NQ][2][4];      // re/im: [chunk][half of the chunk][a0..a3]
+  uint32_t amg[NQ][4];         // magnitude: [4 consecutive frequencies][a0..a3]
   int cur_vh = -1, cur_qbase = 0, cur_nq = 0;
-  float s1[NT], s2[NT];  // running sum / sum of squares of query slot 4*nt + rt over this thread's keys
+  // Running sum / sum of squares of this thread's query slot(s) over its keys, in double: the scores of one
+  // 16-key tile are summed in fp32 in a fixed order, and a double accumulates such fp32 sums exactly, so the
+  // moments - and with them every later stage - do not depend on how the tiles were split over CTAs and warps
+  // (the same request gives the same keep set whatever else is in the batch).
+  double s1[NT], s2[NT];
 #pragma unroll
-  for (int nt = 0; nt < NT; ++nt) s1[nt] = s2[nt] = 0.f;
+  for (int nt = 0; nt < NT; ++nt) s1[nt] = s2[nt] = 0.0;
   float* raw_head = nullptr;
   const uint32_t smem_base = smem_u32(smem_tiles);
   const int gp_total = p.gp_total;
 
   auto flush_moments = [&]() {
     if (cur_vh < 0) return;
+    if constexpr (NT == 2) {
+      // the thread's sums belong to query head rg: combine the 4 lanes of the head, one atomic pair per head
+      s1[0] += __shfl_xor_sync(kFull, s1[0], 1);
+      s2[0] += __shfl_xor_sync(kFull, s2[0], 1);
+      s1[0] += __shfl_xor_sync(kFull, s1[0], 2);
+      s2[0] += __shfl_xor_sync(kFull, s2[0], 2);
+      // (sums of squares round in double; their order over lanes is fixed)
+      if (rt == 0 && rg < cur_nq) {
+        double* m = p.moments + (((size_t)l * p.B + b) * Hq + (size_t)cur_qbase + rg) * 2;
+        atomicAdd(m, s1[0]);
+        atomicAdd(m + 1, s2[0]);
+      }
+      s1[0] = s2[0] = 0.0;
+      return;
+    }
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
@@ -222,11 +249,11 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
       }
       if (lane < 4 && 4 * nt + lane < cur_nq) {
         double* m = p.moments + (((size_t)l * p.B + b) * Hq + (size_t)cur_qbase + 4 * nt + lane) * 2;
-        atomicAdd(m, (double)s1[nt]);
-        atomicAdd(m + 1, (double)s2[nt]);
+        atomicAdd(m, s1[nt]);
+        atomicAdd(m + 1, s2[nt]);
       }
-      s1[nt] = 0.f;
-      s2[nt] = 0.f;
+      s1[nt] = 0.0;
+      s2[nt] = 0.0;
     }
   };
   // 4 consecutive weights starting at w -> this thread's column part, packed as (b0, b1)
@@ -245,6 +272,45 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
     const int kvh = vh / nsub, sub = vh - kvh * nsub;
     cur_qbase = kvh * p.g + sub * GP;
     cur_nq = min(GP, p.g - sub * GP);
+    if constexpr (NT == 2) {
+      // rows rg / rg + 8 of every A fragment: high / low bf16 part of query head rg's weights
+      const bool on = rg < cur_nq;
+      const float* w = p.weights + ((((size_t)l * p.B + b) * Hq + (size_t)cur_qbase + (on ? rg : 0)) * 3) * F;
+      auto pack4 = [&](const float (&x)[4], uint32_t (&a)[4]) {
+        uint32_t hi[4], lo[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) bf16_split(on ? x[e] : 0.f, hi[e], lo[e]);
+        a[0] = hi[0] | (hi[1] << 16);  // row rg,     k = 2t, 2t+1
+        a[1] = lo[0] | (lo[1] << 16);  // row rg + 8, k = 2t, 2t+1
+        a[2] = hi[2] | (hi[3] << 16);  // row rg,     k = 2t+8, 2t+9
+        a[3] = lo[2] | (lo[3] << 16);  // row rg + 8, k = 2t+8, 2t+9
+      };
+#pragma unroll
+      for (int c = 0; c < NQ; ++c)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int d0 = 8 * (rt + 4 * c) + 4 * h;
+          float x[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int d = d0 + e;
+            x[e] = INTERLEAVED ? __ldg(w + (d & 1) * F + (d >> 1)) : __ldg(w + d);
+          }
+          pack4(x, ari[c][h]);
+        }
+      const float* wm = w + 2 * F;
+#pragma unroll
+      for (int j = 0; j < NQ; ++j) {
+        const int f0 = INTERLEAVED ? 4 * (rt + 4 * j) : 8 * (rt + 4 * (j >> 1)) + 4 * (j & 1);
+        float x[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) x[e] = __ldg(wm + f0 + e);
+        pack4(x, amg[j]);
+      }
+      // the thread's results: query head rg, keys 2*rt and 2*rt + 1 of each 8-key group
+      raw_head = p.raw + (((size_t)l * p.B + b) * p.Hkv + kvh) * (size_t)p.t_pad * gp_total + sub * GP + rg;
+      return;
+    }
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
       const int head = 4 * nt + b_head;
@@ -292,6 +358,105 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
     const int tkA = tt * kMmaKeys + rg, tkB = tkA + 8;
     const uint32_t rowA = stage_addr + row_offset(min(tkA, stage_tokens - 1), kvh) + 16u * rt;
     const uint32_t rowB = stage_addr + row_offset(min(tkB, stage_tokens - 1), kvh) + 16u * rt;
+    if constexpr (NT == 2) {
+      // Transposed form.  Group A = keys tt*16 + 0..7, group B = keys tt*16 + 8..15; this thread feeds key rg of each
+      // group as column rg of the B operand and ends with query head rg's score for keys 2*rt, 2*rt + 1 of each group.
+      float accA[2][4], accB[2][4];
+#pragma unroll
+      for (int ch = 0; ch < 2; ++ch)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) accA[ch][e] = accB[ch][e] = 0.f;
+      auto mma_t = [&](float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+        mma_bf16_16816(d, a[0], a[1], a[2], a[3], b0, b1);
+      };
+      auto split_pair = [&](float m0, float m1, uint32_t& hi, uint32_t& lo) {
+        const uint32_t u0 = __float_as_uint(m0), u1 = __float_as_uint(m1);
+        hi = __byte_perm(u0, u1, 0x7632);
+        const float2 r = fsub2(make_float2(m0, m1), make_float2(__uint_as_float(u0 & 0xffff0000u), __uint_as_float(u1 & 0xffff0000u)));
+        lo = pack_bf16x2_rn(r.x, r.y);
+      };
+      if constexpr (!INTERLEAVED) {
+#pragma unroll
+        for (int q = 0; q < NQ / 2; ++q) {
+          constexpr int QI = NQ / 2;
+          const uint4 reA = lds128(rowA + 64u * q), reB = lds128(rowB + 64u * q);
+          const uint4 imA = lds128(rowA + 64u * q + D), imB = lds128(rowB + 64u * q + D);
+          mma_t(accA[0], ari[q][0], reA.x, reA.y);
+          mma_t(accB[0], ari[q][0], reB.x, reB.y);
+          mma_t(accA[1], ari[q][1], reA.z, reA.w);
+          mma_t(accB[1], ari[q][1], reB.z, reB.w);
+          mma_t(accA[0], ari[q + QI][0], imA.x, imA.y);
+          mma_t(accB[0], ari[q + QI][0], imB.x, imB.y);
+          mma_t(accA[1], ari[q + QI][1], imA.z, imA.w);
+          mma_t(accB[1], ari[q + QI][1], imB.z, imB.w);
+          const uint32_t rA[4] = {reA.x, reA.y, reA.z, reA.w}, rB[4] = {reB.x, reB.y, reB.z, reB.w};
+          const uint32_t iA[4] = {imA.x, imA.y, imA.z, imA.w}, iB[4] = {imB.x, imB.y, imB.z, imB.w};
+          uint32_t hA[4], lA[4], hB[4], lB[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 ma = sq_mag_bf16x2(rA[i], iA[i]);
+            const float2 mb = sq_mag_bf16x2(rB[i], iB[i]);
+            split_pair(sqrt_approx(ma.x), sqrt_approx(ma.y), hA[i], lA[i]);
+            split_pair(sqrt_approx(mb.x), sqrt_approx(mb.y), hB[i], lB[i]);
+          }
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            const int j = 2 * q + hh;
+            mma_t(accA[hh], amg[j], hA[2 * hh], hA[2 * hh + 1]);
+            mma_t(accB[hh], amg[j], hB[2 * hh], hB[2 * hh + 1]);
+            mma_t(accA[hh ^ 1], amg[j], lA[2 * hh], lA[2 * hh + 1]);
+            mma_t(accB[hh ^ 1], amg[j], lB[2 * hh], lB[2 * hh + 1]);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < NQ; ++c) {
+          const uint4 xA = lds128(rowA + 64u * c), xB = lds128(rowB + 64u * c);
+          mma_t(accA[0], ari[c][0], xA.x, xA.y);
+          mma_t(accB[0], ari[c][0], xB.x, xB.y);
+          mma_t(accA[1], ari[c][1], xA.z, xA.w);
+          mma_t(accB[1], ari[c][1], xB.z, xB.w);
+          const uint32_t wA[4] = {xA.x, xA.y, xA.z, xA.w}, wB[4] = {xB.x, xB.y, xB.z, xB.w};
+          float mA[4], mB[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            mA[i] = sqrt_approx(sq_mag_bf16_pair(wA[i]));
+            mB[i] = sqrt_approx(sq_mag_bf16_pair(wB[i]));
+          }
+          uint32_t hA[2], lA[2], hB[2], lB[2];
+          split_pair(mA[0], mA[1], hA[0], lA[0]);
+          split_pair(mA[2], mA[3], hA[1], lA[1]);
+          split_pair(mB[0], mB[1], hB[0], lB[0]);
+          split_pair(mB[2], mB[3], hB[1], lB[1]);
+          mma_t(accA[0], amg[c], hA[0], hA[1]);
+          mma_t(accB[0], amg[c], hB[0], hB[1]);
+          mma_t(accA[1], amg[c], lA[0], lA[1]);
+          mma_t(accB[1], amg[c], lB[0], lB[1]);
+        }
+      }
+      // d0/d1 = row rg (high part), d2/d3 = row rg + 8 (low part), columns = keys 2*rt, 2*rt + 1
+      if (rg < cur_nq) {
+        const int k0 = tt * kMmaKeys + 2 * rt;  // first of this thread's keys in group A, relative to the stage
+        const float sc[4] = {(accA[0][0] + accA[1][0]) + (accA[0][2] + accA[1][2]),
+                             (accA[0][1] + accA[1][1]) + (accA[0][3] + accA[1][3]),
+                             (accB[0][0] + accB[1][0]) + (accB[0][2] + accB[1][2]),
+                             (accB[0][1] + accB[1][1]) + (accB[0][3] + accB[1][3])};
+        float t1 = 0.f, t2 = 0.f;  // this tile's share, fixed order
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int tk = k0 + (e & 1) + 8 * (e >> 1);
+          const int gk = stage_tok0 + tk;
+          if (full || (tk < stage_tokens && gk < seq_len)) {
+            raw_head[(size_t)gk * gp_total] = sc[e];
+            t1 += sc[e];
+            t2 = fmaf(sc[e], sc[e], t2);
+          }
+        }
+        s1[0] += (double)t1;
+        s2[0] += (double)t2;
+      }
+      return;
+    }
     constexpr int NCH = NT == 1 ? 2 : 1;  // accumulator chains per column tile (two independent chains in total)
     float acc[NT][NCH][4];
 #pragma unroll
@@ -305,7 +470,8 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
     auto split_pair = [&](float m0, float m1, uint32_t& hi, uint32_t& lo) {
       const uint32_t u0 = __float_as_uint(m0), u1 = __float_as_uint(m1);
       hi = __byte_perm(u0, u1, 0x7632);
-      lo = pack_bf16x2_rn(m0 - __uint_as_float(u0 & 0xffff0000u), m1 - __uint_as_float(u1 & 0xffff0000u));
+      const float2 r = fsub2(make_float2(m0, m1), make_float2(__uint_as_float(u0 & 0xffff0000u), __uint_as_float(u1 & 0xffff0000u)));
+      lo = pack_bf16x2_rn(r.x, r.y);
     };
 
     if constexpr (!INTERLEAVED) {
@@ -326,10 +492,8 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
         uint32_t hA[4], lA[4], hB[4], lB[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const float2 ra = bf16x2_to_float2(rA[i]), ia = bf16x2_to_float2(iA[i]);
-          const float2 rb = bf16x2_to_float2(rB[i]), ib = bf16x2_to_float2(iB[i]);
-          const float2 ma = ffma2(ia, ia, fmul2(ra, ra));
-          const float2 mb = ffma2(ib, ib, fmul2(rb, rb));
+          const float2 ma = sq_mag_bf16x2(rA[i], iA[i]);
+          const float2 mb = sq_mag_bf16x2(rB[i], iB[i]);
           split_pair(sqrt_approx(ma.x), sqrt_approx(ma.y), hA[i], lA[i]);
           split_pair(sqrt_approx(mb.x), sqrt_approx(mb.y), hB[i], lB[i]);
         }
@@ -357,10 +521,8 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
         float mA[4], mB[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const float2 va = bf16x2_to_float2(wA[i]), vb = bf16x2_to_float2(wB[i]);
-          const float2 pa = fmul2(va, va), pb = fmul2(vb, vb);
-          mA[i] = sqrt_approx(pa.x + pa.y);
-          mB[i] = sqrt_approx(pb.x + pb.y);
+          mA[i] = sqrt_approx(sq_mag_bf16_pair(wA[i]));
+          mB[i] = sqrt_approx(sq_mag_bf16_pair(wB[i]));
         }
         uint32_t hA[2], lA[2], hB[2], lB[2];
         split_pair(mA[0], mA[1], hA[0], lA[0]);
@@ -390,16 +552,19 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
       const float scB = c4[2] + c4[3];
       if (4 * nt + rt < cur_nq) {
         float* out = raw_head + (size_t)gA * gp_total + 4 * nt;
+        float t1 = 0.f, t2 = 0.f;  // this tile's share, fixed order
         if (okA) {
           out[0] = scA;
-          s1[nt] += scA;
-          s2[nt] = fmaf(scA, scA, s2[nt]);
+          t1 = scA;
+          t2 = scA * scA;
         }
         if (okB) {
           out[(size_t)8 * gp_total] = scB;
-          s1[nt] += scB;
-          s2[nt] = fmaf(scB, scB, s2[nt]);
+          t1 += scB;
+          t2 = fmaf(scB, scB, t2);
         }
+        s1[nt] += (double)t1;
+        s2[nt] += (double)t2;
       }
     }
   };
@@ -418,7 +583,6 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
   if (p.block_group > 0) {
     const int G = p.block_group;           // warps (KV heads) per block
     const int j = wid / G, kvh = wid - j * G;
-    unsigned target = (unsigned)G;
     for (int it = 0; it < my_tiles; ++it) {
       if ((tile0 + it) * p.mb + j >= nblk) break;  // this warp's block of the tile (and of all later tiles) does not exist
       const bool ready = __all_sync(kFull, mbar_wait_bounded(smem_u32(&blk_bar[stage][j]), parity, &s_err));
@@ -432,12 +596,11 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
       const int stage_tok0 = (tile0 + it) * stage_tokens;
       const int tok_end = min(seq_len - stage_tok0, stage_tokens);
       compute_item(smem_base + (uint32_t)(stage * stage_bytes), j, kvh, stage_tok0, (j + 1) * kMmaKeys <= tok_end);
-      // Hand the block back: __syncwarp orders the warp's shared-memory reads before lane 0's acq_rel add, whose
-      // acquire half covers the reads of the warps that added earlier; the warp completing the count refills.
+      // Hand the block back; the last of the block's G reader warps refills it (a single reader needs no count).
       __syncwarp();
       if (lane == 0) {
-        const unsigned done = G == 1 ? target : atom_add_acq_rel_shared(&s_blk_released[stage][j], 1u) + 1u;
-        if (done == target && it + p.stages < my_tiles) {
+        const bool last = G == 1 ? true : release_and_check_last(smem_u32(&blk_empty_bar[stage][j]));
+        if (last && it + p.stages < my_tiles) {
           fence_proxy_async();  // generic-proxy reads of the block before the async-proxy refill
           issue_block(it + p.stages, stage, j);
         }
@@ -445,11 +608,9 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
       if (++stage == p.stages) {
         stage = 0;
         parity ^= 1u;
-        target += (unsigned)G;
       }
     }
   } else {
-    unsigned release_target = (unsigned)kScoreConsumerWarps;
     for (int it = 0; it < my_tiles; ++it) {
       const bool ready = __all_sync(kFull, mbar_wait_bounded(smem_u32(&full_bar[stage]), parity, &s_err));
       if (!ready) {
@@ -482,10 +643,7 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
       // release the stage; the warp whose release is the last of the 8 refills it with the tile `stages` ahead
       __syncwarp();
       unsigned refill = 0u;
-      if (lane == 0) {
-        const unsigned int done = atom_add_acq_rel_shared(&s_released[stage], 1u) + 1u;
-        if (done == release_target && it + p.stages < my_tiles) refill = 1u;
-      }
+      if (lane == 0 && release_and_check_last(smem_u32(&empty_bar[stage])) && it + p.stages < my_tiles) refill = 1u;
       if (__shfl_sync(kFull, refill, 0)) {
         fence_proxy_async();  // every lane issues copies: each orders the (acquired) generic reads before its own
         issue(it + p.stages, stage, lane);
@@ -493,7 +651,6 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
       if (++stage == p.stages) {
         stage = 0;
         parity ^= 1u;
-        release_target += (unsigned)kScoreConsumerWarps;
       }
     }
   }

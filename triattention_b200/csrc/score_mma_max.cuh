@@ -185,8 +185,7 @@ __global__ void __launch_bounds__(kMaxAggThreads, 1) score_paged_mma_max_kernel(
         uint32_t h[4], lo[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float2 re = bf16x2_to_float2(a[j][e]), im = bf16x2_to_float2(a[j + NMG][e]);
-          const float2 m = ffma2(im, im, fmul2(re, re));
+          const float2 m = sq_mag_bf16x2(a[j][e], a[j + NMG][e]);
           split_pair(sqrt_approx(m.x), sqrt_approx(m.y), h[e], lo[e]);
         }
         mma_bf16_16816(accm[0], h[0], h[1], h[2], h[3], bmg[j][0], bmg[j][1]);
@@ -201,9 +200,7 @@ __global__ void __launch_bounds__(kMaxAggThreads, 1) score_paged_mma_max_kernel(
         for (int s2 = 0; s2 < 2; ++s2)
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const float2 v = bf16x2_to_float2(a[2 * j + s2][e]);
-            const float2 q = fmul2(v, v);
-            m[s2][e] = sqrt_approx(q.x + q.y);
+            m[s2][e] = sqrt_approx(sq_mag_bf16_pair(a[2 * j + s2][e]));
           }
         uint32_t h[4], lo[4];
         split_pair(m[0][0], m[0][2], h[0], lo[0]);  // key rg:   frequencies 16j + rt, 16j + 4 + rt

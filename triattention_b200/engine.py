@@ -208,6 +208,7 @@ def compress_layer_shared(
     prefill_lens: Optional[Sequence[int]] = None,
     process_group=None,
     reduce_stats_to_kv_heads: bool = True,
+    timings: Optional[dict] = None,
 ) -> CompressResult:
     """Layer-shared selection: every layer keeps ONE token set for all its heads (top-k of the max over heads).
 
@@ -216,6 +217,9 @@ def compress_layer_shared(
     of a layer live on different ranks: each rank reduces its local heads, one all-reduce(MAX) over
     ``process_group`` of the fp32 rows ``[L, B, t_pad]`` makes them global, and the deterministic top-k then
     yields the same keep set on every rank.  ``stats`` must already be the rank's shard (``tp.shard_stats``).
+    ``process_group=False`` skips the collective even when torch.distributed is initialised (a rank that holds
+    all heads).  ``timings``, if given, receives ``allreduce_ms`` (a callable: CUDA-event time of the collective,
+    valid after a synchronize) and ``allreduce_bytes``.
     Returns keep ``[L, B, keep_pitch]`` (as ``CompressResult.keep``).
     """
     from . import tp as _tp
@@ -253,7 +257,15 @@ def compress_layer_shared(
     raw, mom = ops.score_paged(view, layout, bt, d_seq, w, offset_agg, int(stats.offsets.numel()), status)
     fin = ops.finalize_scores(layout, raw, mom, d_seq, d_pre if prefill_lens is not None else None, window, normalize,
                               _native.REDUCE_MAX, _native.REDUCE_MAX, _native.REDUCE_NONE)   # [L, B, 1, t_pad]
-    _tp.allreduce_shared_scores(fin, process_group)
+    if timings is not None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+    if process_group is not False:
+        _tp.allreduce_shared_scores(fin, process_group)
+    if timings is not None:
+        e1.record()
+        timings["allreduce_ms"] = lambda: e0.elapsed_time(e1)
+        timings["allreduce_bytes"] = int(fin.numel()) * 4
     L = view.num_layers
     keep = ops.select_topk(fin.view(L * B, fin.shape[-1]), d_seq, d_kc, B, 1, keep_pitch, status)  # rows (l, b)
     ops.compact_paged(view, layout, bt, d_seq, keep, (B * keep_pitch, keep_pitch, 0), d_kc, status)
