@@ -314,3 +314,37 @@ def test_metadata_rope_scaling_sets_frequencies_and_scale(tmp_path):
     af = 0.1 * float(np.log(32.0)) + 1.0
     assert st["attention_factor"] == pytest.approx(af)
     assert torch.allclose(st["head_stats"][0]["freq_scale_sq"], torch.full((4, 32), af * af))
+
+
+# ------------------------------------------------------------------------------------------ perf line
+def test_perf_profile_line(monkeypatch, tmp_path, caplog):
+    """TRIATTN_RUNTIME_PERF_PROFILE: the hook is wrapped and a TRIATTN_PERF line is logged and written to the sink
+    directory every TRIATTN_RUNTIME_PERF_LOG_EVERY calls (switches of runtime/perf_profile.py:54-62)."""
+    import logging
+    from triattention_b200.perf_profile import HookPerfProfile
+    calls = []
+
+    def hook(req_id, signal, scheduler_output):
+        calls.append(req_id)
+        if req_id == "boom":
+            raise RuntimeError("x")
+        return {"applied": req_id == "a", "reason": "kv_compacted:per_head" if req_id == "a" else "under_budget"}
+
+    assert HookPerfProfile.from_env().wrap(hook) is hook          # both switches off: the hook itself
+    monkeypatch.setenv("TRIATTN_RUNTIME_PERF_PROFILE", "1")
+    monkeypatch.setenv("TRIATTN_RUNTIME_PERF_LOG_EVERY", "3")
+    monkeypatch.setenv("TRIATTN_RUNTIME_PERF_SINK_DIR", str(tmp_path))
+    prof = HookPerfProfile.from_env(logging.getLogger("perf_test"))
+    wrapped = prof.wrap(hook)
+    with caplog.at_level(logging.INFO, logger="perf_test"):
+        assert wrapped("a", None, None)["applied"]
+        assert wrapped("b", None, None)["reason"] == "under_budget"
+        with pytest.raises(RuntimeError):
+            wrapped("boom", None, None)
+    assert (prof.calls, prof.applied, prof.skipped, prof.errors) == (3, 1, 1, 1)
+    line = prof.summary_line()
+    assert line.startswith("TRIATTN_PERF steps=3 ") and "applied=1 skipped=1 errors=1" in line
+    assert "top_skip_reasons=under_budget:1" in line and "avg_ms(compress=" in line
+    assert any("TRIATTN_PERF" in r.getMessage() for r in caplog.records)
+    sink = list(tmp_path.glob("triattn_perf_*.log"))
+    assert len(sink) == 1 and sink[0].read_text().startswith("TRIATTN_PERF steps=3")

@@ -299,3 +299,35 @@ def test_engine_cuda_graph_replay_matches_eager():
         for w, r in zip(work, ref_caches):
             assert torch.equal(w.view(torch.int16), r.view(torch.int16)), f"round {round_}"
     assert len(graphed._graphs) == 1
+
+
+def test_flat_pool_entry_matches_slot_arithmetic():
+    """The SGLang-shaped entry (token-granular pool, req_to_token table) against plain advanced indexing on the CPU,
+    i.e. the gather / scatter the reference performs (sglang/kv_compaction.py:372-402)."""
+    from triattention_b200 import flat_pool
+    gen = torch.Generator().manual_seed(77)
+    L, H, D, pool, T, budget = 3, 4, 128, 700, 400, 150
+    kb = [torch.randn((pool, H, D), generator=gen).to(torch.bfloat16) for _ in range(L)]
+    vb = [torch.randn((pool, H, D), generator=gen).to(torch.bfloat16) for _ in range(L)]
+    req_to_token = torch.zeros((3, 512), dtype=torch.int32)
+    slots = torch.randperm(pool - 1, generator=gen)[:T] + 1
+    req_to_token[1, :T] = slots.int()
+    keep = torch.stack([torch.sort(torch.randperm(T, generator=gen)[:budget]).values for _ in range(H)])
+    dk, dv = [x.to(DEV) for x in kb], [x.to(DEV) for x in vb]
+    n = flat_pool.compact_request_kv_in_place_per_head(dk, dv, req_to_token.to(DEV), 1, keep.to(DEV), T, target_layers=[0, 2])
+    assert n == budget
+    head = torch.arange(H).unsqueeze(1).expand(-1, budget)
+    src, dst = slots[keep], slots[:budget].unsqueeze(0).expand(H, -1)
+    for l in range(L):
+        ek, ev = kb[l].clone(), vb[l].clone()
+        if l != 1:
+            gk, gv = ek[src, head].clone(), ev[src, head].clone()
+            ek[dst, head], ev[dst, head] = gk, gv
+        assert torch.equal(dk[l].cpu().view(torch.int16), ek.view(torch.int16)), l
+        assert torch.equal(dv[l].cpu().view(torch.int16), ev.view(torch.int16)), l
+    with pytest.raises(IndexError):
+        flat_pool.compact_request_kv_in_place_per_head(dk, dv, req_to_token.to(DEV), 1, (keep + 300).to(DEV), T)
+    with pytest.raises(ValueError, match="sorted ascending"):
+        flat_pool.compact_request_kv_in_place_per_head(dk, dv, req_to_token.to(DEV), 1, keep.flip(1).to(DEV), T)
+    with pytest.raises(ValueError, match="exceeds effective_len"):
+        flat_pool.compact_request_kv_in_place_per_head(dk, dv, req_to_token.to(DEV), 1, keep.to(DEV), 100)

@@ -79,3 +79,93 @@ def save_stats(path, per_layer: Iterable[Dict[str, torch.Tensor]], head_dim: int
     out = Path(path)
     out.parent.mkdir(parents=True, exist_ok=True)
     torch.save(stats_payload(per_layer, head_dim, rope_style, inv_freq, extra_metadata), out)
+
+
+# ------------------------------------------------------------------------------------------ capture from a model
+def find_attention_layers(model) -> list:
+    """The ``self_attn`` module of every decoder layer (``model.model.layers[i].self_attn``, scripts/calibrate.py:98-113)."""
+    backbone = getattr(model, "model", model)
+    layers = getattr(backbone, "layers", None)
+    if layers is None:
+        raise RuntimeError("Cannot locate transformer layers. Expected model.model.layers.")
+    out = []
+    for layer in layers:
+        attn = getattr(layer, "self_attn", None)
+        if attn is None:
+            raise RuntimeError("Layer missing self_attn attribute.")
+        out.append(attn)
+    return out
+
+
+def _rotate_half(x: torch.Tensor, rope_style: str) -> torch.Tensor:
+    if rope_style == "interleaved":
+        out = torch.empty_like(x)
+        out[..., 0::2] = -x[..., 1::2]
+        out[..., 1::2] = x[..., 0::2]
+        return out
+    half = x.shape[-1] // 2
+    return torch.cat((-x[..., half:], x[..., :half]), dim=-1)
+
+
+def capture_query_stats(model, input_ids: torch.Tensor, rope_style: str = "half", apply_q_norm: bool = False):
+    """Statistics of every layer from ONE forward pass of a Hugging Face style decoder (scripts/calibrate.py:116-272).
+
+    A forward pre-hook on each ``self_attn`` recomputes the query projection of the layer's input, rotates it with
+    the model's own rotary embedding (positions 0..T-1, times its ``attention_scaling``) and keeps it; after the pass
+    the rotation is taken out again and the per-head complex mean and mean magnitude are formed.  ``apply_q_norm``
+    additionally applies the module's ``q_norm`` before the rotation (the reference script does not).
+
+    Returns ``(per_layer, info)``: a list of ``{q_mean_real, q_mean_imag, q_abs_mean}`` ``[H, F]`` dictionaries and
+    ``{"head_dim", "num_heads", "inv_freq", "attn_scale"}``; feed them to :func:`save_stats`.
+    """
+    cfg = model.config
+    num_heads = int(cfg.num_attention_heads)
+    head_dim = int(getattr(cfg, "head_dim", None) or cfg.hidden_size // num_heads)
+    attn_layers = find_attention_layers(model)
+    backbone = getattr(model, "model", model)
+    rotary = backbone.rotary_emb if hasattr(backbone, "rotary_emb") else attn_layers[0].rotary_emb
+    attn_scale = float(getattr(rotary, "attention_scaling", 1.0))
+    captured: Dict[int, torch.Tensor] = {}
+
+    def tables(q_len: int, device, dtype):
+        pos = torch.arange(q_len, device=device).unsqueeze(0)
+        return rotary(torch.zeros(1, q_len, head_dim, device=device, dtype=dtype), pos)   # [1, T, D] each
+
+    def make_hook(idx: int):
+        def hook(module, args, kwargs):
+            hidden = args[0] if args else kwargs.get("hidden_states")
+            if hidden is None:
+                return
+            bsz, q_len, _ = hidden.shape
+            q = module.q_proj(hidden).view(bsz, q_len, num_heads, head_dim)
+            if apply_q_norm and hasattr(module, "q_norm"):
+                q = module.q_norm(q)
+            q = q.transpose(1, 2)
+            cos, sin = tables(q_len, hidden.device, hidden.dtype)
+            captured[idx] = ((q * cos.unsqueeze(1) + _rotate_half(q, rope_style) * sin.unsqueeze(1)) * attn_scale).detach()
+        return hook
+
+    handles = [a.register_forward_pre_hook(make_hook(i), with_kwargs=True) for i, a in enumerate(attn_layers)]
+    try:
+        with torch.no_grad():
+            model(input_ids)
+    finally:
+        for h in handles:
+            h.remove()
+    T = int(input_ids.shape[1])
+    cos_t, sin_t = tables(T, input_ids.device, next(model.parameters()).dtype)
+    F = head_dim // 2
+    # per-frequency tables [T, F]: the rotary embedding repeats (half) or interleaves its F angles over D; the
+    # reference divides the attention scaling out of cos/sin before inverting (scripts/calibrate.py:75-95)
+    sel = slice(0, None, 2) if rope_style == "interleaved" else slice(0, F)
+    cos_f = (cos_t[0, :, sel] / attn_scale).float()
+    sin_f = (sin_t[0, :, sel] / attn_scale).float()
+    per_layer = []
+    for i in range(len(attn_layers)):
+        if i not in captured:
+            raise RuntimeError(f"no queries captured for layer {i}")
+        per_layer.append(query_frequency_stats(captured.pop(i).float(), cos_f, sin_f, attn_scale, rope_style))
+    inv_freq = getattr(rotary, "inv_freq", None)
+    info = {"head_dim": head_dim, "num_heads": num_heads, "attn_scale": attn_scale,
+            "inv_freq": inv_freq.detach().float().cpu() if isinstance(inv_freq, torch.Tensor) else None}
+    return per_layer, info

@@ -104,6 +104,8 @@ class TriAttentionRuntimeConfig:
     # additions of this implementation (not read by the reference)
     preserve_dropped_tokens: bool = False
     """Also rewrite the dropped tokens behind the kept prefix (whole-region byte equality with the reference)."""
+    use_cuda_graph: bool = False
+    """Replay the fused step from a CUDA graph once a geometry repeats (steady-state decode compressions)."""
 
     @classmethod
     def from_env(cls, prefix: str = "TRIATTN_RUNTIME_") -> "TriAttentionRuntimeConfig":

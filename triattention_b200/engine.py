@@ -186,7 +186,7 @@ class PagedCompressor:
                 self._graphs[key] = graph
                 graph.replay()  # a capture records, it does not execute
         torch.cuda.current_stream().synchronize()
-        status = int(self._status_host.item())
+        status = int(self._status_host[0])
         req_blocks = ((kc_np + bs - 1) // bs).tolist()
         kept = [ids[:r] if isinstance(ids, np.ndarray) else [int(x) for x in ids[:r]] for ids, r in zip(block_ids, req_blocks)]
         removed = [ids[r:] if isinstance(ids, np.ndarray) else [int(x) for x in ids[r:]] for ids, r in zip(block_ids, req_blocks)]

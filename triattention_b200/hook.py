@@ -19,6 +19,7 @@ from .kv_compaction import (build_keep_token_indices, compact_group_kv_in_place_
                             compact_request_kv_in_place, compact_request_kv_in_place_per_head,
                             register_kv_layout_axis_hint)
 from .layout_engine import num_required_blocks, truncate_tail_reclaim_group
+from .perf_profile import HookPerfProfile
 from .plan_models import KeepPlan, PlacementPlan, ReclaimEvent
 from .request_state import resolve_hook_request_context, scheduled_tokens_for_req
 from .selector import FusedCompactionError, build_triattention_selector as _build_triattention_selector
@@ -437,7 +438,8 @@ def make_runner_compression_hook(base_runner: Any, config: TriAttentionRuntimeCo
             budget_total=rt.budget_total, recent_unabsorbed_tokens=rt.recent_unabsorbed_tokens,
             block_reclaim=reclaim_event).to_hook_result_dict()
 
-    return _hook
+    # TRIATTN_RUNTIME_PERF_PROFILE / TRIATTN_RUNTIME_NVTX: aggregated TRIATTN_PERF lines, NVTX range per call
+    return HookPerfProfile.from_env().wrap(_hook)
 
 
 def install_runner_compression_hook(base_runner: Any, config: TriAttentionRuntimeConfig) -> None:

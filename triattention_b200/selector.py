@@ -294,7 +294,7 @@ def build_triattention_selector(
             _group_of(dstats.num_heads, view.num_kv_heads)
             comp = fused_engines.get(str(view.device))
             if comp is None:
-                comp = _engine.PagedCompressor(dstats)
+                comp = _engine.PagedCompressor(dstats, use_cuda_graph=bool(getattr(config, "use_cuda_graph", False)))
                 fused_engines[str(view.device)] = comp
             comp.stats = dstats
             comp.window = int(config.window_size) if config.window_size > 0 else 0
@@ -313,7 +313,9 @@ def build_triattention_selector(
             raise FusedCompactionError(f"device_status:{res.device_status}")
         return {
             "mode": "per_head",
-            "indices": res.keep[0].long(),   # a copy: the engine reuses its output buffer
+            # the engine's own int32 output buffer, valid until its next call: the hook only needs the row count
+            # here (the cache is already compacted); callers that keep the indices must copy them
+            "indices": res.keep[0],
             "semantic": "hf_aligned_global_per_head",
             "group_agg_mode": agg,
             "debug_group_layer_indices": [int(i) for i in layer_indices],
