@@ -17,7 +17,7 @@ PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "libtriattn_b200.so"
 SOURCES = ["api.cu"]
-HEADERS = ["common.cuh", "prep.cuh", "score.cuh", "score_fma.cuh", "score_mma.cuh", "score_mma_max.cuh", "finalize.cuh", "select.cuh", "compact.cuh", "reclaim.cuh", "overrides.cuh",
+HEADERS = ["common.cuh", "prep.cuh", "score.cuh", "score_fma.cuh", "score_mma.cuh", "score_mma_max.cuh", "score_umma_max.cuh", "finalize.cuh", "select.cuh", "compact.cuh", "reclaim.cuh", "overrides.cuh",
            "../../include/triattn_b200.h"]
 
 NVCC_FLAGS = [

@@ -1,5 +1,6 @@
 // C ABI of libtriattn_b200.so: argument validation, launch geometry and kernel launches.
 // No allocation, no synchronisation, no exceptions: every entry returns a triattn_status.
+#include <cuda.h>  // tensor-map types; cuTensorMapEncodeTiled itself is looked up at run time (no link against libcuda)
 #include <cuda_runtime.h>
 
 #include <algorithm>
@@ -21,6 +22,7 @@
 #include "score_fma.cuh"
 #include "score_mma.cuh"
 #include "score_mma_max.cuh"
+#include "score_umma_max.cuh"
 #include "select.cuh"
 
 using namespace triattn;
@@ -109,6 +111,71 @@ int launch_score_mma(const ScoreParams& p, dim3 grid, size_t smem, cudaStream_t 
   if (p.gp_total <= 4) TRIATTN_LAUNCH(1)
   TRIATTN_LAUNCH(2)
 #undef TRIATTN_LAUNCH
+}
+
+// ------------------------------------------------------------------------- tensor maps for the tcgen05 scorer
+// Per-layer tensor maps live in a ring of slots inside the library image (the entry points allocate nothing):
+// kTmapRing consecutive scoring calls each get their own kTmapMaxLayers slots, so a call's maps are overwritten
+// only after kTmapRing later max-aggregation calls on the same device have been issued.
+constexpr int kTmapRing = 8;
+constexpr int kTmapMaxLayers = 128;
+static __device__ __align__(128) unsigned char g_tmap_slots[kTmapRing * kTmapMaxLayers * 128];
+std::mutex g_tmap_mutex;
+unsigned char* g_tmap_ptr[kMaxDevicesSmem] = {};
+std::atomic<unsigned> g_tmap_call{0};
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+  static std::atomic<void*> cached{nullptr};
+  void* f = cached.load(std::memory_order_acquire);
+  if (f == nullptr) {
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    cached.store(f, std::memory_order_release);
+  }
+  return reinterpret_cast<EncodeTiledFn>(f);
+}
+
+// Slots of this call (device pointer) or nullptr; also stamps the layers' K pointers into them on `st`.
+const unsigned char* stamp_layer_tensor_maps(const triattn_paged_layout& Y, const void* const* k_layer_ptrs,
+                                             cudaStream_t st, bool pdl) {
+  if (Y.num_layers > kTmapMaxLayers) return nullptr;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevicesSmem) return nullptr;
+  unsigned char* slots = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_tmap_mutex);
+    if (g_tmap_ptr[dev] == nullptr) {
+      void* ptr = nullptr;
+      if (cudaGetSymbolAddress(&ptr, g_tmap_slots) != cudaSuccess || ptr == nullptr) return nullptr;
+      g_tmap_ptr[dev] = static_cast<unsigned char*>(ptr);
+    }
+    slots = g_tmap_ptr[dev];
+  }
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (encode == nullptr) return nullptr;
+  slots += (size_t)(g_tmap_call.fetch_add(1) % kTmapRing) * kTmapMaxLayers * 128;
+  // (dim, KV head, token in block, block), strides in bytes for all but the innermost; box = 64 dims x 16 tokens
+  const cuuint64_t dims[4] = {(cuuint64_t)Y.head_dim, (cuuint64_t)Y.num_kv_heads, (cuuint64_t)Y.block_size,
+                              (cuuint64_t)Y.num_blocks};
+  const cuuint64_t strides[3] = {(cuuint64_t)Y.head_stride * 2, (cuuint64_t)Y.token_stride * 2, (cuuint64_t)Y.block_stride * 2};
+  const cuuint32_t box[4] = {64, 1, 16, 1};
+  const cuuint32_t elem[4] = {1, 1, 1, 1};
+  TensorMapBytes tmpl;
+  static_assert(sizeof(CUtensorMap) == sizeof(TensorMapBytes), "tensor map is 128 bytes");
+  // the base address of the template is a placeholder (its own slot: valid device memory, 128-byte aligned)
+  if (encode(reinterpret_cast<CUtensorMap*>(&tmpl), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, slots, dims, strides, box, elem,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return nullptr;
+  if (launch_kernel(stamp_tensor_maps_kernel, dim3(1), dim3((unsigned)((Y.num_layers + 31) / 32 * 32)), 0, st, pdl, tmpl,
+                    k_layer_ptrs, slots, (int)Y.num_layers) != TRIATTN_OK)
+    return nullptr;
+  return slots;
 }
 
 // How an internal stage is launched: after the preceding kernel as a programmatic dependent or in plain stream
@@ -668,7 +735,30 @@ int score_paged_impl(const triattn_paged_layout* layout, const void* const* k_la
                               : launch_score_mma<64, false>(p, grid, smem, st, opt.pdl);
   }
   if (opt.cuda_core_scorer) return TRIATTN_ERR_UNSUPPORTED_SHAPE;
-  // max over offsets on the tensor cores: one CTA per (layer, request, virtual head, run of 16-key tiles)
+  // max over offsets, head_dim 128: tcgen05 kernel, one CTA per (layer, request, virtual head, run of 128-key tiles)
+  if (p.agg_max && Y.head_dim == 128 && num_offsets >= 1 && 4 * num_offsets <= kUmmaMaxN &&
+      umma_max_smem_bytes(umma_max_cols(num_offsets)) <= 220 * 1024 && (Y.block_size % 16) == 0 &&
+      Y.num_layers <= kTmapMaxLayers && (p.block_stride_bytes % 16) == 0 && (Y.token_stride % 8) == 0 && (Y.head_stride % 8) == 0) {
+    const int n_cols = umma_max_cols(num_offsets);
+    const int nvh = Y.num_kv_heads * ((gp + 3) / 4);
+    const int n_tiles = (p.t_pad + kUmmaTileKeys - 1) / kUmmaTileKeys;
+    // a CTA keeps the block ids of its keys in shared memory; 128 tiles (16384 keys) amortise the weight set-up
+    const int fit = (int)std::max<long long>(1, ((long long)(kUmmaMaxBlocks - 1) * Y.block_size) / kUmmaTileKeys);
+    p.tiles_per_cta = std::min(n_tiles, std::min(128, fit));
+    const int chunks = (n_tiles + p.tiles_per_cta - 1) / p.tiles_per_cta;
+    dim3 grid((unsigned)(nvh * chunks), (unsigned)Y.num_layers, (unsigned)Y.num_reqs);
+    const size_t smem = umma_max_smem_bytes(n_cols);
+    // the layers' tensor maps are stamped by a one-warp kernel in front of the scorer (its programmatic dependent)
+    p.tmaps = stamp_layer_tensor_maps(Y, k_layer_ptrs, st, opt.pdl);
+    if (p.tmaps == nullptr) return TRIATTN_ERR_CUDA;
+    if (Y.rope_interleaved) {
+      if (!ensure_dynamic_smem<score_paged_umma_max_kernel<true>>(smem)) return TRIATTN_ERR_CUDA;
+      return launch_kernel(score_paged_umma_max_kernel<true>, grid, dim3(kUmmaThreads), smem, st, true, p);
+    }
+    if (!ensure_dynamic_smem<score_paged_umma_max_kernel<false>>(smem)) return TRIATTN_ERR_CUDA;
+    return launch_kernel(score_paged_umma_max_kernel<false>, grid, dim3(kUmmaThreads), smem, st, true, p);
+  }
+  // max over offsets on mma.sync (head_dim 64): one CTA per (layer, request, virtual head, run of 16-key tiles)
   if (p.agg_max && (Y.head_dim == 64 || Y.head_dim == 128) && (p.block_stride_bytes % 16) == 0 &&
       max_agg_smem_bytes(Y.head_dim, num_offsets) <= 220 * 1024) {
     const int nvh = Y.num_kv_heads * ((gp + 3) / 4);

@@ -28,8 +28,9 @@ struct ScoreParams {
   int gp_total;  // query-head slots per KV head in the raw layout
   int nhd;       // 1: token-major blocks (head_stride == D, token_stride == Hkv*D)
   int block_group;  // > 0: 16-token blocks, Hkv * mb == 8: block j of a stage is read only by the Hkv warps j*Hkv..(j+1)*Hkv-1
-  int num_offsets;  // generic kernel only
-  int agg_max;      // generic kernel only
+  const unsigned char* tmaps;  // [L] stamped tensor maps of the layers' K caches (tcgen05 scorer only)
+  int num_offsets;
+  int agg_max;
 };
 
 constexpr int kScoreConsumerWarps = 8;
