@@ -52,7 +52,9 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference_gpu"],
+                    help="reference: the reference's CPU path on the host cores; reference_gpu (informational): the "
+                         "reference's own Triton scorer and torch glue on this GPU, through its unmodified selector")
     ap.add_argument("--config", default="c1", choices=sorted(CONFIGS))
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (smaller captures)")
     ap.add_argument("--batch", type=int, default=0, help="override the request count")
@@ -85,10 +87,23 @@ def measured_peaks():
     return 6650.0, "fallback"
 
 
-# DRAM traffic of the score kernel per key from the ncu capture summarised in
-# profiles/score_paged_mma_kernel_c1_2layers.md (dram__bytes_read + dram__bytes_write = 1.0743 GB + 64.5 MB for
-# 4 194 304 keys); traffic grows in proportion to the keys scored, so a full launch is this figure x its keys.
-SCORE_DRAM_BYTES_PER_KEY_NCU = (1.074343e9 + 64.52e6) / 4194304.0
+# DRAM traffic of the score kernel per key (dram__bytes_read + dram__bytes_write) from the ncu captures summarised
+# under profiles/ (score_paged_mma_kernel_c1_2layers.md, score_paged_mma_kernel_c2_tp8_4layers.md,
+# score_paged_umma_max_kernel_c1_2layers.md); K is read once and the raw scores are written once, so traffic grows
+# in proportion to the keys scored and a full launch is this figure x its keys.
+SCORE_DRAM_BYTES_PER_KEY_NCU = {
+    ("mean", 4): (1.074319e9 + 64.09e6) / 4194304.0,     # 271.4 B: 256 B of K + 16 B of raw scores
+    ("mean", 8): (4.299367e9 + 529.69e6) / 16777216.0,   # 287.8 B: 256 B of K + 32 B of raw scores
+    ("max", 4): (1.078619e9 + 64.30e6) / 4194304.0,      # 272.5 B
+}
+
+
+def score_kernel_name(c: dict, aggregation: str) -> str:
+    """The kernel triattn_score_paged dispatches to for this shape (csrc/api.cu score_paged_impl)."""
+    if aggregation == "max":
+        tcgen05 = c["D"] == 128 and BLOCK_SIZE % 16 == 0 and c["L"] <= 128
+        return "score_paged_umma_max_kernel" if tcgen05 else "score_paged_mma_max_kernel"
+    return "score_paged_mma_kernel"
 
 
 def algorithmic_bytes_per_key(T: int, k: int) -> float:
@@ -235,7 +250,7 @@ def dist_setup(args):
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if world > 1 and args.impl == "ours":
-        # the reference arm runs on rank 0's host cores only: it needs no process group
+        # the reference arms run on rank 0 only: they need no process group
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local))
@@ -346,6 +361,43 @@ def run_reference(args, world, rank):
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+def run_reference_gpu(args, rank):
+    """Informational: the reference's own GPU path (Triton scorer + torch selection and compaction, from
+    oracle/_ref, unmodified) on this GPU, on the slice the CPU baseline uses: one request x two layers."""
+    if rank != 0:
+        return
+    import synth
+    from oracle import ref_runner
+
+    if not ref_runner.available() or not torch.cuda.is_available():
+        print(json.dumps({"impl": "reference_gpu", "unavailable": "needs oracle/_ref and a CUDA device"}), flush=True)
+        return
+    c = resolve_config(args, 1, "c3s" if args.config == "c3" else args.config)
+    L2, T = min(2, c["L"]), min(c["T"], 32768)
+    stats, caches, block_ids, _ = _cpu_slice_inputs(c, L2, T)
+    kk = min(c["budget"], T)
+    times = []
+    try:
+        with tempfile.TemporaryDirectory() as td:
+            sel = ref_runner.make_group_selector(ref_runner.stats_file(td, synth.save_stats_pt, stats), c["budget"], c["window"], gpu=True)
+            for it in range(args.warmup + args.steps):
+                work = [x.cuda() for x in caches]
+                _, dt = ref_runner.select_and_compact(sel, work, block_ids, BLOCK_SIZE, T, T, kk)
+                if it >= args.warmup:
+                    times.append(dt)
+    except Exception as exc:
+        print(json.dumps({"impl": "reference_gpu", "unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"}), flush=True)
+        return
+    keys = L2 * c["Hkv"] * T
+    dt = statistics.mean(times)
+    print(json.dumps({"impl": "reference_gpu", "metric": METRIC, "value": keys / dt, "unit": UNIT, "n_gpus": 1,
+                      "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+                      "data": "synthetic", "config": {"workload": workload_name(args, c),
+                      "sample": f"1 request x {L2} layers x {c['Hkv']} KV heads x {T} tokens, budget {kk}",
+                      "path": "reference Triton scorer + torch top-k + torch compaction, wall clock, device synchronised"}}),
+          flush=True)
 
 
 def workload_name(args, c):
@@ -746,12 +798,13 @@ def run_ours(args, world, rank, local):
         "keys_per_s_per_gpu": value / world,
         "step_hbm_gbs": bytes_step / (step_ms * 1e-3) / 1e9, "step_hbm_frac": bytes_step / (step_ms * 1e-3) / 1e9 / peak,
         "stage_ms": stage,
-        "roofline": {"kernel": ("score_paged_mma_max_kernel" if args.aggregation == "max" else "score_paged_mma_kernel"),
+        "roofline": {"kernel": score_kernel_name(c, args.aggregation),
                      "bound": "hbm", "achieved": achieved, "peak": peak,
                      "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
-                     "traffic": (keys_per_gpu * SCORE_DRAM_BYTES_PER_KEY_NCU
-                                 if (c["D"], c["g"], c["Hkv_local"]) == (128, 4, 8) else None),
-                     "traffic_note": "bytes per launch, scaled by keys from a 2-layer ncu capture of the same shape"},
+                     "traffic": (keys_per_gpu * SCORE_DRAM_BYTES_PER_KEY_NCU[(args.aggregation, c["g"])]
+                                 if c["D"] == 128 and (args.aggregation, c["g"]) in SCORE_DRAM_BYTES_PER_KEY_NCU else None),
+                     "traffic_note": "bytes per launch, scaled by keys from a small ncu capture of the same kernel "
+                                     "and group size (profiles/)"},
         "e2e": {"value": keys_per_gpu * world / e2e_s, "unit": UNIT, "h2d_bytes_per_step": m["h2d"],
                 "d2h_bytes_per_step": m["d2h"], "ms_per_step": e2e_s * 1e3,
                 "api": "engine.PagedCompressor.compress (host block tables -> pinned -> H2D, kernels, D2H status)"},
@@ -784,6 +837,8 @@ def main():
     try:
         if args.impl == "reference":
             run_reference(args, world, rank)
+        elif args.impl == "reference_gpu":
+            run_reference_gpu(args, rank)
         elif args.config == "c3":
             from bench_decode import run_decode_interleaved
             run_decode_interleaved(args, world, rank, local)
