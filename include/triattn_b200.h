@@ -299,8 +299,8 @@ size_t triattn_compress_workspace_bytes_min(const triattn_paged_layout* layout /
  * top-k -> in-place compaction of every layer with the shared keep set.
  * keep_out [B, Hkv, keep_pitch] int32 receives the ascending keep indices.
  * workspace_bytes selects how many layers are scored per launch (see triattn_compress_workspace_bytes_min).
- * The launches after the first are programmatic dependents of their predecessors (each kernel starts with
- * griddepcontrol.wait), so the tail of one kernel overlaps the launch of the next.
+ * The score, top-k and compaction launches are programmatic dependents of their predecessors (each kernel
+ * starts with griddepcontrol.wait), so the tail of one kernel overlaps the launch of the next.
  * Replaces, for all requests of a step at once, select_keep_indices_for_group
  * (selector_hf.py:749-1033) followed by execute_group_compaction's per-layer calls
  * (triattention/vllm/runtime/layout_engine.py:112-139).

@@ -59,6 +59,18 @@ __device__ __forceinline__ float sq_mag_bf16_pair(uint32_t w) {
       : "r"(w));
   return m;
 }
+// Split two non-negative fp32 values into bf16 pairs (hi, lo) with m = hi + lo + e, |e| <= 2^-18 m: hi is m rounded
+// to nearest bf16 (one packed convert), the remainder m - hi is exact in fp32 and is formed by the mixed-precision
+// FMA straight from the packed halves of hi (hi * -1 + m), lo is its bf16 rounding.  Four instructions per pair.
+__device__ __forceinline__ void split_bf16x2_hi_lo(float m0, float m1, uint32_t& hi, uint32_t& lo) {
+  asm("{\n\t.reg .b16 hl, hh, neg1;\n\t.reg .f32 r0, r1;\n\t"
+      "cvt.rn.bf16x2.f32 %0, %3, %2;\n\t"
+      "mov.b32 {hl, hh}, %0;\n\tmov.b16 neg1, 0xBF80;\n\t"
+      "fma.rn.f32.bf16 r0, hl, neg1, %2;\n\tfma.rn.f32.bf16 r1, hh, neg1, %3;\n\t"
+      "cvt.rn.bf16x2.f32 %1, r1, r0;\n\t}"
+      : "=&r"(hi), "=r"(lo)
+      : "f"(m0), "f"(m1));
+}
 __device__ __forceinline__ float2 fsub2(float2 a, float2 b) {
   float2 d;
   asm("sub.rn.f32x2 %0, %1, %2;"

@@ -35,10 +35,16 @@ constexpr int kMmaKeys = 16;  // keys per MMA tile and work item
 
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// d = a * b (no accumulator input: the first MMA of a chain needs no zeroed registers)
+__device__ __forceinline__ void mma_bf16_16816_first(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                     uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
 }
 
 // bf16 (round to nearest even) of x, as the upper 16 bits of an fp32 pattern
@@ -352,39 +358,33 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
     return (uint32_t)(j * p.block_bytes + (kvh * p.head_stride + in * p.token_stride) * 2);
   };
 
-  // One work item: keys tt*16 .. tt*16+15 of the stage for the current virtual head.
-  // `full` = all 16 keys exist (inside the stage and below seq_len), so stores need no per-key test.
-  auto compute_item = [&](uint32_t stage_addr, int tt, int kvh, int stage_tok0, bool full) {
-    const int tkA = tt * kMmaKeys + rg, tkB = tkA + 8;
-    const uint32_t rowA = stage_addr + row_offset(min(tkA, stage_tokens - 1), kvh) + 16u * rt;
-    const uint32_t rowB = stage_addr + row_offset(min(tkB, stage_tokens - 1), kvh) + 16u * rt;
+  // One work item: 16 keys of the current virtual head.  rowA / rowB = shared-memory address of this thread's 16-byte
+  // chunk `rt` of the item's key rg / rg + 8, tok0 = token index (in the request) of the item's first key, valid =
+  // how many of the 16 keys exist (inside the stage and below seq_len); with all 16 the stores need no per-key test.
+  auto compute_rows = [&](uint32_t rowA, uint32_t rowB, int tok0, int valid) {
+    const bool full = valid >= kMmaKeys;
     if constexpr (NT == 2) {
       // Transposed form.  Group A = keys tt*16 + 0..7, group B = keys tt*16 + 8..15; this thread feeds key rg of each
       // group as column rg of the B operand and ends with query head rg's score for keys 2*rt, 2*rt + 1 of each group.
       float accA[2][4], accB[2][4];
-#pragma unroll
-      for (int ch = 0; ch < 2; ++ch)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) accA[ch][e] = accB[ch][e] = 0.f;
       auto mma_t = [&](float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
         mma_bf16_16816(d, a[0], a[1], a[2], a[3], b0, b1);
       };
-      auto split_pair = [&](float m0, float m1, uint32_t& hi, uint32_t& lo) {
-        const uint32_t u0 = __float_as_uint(m0), u1 = __float_as_uint(m1);
-        hi = __byte_perm(u0, u1, 0x7632);
-        const float2 r = fsub2(make_float2(m0, m1), make_float2(__uint_as_float(u0 & 0xffff0000u), __uint_as_float(u1 & 0xffff0000u)));
-        lo = pack_bf16x2_rn(r.x, r.y);
+      auto mma_t0 = [&](bool first, float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+        if (first) mma_bf16_16816_first(d, a[0], a[1], a[2], a[3], b0, b1);
+        else mma_bf16_16816(d, a[0], a[1], a[2], a[3], b0, b1);
       };
+      auto split_pair = [&](float m0, float m1, uint32_t& hi, uint32_t& lo) { split_bf16x2_hi_lo(m0, m1, hi, lo); };
       if constexpr (!INTERLEAVED) {
 #pragma unroll
         for (int q = 0; q < NQ / 2; ++q) {
           constexpr int QI = NQ / 2;
           const uint4 reA = lds128(rowA + 64u * q), reB = lds128(rowB + 64u * q);
           const uint4 imA = lds128(rowA + 64u * q + D), imB = lds128(rowB + 64u * q + D);
-          mma_t(accA[0], ari[q][0], reA.x, reA.y);
-          mma_t(accB[0], ari[q][0], reB.x, reB.y);
-          mma_t(accA[1], ari[q][1], reA.z, reA.w);
-          mma_t(accB[1], ari[q][1], reB.z, reB.w);
+          mma_t0(q == 0, accA[0], ari[q][0], reA.x, reA.y);
+          mma_t0(q == 0, accB[0], ari[q][0], reB.x, reB.y);
+          mma_t0(q == 0, accA[1], ari[q][1], reA.z, reA.w);
+          mma_t0(q == 0, accB[1], ari[q][1], reB.z, reB.w);
           mma_t(accA[0], ari[q + QI][0], imA.x, imA.y);
           mma_t(accB[0], ari[q + QI][0], imB.x, imB.y);
           mma_t(accA[1], ari[q + QI][1], imA.z, imA.w);
@@ -412,10 +412,10 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
 #pragma unroll
         for (int c = 0; c < NQ; ++c) {
           const uint4 xA = lds128(rowA + 64u * c), xB = lds128(rowB + 64u * c);
-          mma_t(accA[0], ari[c][0], xA.x, xA.y);
-          mma_t(accB[0], ari[c][0], xB.x, xB.y);
-          mma_t(accA[1], ari[c][1], xA.z, xA.w);
-          mma_t(accB[1], ari[c][1], xB.z, xB.w);
+          mma_t0(c == 0, accA[0], ari[c][0], xA.x, xA.y);
+          mma_t0(c == 0, accB[0], ari[c][0], xB.x, xB.y);
+          mma_t0(c == 0, accA[1], ari[c][1], xA.z, xA.w);
+          mma_t0(c == 0, accB[1], ari[c][1], xB.z, xB.w);
           const uint32_t wA[4] = {xA.x, xA.y, xA.z, xA.w}, wB[4] = {xB.x, xB.y, xB.z, xB.w};
           float mA[4], mB[4];
 #pragma unroll
@@ -436,20 +436,39 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
       }
       // d0/d1 = row rg (high part), d2/d3 = row rg + 8 (low part), columns = keys 2*rt, 2*rt + 1
       if (rg < cur_nq) {
-        const int k0 = tt * kMmaKeys + 2 * rt;  // first of this thread's keys in group A, relative to the stage
+        // this thread's keys: 2*rt, 2*rt + 1 of group A and of group B (8 keys further)
         const float sc[4] = {(accA[0][0] + accA[1][0]) + (accA[0][2] + accA[1][2]),
                              (accA[0][1] + accA[1][1]) + (accA[0][3] + accA[1][3]),
                              (accB[0][0] + accB[1][0]) + (accB[0][2] + accB[1][2]),
                              (accB[0][1] + accB[1][1]) + (accB[0][3] + accB[1][3])};
-        float t1 = 0.f, t2 = 0.f;  // this tile's share, fixed order
+        float* out = raw_head + (size_t)(tok0 + 2 * rt) * gp_total;
+        float t1 = 0.f, t2 = 0.f;  // this tile's share, fixed order (the same in both branches)
+        if (full) {
+          if (gp_total == 8) {  // the usual record of 8 query heads: constant store offsets
+            out[0] = sc[0];
+            out[8] = sc[1];
+            out[64] = sc[2];
+            out[72] = sc[3];
+          } else {
+            out[0] = sc[0];
+            out[gp_total] = sc[1];
+            out[(size_t)8 * gp_total] = sc[2];
+            out[(size_t)9 * gp_total] = sc[3];
+          }
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int tk = k0 + (e & 1) + 8 * (e >> 1);
-          const int gk = stage_tok0 + tk;
-          if (full || (tk < stage_tokens && gk < seq_len)) {
-            raw_head[(size_t)gk * gp_total] = sc[e];
+          for (int e = 0; e < 4; ++e) {
             t1 += sc[e];
             t2 = fmaf(sc[e], sc[e], t2);
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int ki = (e & 1) + 8 * (e >> 1);
+            if (2 * rt + ki < valid) {
+              out[(size_t)ki * gp_total] = sc[e];
+              t1 += sc[e];
+              t2 = fmaf(sc[e], sc[e], t2);
+            }
           }
         }
         s1[0] += (double)t1;
@@ -459,20 +478,14 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
     }
     constexpr int NCH = NT == 1 ? 2 : 1;  // accumulator chains per column tile (two independent chains in total)
     float acc[NT][NCH][4];
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-      for (int ch = 0; ch < NCH; ++ch)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) acc[nt][ch][e] = 0.f;
+    auto mma_k0 = [&](bool first, float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                      uint32_t b1) {
+      if (first) mma_bf16_16816_first(d, a0, a1, a2, a3, b0, b1);
+      else mma_bf16_16816(d, a0, a1, a2, a3, b0, b1);
+    };
 
     // (hi, lo) bf16x2 pairs of two adjacent |k| values; lo is the bf16 of the exact remainder
-    auto split_pair = [&](float m0, float m1, uint32_t& hi, uint32_t& lo) {
-      const uint32_t u0 = __float_as_uint(m0), u1 = __float_as_uint(m1);
-      hi = __byte_perm(u0, u1, 0x7632);
-      const float2 r = fsub2(make_float2(m0, m1), make_float2(__uint_as_float(u0 & 0xffff0000u), __uint_as_float(u1 & 0xffff0000u)));
-      lo = pack_bf16x2_rn(r.x, r.y);
-    };
+    auto split_pair = [&](float m0, float m1, uint32_t& hi, uint32_t& lo) { split_bf16x2_hi_lo(m0, m1, hi, lo); };
 
     if constexpr (!INTERLEAVED) {
 #pragma unroll
@@ -482,8 +495,8 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
         const uint4 imA = lds128(rowA + 64u * q + D), imB = lds128(rowB + 64u * q + D);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-          mma_bf16_16816(acc[nt][0], reA.x, reB.x, reA.y, reB.y, bri[nt][q][0][0], bri[nt][q][0][1]);
-          mma_bf16_16816(acc[nt][NCH - 1], reA.z, reB.z, reA.w, reB.w, bri[nt][q][1][0], bri[nt][q][1][1]);
+          mma_k0(q == 0, acc[nt][0], reA.x, reB.x, reA.y, reB.y, bri[nt][q][0][0], bri[nt][q][0][1]);
+          mma_k0(q == 0 && NCH == 2, acc[nt][NCH - 1], reA.z, reB.z, reA.w, reB.w, bri[nt][q][1][0], bri[nt][q][1][1]);
           mma_bf16_16816(acc[nt][0], imA.x, imB.x, imA.y, imB.y, bri[nt][q + QI][0][0], bri[nt][q + QI][0][1]);
           mma_bf16_16816(acc[nt][NCH - 1], imA.z, imB.z, imA.w, imB.w, bri[nt][q + QI][1][0], bri[nt][q + QI][1][1]);
         }
@@ -514,8 +527,8 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
         const uint4 xA = lds128(rowA + 64u * c), xB = lds128(rowB + 64u * c);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-          mma_bf16_16816(acc[nt][0], xA.x, xB.x, xA.y, xB.y, bri[nt][c][0][0], bri[nt][c][0][1]);
-          mma_bf16_16816(acc[nt][NCH - 1], xA.z, xB.z, xA.w, xB.w, bri[nt][c][1][0], bri[nt][c][1][1]);
+          mma_k0(c == 0, acc[nt][0], xA.x, xB.x, xA.y, xB.y, bri[nt][c][0][0], bri[nt][c][0][1]);
+          mma_k0(c == 0 && NCH == 2, acc[nt][NCH - 1], xA.z, xB.z, xA.w, xB.w, bri[nt][c][1][0], bri[nt][c][1][1]);
         }
         const uint32_t wA[4] = {xA.x, xA.y, xA.z, xA.w}, wB[4] = {xB.x, xB.y, xB.z, xB.w};
         float mA[4], mB[4];
@@ -537,9 +550,9 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
       }
     }
     // columns 2*rt and 2*rt+1 of a column tile are the two weight parts of query slot 4*nt + rt
-    const int gA = stage_tok0 + tkA;
-    const bool okA = full || (tkA < stage_tokens && gA < seq_len);
-    const bool okB = full || (tkB < stage_tokens && gA + 8 < seq_len);
+    const int gA = tok0 + rg;
+    const bool okA = full || rg < valid;
+    const bool okB = full || rg + 8 < valid;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
       float c4[4];  // the column tile's accumulator, chains summed
@@ -568,6 +581,13 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
       }
     }
   };
+  // Item tt (keys tt*16 .. tt*16 + 15 of the stage) of KV head kvh, any block geometry.
+  auto compute_item = [&](uint32_t stage_addr, int tt, int kvh, int stage_tok0, int tok_end) {
+    const int tkA = tt * kMmaKeys + rg, tkB = tkA + 8;
+    const uint32_t rowA = stage_addr + row_offset(min(tkA, stage_tokens - 1), kvh) + 16u * rt;
+    const uint32_t rowB = stage_addr + row_offset(min(tkB, stage_tokens - 1), kvh) + 16u * rt;
+    compute_rows(rowA, rowB, stage_tok0 + tt * kMmaKeys, tok_end - tt * kMmaKeys);
+  };
 
   const int slots = (n_items + kScoreConsumerWarps - 1) / kScoreConsumerWarps;
   // common case: every warp keeps one virtual head for the whole CTA
@@ -581,10 +601,20 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
   int stage = 0;
   uint32_t parity = 0;
   if (p.block_group > 0) {
+    // 16-token blocks: item = block, and everything but the stage base is fixed for the warp.
     const int G = p.block_group;           // warps (KV heads) per block
     const int j = wid / G, kvh = wid - j * G;
-    for (int it = 0; it < my_tiles; ++it) {
-      if ((tile0 + it) * p.mb + j >= nblk) break;  // this warp's block of the tile (and of all later tiles) does not exist
+    const int first_blk = tile0 * p.mb + j;  // this warp's block in the CTA's first stage-tile
+    const int my_n = first_blk < nblk ? min(my_tiles, (nblk - first_blk + p.mb - 1) / p.mb) : 0;
+    const int refill_n = my_n - p.stages;    // iterations below this one hand their block to a later iteration
+    const uint32_t blk_rel = (uint32_t)(j * p.block_bytes);
+    const uint32_t row_rel = blk_rel + (uint32_t)((kvh * p.head_stride + rg * p.token_stride) * 2) + 16u * rt;
+    const uint32_t rowB_delta = (uint32_t)(16 * p.token_stride);
+    uint32_t stage_off = 0u;                 // stage * stage_bytes
+    unsigned round = 0u;                     // it / stages
+    int tok0 = first_blk * kMmaKeys;
+    int bt_next = p.stages * p.mb + j;       // position (in the CTA's block list) of the block that refills this slot
+    for (int it = 0; it < my_n; ++it) {
       const bool ready = __all_sync(kFull, mbar_wait_bounded(smem_u32(&blk_bar[stage][j]), parity, &s_err));
       if (!ready) {
         if (lane == 0) {
@@ -593,21 +623,39 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
         }
         break;
       }
-      const int stage_tok0 = (tile0 + it) * stage_tokens;
-      const int tok_end = min(seq_len - stage_tok0, stage_tokens);
-      compute_item(smem_base + (uint32_t)(stage * stage_bytes), j, kvh, stage_tok0, (j + 1) * kMmaKeys <= tok_end);
+      const uint32_t rowA = smem_base + stage_off + row_rel;
+      compute_rows(rowA, rowA + rowB_delta, tok0, seq_len - tok0);
       // Hand the block back; the last of the block's G reader warps refills it (a single reader needs no count).
       __syncwarp();
       if (lane == 0) {
         const bool last = G == 1 ? true : release_and_check_last(smem_u32(&blk_empty_bar[stage][j]));
-        if (last && it + p.stages < my_tiles) {
+        if (last && it < refill_n) {
           fence_proxy_async();  // generic-proxy reads of the block before the async-proxy refill
-          issue_block(it + p.stages, stage, j);
+          int blk;
+          if (bt_in_smem) {
+            blk = s_bt[bt_next];
+          } else {
+            blk = bt[tile0 * p.mb + bt_next];
+            if ((unsigned)blk >= (unsigned)p.num_blocks) {
+              flag_status(p.status, TRIATTN_DEV_BAD_BLOCK_ID);
+              blk = 0;
+            }
+          }
+          const uint32_t bar = smem_u32(&blk_bar[stage][j]);
+          mbar_arrive_expect_tx(bar, (uint32_t)p.block_bytes + kTestExtraTxBytes);
+          s_blk_issued[stage][j] = round + 2u;  // armed once before the loop and once per earlier round
+          bulk_copy_g2s(smem_base + stage_off + blk_rel, kbase + (long long)blk * p.block_stride_bytes,
+                        (uint32_t)p.block_bytes, bar);
         }
       }
+      tok0 += stage_tokens;
+      bt_next += p.mb;
+      stage_off += (uint32_t)stage_bytes;
       if (++stage == p.stages) {
         stage = 0;
+        stage_off = 0u;
         parity ^= 1u;
+        ++round;
       }
     }
   } else {
@@ -625,7 +673,7 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
       const int tok_end = min(seq_len - stage_tok0, stage_tokens);  // keys of this stage that exist
       if (fixed) {
         for (int tt = tt_first; tt * kMmaKeys < tok_end; tt += tt_step)
-          compute_item(stage_addr, tt, fixed_kvh, stage_tok0, (tt + 1) * kMmaKeys <= tok_end);
+          compute_item(stage_addr, tt, fixed_kvh, stage_tok0, tok_end);
       } else {
         for (int sl = 0; sl < slots; ++sl) {
           const int item = wid + sl * kScoreConsumerWarps;  // warp-uniform
@@ -637,7 +685,7 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
             load_weights(vh);
             cur_vh = vh;
           }
-          compute_item(stage_addr, tt, vh / nsub, stage_tok0, (tt + 1) * kMmaKeys <= tok_end);
+          compute_item(stage_addr, tt, vh / nsub, stage_tok0, tok_end);
         }
       }
       // release the stage; the warp whose release is the last of the 8 refills it with the tile `stages` ahead

@@ -165,11 +165,7 @@ __global__ void __launch_bounds__(kMaxAggThreads, 1) score_paged_mma_max_kernel(
   for (int i = 0; i < kMaxAggTiles; ++i)
     if (i < n_mine) fetch(wid + i * kMaxAggWarps, i);
 
-  auto split_pair = [&](float m0, float m1, uint32_t& hi, uint32_t& lo) {
-    const uint32_t u0 = __float_as_uint(m0), u1 = __float_as_uint(m1);
-    hi = __byte_perm(u0, u1, 0x7632);
-    lo = pack_bf16x2_rn(m0 - __uint_as_float(u0 & 0xffff0000u), m1 - __uint_as_float(u1 & 0xffff0000u));
-  };
+  auto split_pair = [&](float m0, float m1, uint32_t& hi, uint32_t& lo) { split_bf16x2_hi_lo(m0, m1, hi, lo); };
   // A fragments of one tile (kept for all offsets) and its magnitude term for this thread's two keys
   auto load_tile = [&](uint32_t base, uint32_t (&a)[KS][4], float& magA, float& magB) {
     // lane -> (row, 8-column block) of the 8x8 matrix it addresses: matrices 0..3 = (rows 0-7 | 8-15) x (k 0-7 | 8-15)
