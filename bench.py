@@ -822,6 +822,8 @@ def run_ours(args, world, rank, local):
         line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": torch.get_num_threads(), "kind": kind,
                                 "sample": desc, "seconds": dt}
     print(json.dumps(line), flush=True)
+    if m["device_status"] != 0:
+        raise SystemExit(f"device status {m['device_status']:#x}: a kernel flagged bad metadata or a wait that ran out")
     if parity is not None and not parity["ok"]:
         raise SystemExit("parity gate failed: " + json.dumps(parity))
     if extra.get("c2", {}).get("parity") and not all(extra["c2"]["parity"][x] for x in

@@ -341,3 +341,5 @@ def run_sweep(args, world, rank, local):
                 cpu_cache[ck] = {"keys_per_s": v, "kind": kind, "cores": torch.get_num_threads(), "sample": desc}
             row["cpu"] = cpu_cache[ck]
         print(json.dumps(row), flush=True)
+        if m["device_status"] != 0:
+            raise SystemExit(f"device status {m['device_status']:#x} at sweep point {row['sweep']}")

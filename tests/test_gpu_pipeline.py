@@ -305,3 +305,38 @@ def test_results_do_not_depend_on_the_batch(g, hkv):
         assert r.device_status == 0
         assert torch.equal(r.keep[0, :, :budget[b]], keep_b[b, :, :budget[b]]), b
     assert all(torch.equal(a, b) for a, b in zip(batch, solo))
+
+
+# ------------------------------------------------------------------------------------------ many CTAs, many launches
+@pytest.mark.parametrize("agg", [_native.OFFSETS_MAX, _native.OFFSETS_MEAN])
+def test_scorer_is_repeatable_over_many_launches(agg):
+    """Thousands of CTAs per launch, dozens of launches: no wait may run out (status 0) and every launch must give
+    bit-identical raw scores and moments.  The tensor-core scorer for max aggregation hands a tile to warps that
+    each take every fourth tile; a warp that got ahead of the copies once read a stage before it was refilled,
+    which showed up as a rare wait timeout and scores that differed between launches."""
+    L, B, Hkv, g, D, T = 8, 8, 8, 4, 128, 16384
+    nblk = T // BS
+    gen = torch.Generator(device=DEV).manual_seed(77)
+    cgen = torch.Generator().manual_seed(77)
+    caches = [torch.randn((2, B * nblk + 3, BS, Hkv, D), generator=gen, device=DEV, dtype=torch.float32).to(torch.bfloat16)
+              for _ in range(L)]
+    perm = torch.randperm(B * nblk, generator=cgen)
+    ids = [perm[b * nblk:(b + 1) * nblk].tolist() for b in range(B)]
+    inv = synth.rope_inv_freq(D, 1e6)
+    stats = synth.make_stats(L, Hkv * g, D, inv, cgen)
+    ds = device_stats(stats, oracle.geometric_offsets())
+    view = ops.PagedCacheView.from_layers(caches, kv_axis=0)
+    bt = block_table_tensor(ids)
+    layout = view.layout(B, g, bt.shape[1])
+    seq = torch.full((B,), T, dtype=torch.int32, device=DEV)
+    rs = torch.full((B,), T + 5, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    w = ops.prep_weights_fused(ds, rs, agg)
+    O = int(ds.offsets.numel())
+    raw0, mom0 = ops.score_paged(view, layout, bt, seq, w, agg, O, status=status)
+    raw0, mom0 = raw0.clone(), mom0.clone()
+    for it in range(40):
+        raw, mom = ops.score_paged(view, layout, bt, seq, w, agg, O, status=status)
+        assert int(status.item()) == 0, f"launch {it}: device status {int(status.item())}"
+        assert torch.equal(raw, raw0), f"launch {it}: raw scores differ"
+        assert torch.equal(mom, mom0), f"launch {it}: moments differ"

@@ -86,6 +86,13 @@ __device__ __forceinline__ void tmem_ld16(uint32_t addr, uint32_t (&v)[16]) {
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// One lane of a fully converged warp.  The warp runs the surrounding loop as a whole (barrier waits, descriptor and
+// coordinate arithmetic stay warp-uniform) and only the asynchronous instruction itself is issued by the elected lane.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0u;
+}
 // tiled TMA load of one box (coordinates innermost first) into this CTA's shared memory; no multicast
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, uint32_t bar, int c0, int c1, int c2, int c3) {
   asm volatile(
@@ -133,6 +140,14 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) score_paged_umma_max_kernel(c
   __shared__ __align__(8) uint64_t full_bar[kUmmaStages], empty_bar[kUmmaStages], mag_bar[kUmmaStages], acc_full[2], acc_empty[2];
   __shared__ uint32_t s_tmem;
   __shared__ int s_err;
+  // Tile each stage was last armed for.  A barrier wait names its phase by one parity bit, so it is only exact for a
+  // waiter that is at most one phase away.  The MMA warp, the producer and the epilogue groups visit a stage's
+  // barriers in step with its reuse; the magnitude warps do not: a pair takes every fourth tile, and the copies of
+  // two tiles may land out of order, so a pair can finish tile i - 4 and ask for tile i while tile i - 5 - the
+  // previous user of the same stage - has not even landed.  Its parity wait would then pass at once (the barrier
+  // is still in the phase BEFORE the one it wants) and it would read and release a stage that is not its own.
+  // It therefore first waits until the producer has armed the stage for its tile.
+  __shared__ int s_armed[kUmmaStages];
 
   grid_dependency_wait();  // no global access before the preceding kernel of the stream has completed
   trigger_dependents();
@@ -179,6 +194,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) score_paged_umma_max_kernel(c
     }
     mbar_fence_init();
     s_err = 0;
+    for (int st = 0; st < kUmmaStages; ++st) s_armed[st] = st;  // the first round needs no check
   }
   if (wid == 0) {  // one warp allocates the accumulator columns and gives up the permit
     tmem_alloc(smem_u32(&s_tmem), kUmmaTmemCols);
@@ -304,9 +320,14 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) score_paged_umma_max_kernel(c
         }
       }
     }
-    // moments: one pair of atomics per warp and head (doubles hold the fp32 sums exactly)
+    // Moments: one pair of atomics per warp and head.  A thread's own sums are formed in a fixed order (its keys
+    // are fixed by the tile split) but are not exact; snapping them to a grid (2^-20 for the sum, 2^-10 for the
+    // sum of squares, both far below the fp32 rounding of a single score) makes every later addition - the
+    // shuffles, the atomics of other warps and CTAs in whatever order - exact, so the moments are reproducible.
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
+      s1[q] = (s1[q] + 4294967296.0) - 4294967296.0;            // 2^32: unit in the last place 2^-20
+      s2[q] = (s2[q] + 4398046511104.0) - 4398046511104.0;      // 2^42: unit in the last place 2^-10
 #pragma unroll
       for (int s = 16; s >= 1; s >>= 1) {
         s1[q] += __shfl_xor_sync(0xffffffffu, s1[q], s);
@@ -324,6 +345,23 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) score_paged_umma_max_kernel(c
     const int row0 = (mw & 1) * 64 + lane;  // this thread's 2 keys: rows row0 and row0 + 32 of the tile
     for (int i = mw >> 1; i < my_tiles; i += kUmmaMagWarps / 2) {
       const int stage = i % kUmmaStages;
+      if (i >= kUmmaStages) {
+        // bounded: the producer arms tile i as soon as the stage's previous tile has been released
+        bool armed = false;
+        for (uint32_t n = 0; n < kWaitLimit && !armed; ++n) {
+          int a;
+          asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(a) : "r"(smem_u32(&s_armed[stage])) : "memory");
+          armed = a == i;
+          if (!armed) {
+            if (*err != 0) break;
+            __nanosleep(200);
+          }
+        }
+        if (!__all_sync(0xffffffffu, armed)) {
+          if (lane == 0) fail();
+          break;
+        }
+      }
       if (!__all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&full_bar[stage]), (uint32_t)(i / kUmmaStages) & 1u, err))) {
         if (lane == 0) fail();
         break;
@@ -407,14 +445,27 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) score_paged_umma_max_kernel(c
       // 16-token groups of the tile that hold at least one key of the request (whole boxes are loaded: the rows of
       // a group beyond the request's length come from its last block and are not used)
       const int groups = min(kUmmaTileKeys / 16, (seq_len - t_base + 15) / 16);
-      if (lane == 0) mbar_arrive_expect_tx(bar, (uint32_t)groups * 2u * 2048u + kTestExtraTxBytes);
+      // position of the tile's first token: block (relative to the CTA's first) and offset inside it
+      int bi = t_base / p.bs;
+      int in_blk = t_base - bi * p.bs;
+      bi -= bi0;
+      if (elect_one()) {
+        // published before the arming: whoever reads i here finds the barrier in the phase of tile i or later
+        asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_u32(&s_armed[stage])), "r"(i) : "memory");
+        mbar_arrive_expect_tx(bar, (uint32_t)groups * 2u * 2048u + kTestExtraTxBytes);
+      }
       __syncwarp();
-      const int gi = lane >> 1, half = lane & 1;  // lanes 0..15: one box each
-      if (lane < 16 && gi < groups) {
-        const int t = t_base + 16 * gi;
-        const int bi = t / p.bs;
-        tma_load_4d(a_st + (uint32_t)half * kUmmaKBlockBytes + (uint32_t)gi * 2048u, tmap, bar, half * 64, kvh, t - bi * p.bs,
-                    s_bt[bi - bi0]);
+      for (int gi = 0; gi < groups; ++gi) {
+        const int blk = s_bt[bi];
+        if (elect_one()) {
+          tma_load_4d(a_st + (uint32_t)gi * 2048u, tmap, bar, 0, kvh, in_blk, blk);
+          tma_load_4d(a_st + kUmmaKBlockBytes + (uint32_t)gi * 2048u, tmap, bar, 64, kvh, in_blk, blk);
+        }
+        in_blk += 16;
+        if (in_blk >= p.bs) {
+          in_blk = 0;
+          ++bi;
+        }
       }
     }
     // Nothing may still be landing when the CTA retires: the copies of the last tiles (one per stage) have
@@ -424,25 +475,27 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) score_paged_umma_max_kernel(c
         mbar_wait_bounded(smem_u32(&full_bar[j % kUmmaStages]), (uint32_t)(j / kUmmaStages) & 1u);
   } else {
     // ------------------------------------------------------------------ MMA issue (one thread)
-    if (lane == 0) {
-      // instruction descriptor: D fp32, A and B bf16, both K-major, N = n_cols, M = 128
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n_cols >> 3) << 17) | ((128u >> 4) << 24);
-      const uint64_t desc_b0 = umma_smem_desc(b_base);
-      const uint64_t b_kblock = (uint64_t)((n_cols * 128) >> 4);
-      for (int i = 0; i < my_tiles; ++i) {
-        const int stage = i % kUmmaStages, acc = i & 1, use = i >> 1;
-        if (!mbar_wait_bounded(smem_u32(&full_bar[stage]), (uint32_t)(i / kUmmaStages) & 1u, err)) {
-          fail();
-          break;
-        }
-        if (use > 0 && !mbar_wait_bounded(smem_u32(&acc_empty[acc]), (uint32_t)(use - 1) & 1u, err)) {
-          fail();
-          break;
-        }
-        fence_proxy_async();
-        tc_fence_after();
-        const uint64_t desc_a0 = umma_smem_desc(a_base + (uint32_t)stage * kUmmaStageBytes);
-        const uint32_t d_addr = tmem_base + (uint32_t)(acc * kUmmaAccStride);
+    // The whole warp runs the loop; one elected lane issues the MMAs and commits of a tile.
+    // instruction descriptor: D fp32, A and B bf16, both K-major, N = n_cols, M = 128
+    const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n_cols >> 3) << 17) | ((128u >> 4) << 24);
+    const uint64_t desc_b0 = umma_smem_desc(b_base);
+    const uint64_t b_kblock = (uint64_t)((n_cols * 128) >> 4);
+    for (int i = 0; i < my_tiles; ++i) {
+      const int stage = i % kUmmaStages, acc = i & 1, use = i >> 1;
+      if (!__all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&full_bar[stage]), (uint32_t)(i / kUmmaStages) & 1u, err))) {
+        if (lane == 0) fail();
+        break;
+      }
+      if (use > 0 &&
+          !__all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&acc_empty[acc]), (uint32_t)(use - 1) & 1u, err))) {
+        if (lane == 0) fail();
+        break;
+      }
+      fence_proxy_async();
+      tc_fence_after();
+      const uint64_t desc_a0 = umma_smem_desc(a_base + (uint32_t)stage * kUmmaStageBytes);
+      const uint32_t d_addr = tmem_base + (uint32_t)(acc * kUmmaAccStride);
+      if (elect_one()) {
 #pragma unroll
         for (int part = 0; part < 2; ++part) {
 #pragma unroll
@@ -456,8 +509,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) score_paged_umma_max_kernel(c
         umma_commit(smem_u32(&acc_full[acc]));      // accumulator complete
         umma_commit(smem_u32(&empty_bar[stage]));   // the tensor core no longer reads the stage
       }
+      __syncwarp();
     }
-    __syncwarp();
   }
   // all roles are done (or gave up): free the tensor memory
   tc_fence_before();
