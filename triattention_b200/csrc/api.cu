@@ -159,16 +159,21 @@ const unsigned char* stamp_layer_tensor_maps(const triattn_paged_layout& Y, cons
   EncodeTiledFn encode = encode_tiled_fn();
   if (encode == nullptr) return nullptr;
   slots += (size_t)(g_tmap_call.fetch_add(1) % kTmapRing) * kTmapMaxLayers * 128;
-  // (dim, KV head, token in block, block), strides in bytes for all but the innermost; box = 64 dims x 16 tokens
-  const cuuint64_t dims[4] = {(cuuint64_t)Y.head_dim, (cuuint64_t)Y.num_kv_heads, (cuuint64_t)Y.block_size,
-                              (cuuint64_t)Y.num_blocks};
-  const cuuint64_t strides[3] = {(cuuint64_t)Y.head_stride * 2, (cuuint64_t)Y.token_stride * 2, (cuuint64_t)Y.block_stride * 2};
-  const cuuint32_t box[4] = {64, 1, 16, 1};
-  const cuuint32_t elem[4] = {1, 1, 1, 1};
+  // Rank 5, innermost first: (64 dims = 128 bytes, token mod 8, half of the head vector, token / 8 inside the block,
+  // head slot).  A head slot is one (block, KV head) pair: slots are head_stride apart and a block holds
+  // block_stride / head_stride of them, which covers token-major and head-major blocks alike.  The box is 16 tokens
+  // of one head, 4 KB; in shared memory it reads [8-token group][half][token mod 8][128 B], i.e. complete 8-row
+  // swizzle atoms of the real parts and of the imaginary parts in turn.  (Strides need not ascend.)
+  const cuuint64_t slots_per_block = (cuuint64_t)(Y.block_stride / Y.head_stride);
+  const cuuint64_t dims[5] = {64, 8, 2, (cuuint64_t)Y.block_size / 8, (cuuint64_t)Y.num_blocks * slots_per_block};
+  const cuuint64_t strides[4] = {(cuuint64_t)Y.token_stride * 2, 128, (cuuint64_t)Y.token_stride * 16,
+                                 (cuuint64_t)Y.head_stride * 2};
+  const cuuint32_t box[5] = {64, 8, 2, 2, 1};
+  const cuuint32_t elem[5] = {1, 1, 1, 1, 1};
   TensorMapBytes tmpl;
   static_assert(sizeof(CUtensorMap) == sizeof(TensorMapBytes), "tensor map is 128 bytes");
   // the base address of the template is a placeholder (its own slot: valid device memory, 128-byte aligned)
-  if (encode(reinterpret_cast<CUtensorMap*>(&tmpl), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, slots, dims, strides, box, elem,
+  if (encode(reinterpret_cast<CUtensorMap*>(&tmpl), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, slots, dims, strides, box, elem,
              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return nullptr;
@@ -738,9 +743,11 @@ int score_paged_impl(const triattn_paged_layout* layout, const void* const* k_la
   }
   if (opt.cuda_core_scorer) return TRIATTN_ERR_UNSUPPORTED_SHAPE;
   // max over offsets, head_dim 128: tcgen05 kernel, one CTA per (layer, request, virtual head, run of 128-key tiles)
-  if (p.agg_max && Y.head_dim == 128 && num_offsets >= 1 && 4 * num_offsets <= kUmmaMaxN &&
+  if (p.agg_max && Y.head_dim == 128 && num_offsets >= 1 && 2 * umma_max_cols(num_offsets) <= kUmmaMaxN &&
       umma_max_smem_bytes(umma_max_cols(num_offsets)) <= 220 * 1024 && (Y.block_size % 16) == 0 &&
-      Y.num_layers <= kTmapMaxLayers && (p.block_stride_bytes % 16) == 0 && (Y.token_stride % 8) == 0 && (Y.head_stride % 8) == 0) {
+      Y.num_layers <= kTmapMaxLayers && (p.block_stride_bytes % 16) == 0 && (Y.token_stride % 8) == 0 &&
+      (Y.head_stride % 8) == 0 && Y.head_stride > 0 && (Y.block_stride % Y.head_stride) == 0 &&
+      (long long)Y.num_blocks * (Y.block_stride / Y.head_stride) < (1ll << 31)) {
     const int n_cols = umma_max_cols(num_offsets);
     const int nvh = Y.num_kv_heads * ((gp + 3) / 4);
     const int n_tiles = (p.t_pad + kUmmaTileKeys - 1) / kUmmaTileKeys;
@@ -751,6 +758,7 @@ int score_paged_impl(const triattn_paged_layout* layout, const void* const* k_la
     dim3 grid((unsigned)(nvh * chunks), (unsigned)Y.num_layers, (unsigned)Y.num_reqs);
     const size_t smem = umma_max_smem_bytes(n_cols);
     // the layers' tensor maps are stamped by a one-warp kernel in front of the scorer (its programmatic dependent)
+    p.tmap_slots_per_block = (int)(Y.block_stride / Y.head_stride);
     p.tmaps = stamp_layer_tensor_maps(Y, k_layer_ptrs, st, opt.pdl);
     if (p.tmaps == nullptr) return TRIATTN_ERR_CUDA;
     if (Y.rope_interleaved) {

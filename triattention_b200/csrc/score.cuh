@@ -29,6 +29,7 @@ struct ScoreParams {
   int nhd;       // 1: token-major blocks (head_stride == D, token_stride == Hkv*D)
   int block_group;  // > 0: 16-token blocks, Hkv * mb == 8: block j of a stage is read only by the Hkv warps j*Hkv..(j+1)*Hkv-1
   const unsigned char* tmaps;  // [L] stamped tensor maps of the layers' K caches (tcgen05 scorer only)
+  int tmap_slots_per_block;    // head slots (head_stride apart) per cache block in those maps
   int num_offsets;
   int agg_max;
 };

@@ -244,8 +244,7 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
         atomicAdd(m + 1, s2[0]);
       }
       s1[0] = s2[0] = 0.0;
-      return;
-    }
+    } else {
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
@@ -260,6 +259,7 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
       }
       s1[nt] = 0.0;
       s2[nt] = 0.0;
+    }
     }
   };
   // 4 consecutive weights starting at w -> this thread's column part, packed as (b0, b1)
@@ -315,8 +315,7 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
       }
       // the thread's results: query head rg, keys 2*rt and 2*rt + 1 of each 8-key group
       raw_head = p.raw + (((size_t)l * p.B + b) * p.Hkv + kvh) * (size_t)p.t_pad * gp_total + sub * GP + rg;
-      return;
-    }
+    } else {
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
       const int head = 4 * nt + b_head;
@@ -349,6 +348,7 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
       }
     }
     raw_head = p.raw + (((size_t)l * p.B + b) * p.Hkv + kvh) * (size_t)p.t_pad * gp_total + sub * GP + rt;
+    }
   };
 
   // shared-memory byte offset (inside a stage) of token `tk` of the stage for KV head `kvh`
@@ -474,8 +474,7 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
         s1[0] += (double)t1;
         s2[0] += (double)t2;
       }
-      return;
-    }
+    } else {
     constexpr int NCH = NT == 1 ? 2 : 1;  // accumulator chains per column tile (two independent chains in total)
     float acc[NT][NCH][4];
     auto mma_k0 = [&](bool first, float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -579,6 +578,7 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
         s1[nt] += (double)t1;
         s2[nt] += (double)t2;
       }
+    }
     }
   };
   // Item tt (keys tt*16 .. tt*16 + 15 of the stage) of KV head kvh, any block geometry.

@@ -3,29 +3,38 @@
 //
 // With max aggregation every (query head, offset) pair is its own dot product against the key, so a tile of
 // 128 keys times the O offsets of 4 query heads is a [128 x 128] x [128 x 4*O] matrix product.  The fp32 weights
-// are carried as a bf16 high part and the bf16 of the remainder; both parts accumulate into the SAME column
-// (D = K x W_hi + K x W_lo), so the accumulator of a tile is [128 keys x 4*O] fp32 (68 columns for 17 offsets,
-// padded to 80) and a tile costs sixteen tcgen05.mma of shape M = 128, N = 80, K = 16.
+// are carried as a bf16 high part and the bf16 of the remainder, side by side as columns of one operand
+// (D = K x [W_hi | W_lo]), so the accumulator of a tile is [128 keys x 2 x 4*O] fp32 (2 x 68 columns for 17
+// offsets, each part padded to 80), a tile costs eight tcgen05.mma of shape M = 128, N = 160, K = 16 - the keys
+// are read from shared memory once per K step - and the epilogue adds the two parts.
 //
 // A CTA (one per SM, 18 warps) works on a run of 128-key tiles of one (layer, request, virtual head of <= 4
 // query heads); the weights go to shared memory once, in the K-major 128-byte-swizzled operand layout (40 KB).
 //   * One producer warp streams the keys with tiled TMA loads (cp.async.bulk.tensor, no multicast): the layer's
-//     K cache is described by a rank-4 tensor map (dim, KV head, token in block, block) with the 128-byte
-//     swizzle, so a box of 64 dims x 16 tokens of one head lands in the ring already in the operand layout -
-//     16 loads of 2 KB per tile, real parts into K block 0 and imaginary parts into K block 1 of a 5-stage ring,
-//     completing on an mbarrier.  The engine hands the per-layer base pointers over in DEVICE memory, so the
-//     host encodes one template map for the geometry and a one-warp kernel stamps each layer's address into a
-//     copy of it (tensormap.replace) before the scorer starts.
-//   * One thread of the MMA warp issues the MMAs of a tile into one of two TMEM accumulators and commits to two
-//     mbarriers (accumulator complete; stage no longer read by the tensor core).
+//     K cache is described by a rank-5 tensor map (64 dims, token mod 8, half of the head vector, token / 8 in
+//     the block, head slot) with the 128-byte swizzle, so ONE box brings the 16 tokens of a head that a cache
+//     block holds - 4 KB - and lands in the ring as complete 8-row operand atoms: [8-key group][real | imaginary]
+//     [8 rows x 128 B].  8 loads per tile into a 5-stage ring, completing on an mbarrier.  The producer starts
+//     streaming right after the mbarriers are set up, while the other warps still build the weight operand.
+//     The engine hands the per-layer base pointers over in DEVICE memory, so the host encodes one template map
+//     for the geometry and a one-warp kernel stamps each layer's address into a copy of it (tensormap.replace)
+//     before the scorer starts.
+//   * The MMA warp issues the 8 MMAs of a tile (through one elected lane) into one of two TMEM accumulators and
+//     commits to two mbarriers (accumulator complete; stage no longer read by the tensor core).
 //   * 8 magnitude warps (two per tile, four tiles in flight) form sum_f |k_f| * w_mag in fp32 straight from
 //     the shared-memory tile - no bf16 split of |k| - with 2 keys per thread, so that one load of a frequency's
 //     weights serves 2 keys; the work is latency-bound, hence the many warps.
 //   * 8 epilogue warps in two groups (even / odd tiles).  A thread owns one key (= one TMEM lane): it reads its
-//     accumulator row with tcgen05.ld, takes the max over the offsets of each head, adds the magnitude term and
-//     stores the 4 scores of its key as one 16-byte store.
+//     accumulator row with tcgen05.ld, adds the two weight parts, takes the max over the offsets of each head,
+//     adds the magnitude term and stores the 4 scores of its key as one 16-byte store.
 // Every wait is bounded; a wait that runs out sets TRIATTN_DEV_WAIT_TIMEOUT, all roles leave their loops, the
-// producers drain their copies, and the tensor memory is freed before the CTA exits.
+// producer drains its copies, and the tensor memory is freed before the CTA exits.
+// What limits it (measured with per-role cycle counters): a tile's loads complete about 4000 cycles after they
+// were issued and the stage is released about 3500 cycles after that, so five stages turn over once per ~2000
+// cycles; halving the MMAs per tile, halving the loads per tile, a second producer warp, releasing stages
+// earlier and an L2 prefetch ahead of the loads all left the rate unchanged (the prefetch lowered it): the tiled
+// loads of one SM do not complete faster than ~16 bytes per cycle here, against ~24 for the untiled bulk copies
+// of the mean-aggregation kernel.
 #pragma once
 
 #include "score_mma.cuh"
@@ -35,15 +44,18 @@ namespace triattn {
 constexpr int kUmmaEpiWarps = 8;     // two groups of 4: warp w may only touch TMEM lanes 32*(w % 4) .. +31
 constexpr int kUmmaMagWarps = 8;     // two per tile (64 keys each), four tiles in flight
 constexpr int kUmmaProdWarps = 1;
-constexpr int kUmmaWarps = kUmmaEpiWarps + kUmmaMagWarps + kUmmaProdWarps + 1;  // + the MMA warp
+constexpr int kUmmaMmaWarp = kUmmaEpiWarps + kUmmaMagWarps;  // warp order: epilogue, magnitude, MMA, producers
+constexpr int kUmmaWarps = kUmmaMmaWarp + 1 + kUmmaProdWarps;
 constexpr int kUmmaThreads = kUmmaWarps * 32;
+constexpr int kUmmaSetupThreads = (kUmmaMmaWarp + 1) * 32;  // every warp but the producers prepares the weights
 constexpr int kUmmaTileKeys = 128;
 constexpr int kUmmaStages = 5;      // 160 KB of keys in flight or in use per SM
-constexpr int kUmmaStageBytes = kUmmaTileKeys * 256;  // 32 KB: two K blocks of [128 rows x 128 B]
-constexpr int kUmmaKBlockBytes = kUmmaTileKeys * 128;
+constexpr int kUmmaStageBytes = kUmmaTileKeys * 256;  // 32 KB: 16 groups of 8 keys, each [real | imaginary][8 rows x 128 B]
+constexpr int kUmmaGroupBytes = 2048;                 // one 8-key group: the 1 KB atom of the real parts, then the imaginary parts
+constexpr int kUmmaHalfBytes = 1024;
 constexpr int kUmmaMaxN = 256;
-constexpr int kUmmaAccStride = 128;  // TMEM columns between the two accumulators
-constexpr int kUmmaTmemCols = 256;
+constexpr int kUmmaAccStride = 256;  // TMEM columns between the two accumulators
+constexpr int kUmmaTmemCols = 512;
 constexpr int kUmmaMaxBlocks = 1152; // block ids of a CTA's keys kept in shared memory
 
 // accumulator columns: 4 heads x O offsets, padded to a multiple of 16
@@ -94,10 +106,10 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0u;
 }
 // tiled TMA load of one box (coordinates innermost first) into this CTA's shared memory; no multicast
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, uint32_t bar, int c0, int c1, int c2, int c3) {
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const void* tmap, uint32_t bar, int c0, int c1, int c2, int c3, int c4) {
   asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-      ::"r"(dst), "l"(tmap), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(dst), "l"(tmap), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
       : "memory");
 }
 
@@ -121,17 +133,21 @@ __global__ void stamp_tensor_maps_kernel(const __grid_constant__ TensorMapBytes 
   asm volatile("fence.proxy.tensormap::generic.release.gpu;" ::: "memory");
 }
 
-// shared-memory matrix descriptor: K-major operand, 128-byte swizzle, 8-row groups 1024 bytes apart
-__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr) {
+// shared-memory matrix descriptor: K-major operand, 128-byte swizzle, 8-row groups `sbo_bytes` apart
+__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr, uint32_t sbo_bytes) {
   uint64_t d = (uint64_t)((smem_addr & 0x3ffffu) >> 4);  // start address, 16-byte units
   d |= (uint64_t)1 << 16;                                 // leading byte offset (unused with swizzled K-major): 1
-  d |= (uint64_t)(1024 >> 4) << 32;                       // stride byte offset between 8-row groups
+  d |= (uint64_t)(sbo_bytes >> 4) << 32;                  // stride byte offset between 8-row groups
   d |= (uint64_t)1 << 46;                                 // descriptor version of this architecture
   d |= (uint64_t)2 << 61;                                 // SWIZZLE_128B
   return d;
 }
 // byte offset of 16-byte chunk `c` (0..7) of row `r` inside a [rows x 128 B] swizzled K block
 __device__ __forceinline__ uint32_t swz128(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
+// the same for key row `r` (0..127) of a stage, half `h` (0 real, 1 imaginary parts)
+__device__ __forceinline__ uint32_t key_chunk(int r, int h, int c) {
+  return (uint32_t)((r >> 3) * kUmmaGroupBytes + h * kUmmaHalfBytes + (r & 7) * 128 + ((c ^ (r & 7)) << 4));
+}
 
 template <bool INTERLEAVED>
 __global__ void __launch_bounds__(kUmmaThreads, 1) score_paged_umma_max_kernel(const __grid_constant__ ScoreParams p) {
@@ -213,9 +229,21 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) score_paged_umma_max_kernel(c
     }
     s_bt[i] = blk;
   }
-  // B operands: part 0 = high bf16 parts, part 1 = remainders; row n = o * 4 + q (offset-major, so the head of a
-  // column is a compile-time constant in the epilogue), column k = key dimension; 16-byte chunks of 8 dimensions
-  for (int e = tid; e < 2 * n_cols * 16; e += kUmmaThreads) {
+  // First barrier: mbarriers, TMEM address and block ids are in place.  The producers start streaming keys right
+  // away; the other warps build the weight operands meanwhile and meet at a barrier of their own.
+  __syncthreads();
+  const uint32_t tmem_base = s_tmem;
+  const volatile int* err = &s_err;
+  auto fail = [&]() {
+    if (*err == 0) flag_status(p.status, TRIATTN_DEV_WAIT_TIMEOUT);
+    s_err = 1;
+  };
+  if (wid <= kUmmaMmaWarp) {
+  // B operand: rows 0 .. n_cols-1 = high bf16 parts, rows n_cols .. 2*n_cols-1 = remainders, so that one MMA of
+  // N = 2 * n_cols covers both and the keys (the A operand) are read once per K step; row n = o * 4 + q inside a part
+  // (offset-major, so the head of a column is a compile-time constant in the epilogue), column k = key dimension;
+  // 16-byte chunks of 8 dimensions
+  for (int e = tid; e < 2 * n_cols * 16; e += kUmmaSetupThreads) {
     const int part = e / (n_cols * 16), r = e - part * n_cols * 16;
     const int n = r >> 4, c16 = r & 15;  // chunk c16 covers key dims 8*c16 .. 8*c16+7
     const int o = n >> 2, q = n & 3;
@@ -232,13 +260,13 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) score_paged_umma_max_kernel(c
       bf16_split(x, hi, lo);
       v[i] = part ? lo : hi;
     }
-    const uint32_t dst = b_base + (uint32_t)(part * 2 + (c16 >> 3)) * (uint32_t)(n_cols * 128) + swz128(n, c16 & 7);
+    const uint32_t dst = b_base + (uint32_t)(c16 >> 3) * (uint32_t)(2 * n_cols * 128) + swz128(part * n_cols + n, c16 & 7);
     asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(v[0] | (v[1] << 16)), "r"(v[2] | (v[3] << 16)),
                  "r"(v[4] | (v[5] << 16)), "r"(v[6] | (v[7] << 16))
                  : "memory");
   }
   // magnitude weights, fp32, [f][4 heads]
-  for (int f = tid; f < F; f += kUmmaThreads) {
+  for (int f = tid; f < F; f += kUmmaSetupThreads) {
     float m[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q)
@@ -247,15 +275,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) score_paged_umma_max_kernel(c
   }
   fence_proxy_async();  // the B operands were written through the generic proxy; the tensor core reads them through the async proxy
   tc_fence_before();
-  __syncthreads();
+  asm volatile("bar.sync 1, %0;" ::"r"(kUmmaSetupThreads) : "memory");
   tc_fence_after();
-  const uint32_t tmem_base = s_tmem;
-  const unsigned char* kbase = reinterpret_cast<const unsigned char*>(p.k_ptrs[l]);
-  const volatile int* err = &s_err;
-  auto fail = [&]() {
-    if (*err == 0) flag_status(p.status, TRIATTN_DEV_WAIT_TIMEOUT);
-    s_err = 1;
-  };
+  }
 
   if (wid < kUmmaEpiWarps) {
     // ------------------------------------------------------------------ epilogue: tiles with (i & 1) == group
@@ -275,11 +297,15 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) score_paged_umma_max_kernel(c
       tc_fence_after();
       float best[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       for (int c0 = 0; c0 < n_cols; c0 += 32) {
-        // two 16-column loads in flight per wait
-        uint32_t v[2][16];
+        // columns c0 .. c0+31 of the high part and of the remainder part: up to four 16-column loads per wait
+        uint32_t vh[2][16], vl[2][16];
         const bool second = c0 + 16 < n_cols;
-        tmem_ld16(t_row + (uint32_t)c0, v[0]);
-        if (second) tmem_ld16(t_row + (uint32_t)c0 + 16u, v[1]);
+        tmem_ld16(t_row + (uint32_t)c0, vh[0]);
+        tmem_ld16(t_row + (uint32_t)(n_cols + c0), vl[0]);
+        if (second) {
+          tmem_ld16(t_row + (uint32_t)c0 + 16u, vh[1]);
+          tmem_ld16(t_row + (uint32_t)(n_cols + c0) + 16u, vl[1]);
+        }
         tmem_ld_wait();
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -288,7 +314,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) score_paged_umma_max_kernel(c
           const bool whole = cb + 16 <= n_used;
 #pragma unroll
           for (int j = 0; j < 16; ++j)  // column cb + j = (offset, head j & 3)
-            if (whole || cb + j < n_used) best[j & 3] = fmaxf(best[j & 3], __uint_as_float(v[h][j]));
+            if (whole || cb + j < n_used)
+              best[j & 3] = fmaxf(best[j & 3], __uint_as_float(vh[h][j]) + __uint_as_float(vl[h][j]));
         }
       }
       tc_fence_before();
@@ -381,8 +408,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) score_paged_umma_max_kernel(c
           uint4 re[2], im[2];
 #pragma unroll
           for (int j = 0; j < 2; ++j) {
-            re[j] = lds128(a_st + swz128(row0 + 32 * j, c));
-            im[j] = lds128(a_st + kUmmaKBlockBytes + swz128(row0 + 32 * j, c));
+            re[j] = lds128(a_st + key_chunk(row0 + 32 * j, 0, c));
+            im[j] = lds128(a_st + key_chunk(row0 + 32 * j, 1, c));
           }
 #pragma unroll
           for (int wd = 0; wd < 4; ++wd) {
@@ -402,7 +429,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) score_paged_umma_max_kernel(c
         for (int c = 0; c < 16; ++c) {
           uint4 x[2];
 #pragma unroll
-          for (int j = 0; j < 2; ++j) x[j] = lds128(a_st + (uint32_t)(c >> 3) * kUmmaKBlockBytes + swz128(row0 + 32 * j, c & 7));
+          for (int j = 0; j < 2; ++j) x[j] = lds128(a_st + key_chunk(row0 + 32 * j, c >> 3, c & 7));
 #pragma unroll
           for (int wd = 0; wd < 4; ++wd) {
             const float4 w0 = s_wmag[4 * c + wd];
@@ -423,7 +450,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) score_paged_umma_max_kernel(c
         mbar_arrive(smem_u32(&empty_bar[stage]));  // this warp's reads of the stage's keys are done
       }
     }
-  } else if (wid < kUmmaEpiWarps + kUmmaMagWarps + kUmmaProdWarps) {
+  } else if (wid > kUmmaMmaWarp) {
     // ------------------------------------------------------------------ producer: boxes of keys -> ring (tiled TMA)
     const void* tmap = p.tmaps + (size_t)l * 128;
     // the map was stamped by another kernel through the generic proxy: acquire it for the tensor-map proxy
@@ -452,15 +479,13 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) score_paged_umma_max_kernel(c
       if (elect_one()) {
         // published before the arming: whoever reads i here finds the barrier in the phase of tile i or later
         asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_u32(&s_armed[stage])), "r"(i) : "memory");
-        mbar_arrive_expect_tx(bar, (uint32_t)groups * 2u * 2048u + kTestExtraTxBytes);
+        mbar_arrive_expect_tx(bar, (uint32_t)groups * 4096u + kTestExtraTxBytes);
       }
       __syncwarp();
       for (int gi = 0; gi < groups; ++gi) {
-        const int blk = s_bt[bi];
-        if (elect_one()) {
-          tma_load_4d(a_st + (uint32_t)gi * 2048u, tmap, bar, 0, kvh, in_blk, blk);
-          tma_load_4d(a_st + kUmmaKBlockBytes + (uint32_t)gi * 2048u, tmap, bar, 64, kvh, in_blk, blk);
-        }
+        // one box = 16 tokens of this head, both halves: 4 KB = two 8-key groups of the stage
+        const int slot = s_bt[bi] * p.tmap_slots_per_block + kvh;
+        if (elect_one()) tma_load_5d(a_st + (uint32_t)gi * 4096u, tmap, bar, 0, 0, 0, in_blk >> 3, slot);
         in_blk += 16;
         if (in_blk >= p.bs) {
           in_blk = 0;
@@ -477,9 +502,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) score_paged_umma_max_kernel(c
     // ------------------------------------------------------------------ MMA issue (one thread)
     // The whole warp runs the loop; one elected lane issues the MMAs and commits of a tile.
     // instruction descriptor: D fp32, A and B bf16, both K-major, N = n_cols, M = 128
-    const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n_cols >> 3) << 17) | ((128u >> 4) << 24);
-    const uint64_t desc_b0 = umma_smem_desc(b_base);
-    const uint64_t b_kblock = (uint64_t)((n_cols * 128) >> 4);
+    const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)((2 * n_cols) >> 3) << 17) | ((128u >> 4) << 24);
+    const uint64_t desc_b0 = umma_smem_desc(b_base, 1024u);
+    const uint64_t b_kblock = (uint64_t)((2 * n_cols * 128) >> 4);
     for (int i = 0; i < my_tiles; ++i) {
       const int stage = i % kUmmaStages, acc = i & 1, use = i >> 1;
       if (!__all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&full_bar[stage]), (uint32_t)(i / kUmmaStages) & 1u, err))) {
@@ -493,18 +518,15 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) score_paged_umma_max_kernel(c
       }
       fence_proxy_async();
       tc_fence_after();
-      const uint64_t desc_a0 = umma_smem_desc(a_base + (uint32_t)stage * kUmmaStageBytes);
+      const uint64_t desc_a0 = umma_smem_desc(a_base + (uint32_t)stage * kUmmaStageBytes, (uint32_t)kUmmaGroupBytes);
       const uint32_t d_addr = tmem_base + (uint32_t)(acc * kUmmaAccStride);
       if (elect_one()) {
 #pragma unroll
-        for (int part = 0; part < 2; ++part) {
-#pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            // K step of 16 dims = 32 bytes inside the 128-byte swizzle span; dims 64..127 live in the second K block
-            const uint64_t ka = (uint64_t)((k & 3) * 2) + (k >= 4 ? (uint64_t)(kUmmaKBlockBytes >> 4) : 0);
-            const uint64_t kb = (uint64_t)((k & 3) * 2) + (uint64_t)(part * 2 + (k >= 4 ? 1 : 0)) * b_kblock;
-            umma_bf16(d_addr, desc_a0 + ka, desc_b0 + kb, idesc, (part | k) ? 1u : 0u);
-          }
+        for (int k = 0; k < 8; ++k) {
+          // K step of 16 dims = 32 bytes inside the 128-byte swizzle span; dims 64..127 live in the second K block
+          const uint64_t ka = (uint64_t)((k & 3) * 2) + (k >= 4 ? (uint64_t)(kUmmaHalfBytes >> 4) : 0);
+          const uint64_t kb = (uint64_t)((k & 3) * 2) + (k >= 4 ? b_kblock : 0);
+          umma_bf16(d_addr, desc_a0 + ka, desc_b0 + kb, idesc, k ? 1u : 0u);
         }
         umma_commit(smem_u32(&acc_full[acc]));      // accumulator complete
         umma_commit(smem_u32(&empty_bar[stage]));   // the tensor core no longer reads the stage
