@@ -851,8 +851,16 @@ int finalize_scores_impl(const triattn_paged_layout* layout, const float* raw_sc
 #undef TRIATTN_FIN
 #undef TRIATTN_FIN_LR
   }
-  if (!ensure_dynamic_smem<finalize_scores_kernel>(smem)) return TRIATTN_ERR_CUDA;
-  return launch_kernel(finalize_scores_kernel, grid, dim3(256), smem, st, pdl, p);
+  // general kernel: without a layer reduction every layer is its own output row, so the layers go into the grid
+  // (one layer per CTA: more loads in flight than a per-thread loop over the layers, and less shared memory)
+  size_t smem_gen = smem;
+  if (layer_reduce == TRIATTN_REDUCE_NONE) {
+    if ((long long)Ho * Y.num_layers > 65535) return TRIATTN_ERR_UNSUPPORTED_SHAPE;
+    grid.y = (unsigned)(Ho * Y.num_layers);
+    smem_gen = sizeof(float2) * heads_per_cta;
+  }
+  if (!ensure_dynamic_smem<finalize_scores_kernel>(smem_gen)) return TRIATTN_ERR_CUDA;
+  return launch_kernel(finalize_scores_kernel, grid, dim3(256), smem_gen, st, pdl, p);
 }
 
 }  // namespace

@@ -43,17 +43,24 @@ __global__ void __launch_bounds__(256) finalize_scores_kernel(const __grid_const
   grid_dependency_wait();
   trigger_dependents();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
-  const int ho = blockIdx.y, b = blockIdx.z;
+  const int b = blockIdx.z;
   const int seq_len = min(p.seq_lens[b], p.t_pad);
   const int gp = p.gp;
   const int Hq = p.Hkv * p.g;
   const int Ho = p.head_reduce != TRIATTN_REDUCE_NONE ? 1 : p.Hkv;
+  // with a layer reduction a CTA walks all layers of its output row; without one blockIdx.y also names the layer
+  int ho = blockIdx.y, l_lo = 0, l_hi = p.L;
+  if (p.layer_reduce == TRIATTN_REDUCE_NONE) {
+    l_lo = blockIdx.y / Ho;
+    l_hi = l_lo + 1;
+    ho = blockIdx.y - l_lo * Ho;
+  }
   const int h_begin = p.head_reduce != TRIATTN_REDUCE_NONE ? 0 : ho;
   const int h_end = p.head_reduce != TRIATTN_REDUCE_NONE ? p.Hkv : ho + 1;
   const int nh = (h_end - h_begin) * p.g;  // query heads this CTA reads
   if (blockIdx.x * blockDim.x >= seq_len) return;  // whole CTA beyond the request
-  for (int i = threadIdx.x; i < p.L * nh; i += blockDim.x) {
-    const int l = i / nh, hq = h_begin * p.g + (i - l * nh);
+  for (int i = threadIdx.x; i < (l_hi - l_lo) * nh; i += blockDim.x) {
+    const int l = l_lo + i / nh, hq = h_begin * p.g + i % nh;
     s_ms[i] = mean_rstd_from_moments(p.moments + (((size_t)l * p.B + b) * Hq + hq) * 2, seq_len);
   }
   __syncthreads();
@@ -65,7 +72,7 @@ __global__ void __launch_bounds__(256) finalize_scores_kernel(const __grid_const
   float* out_red = p.out + ((size_t)b * Ho + ho) * (size_t)p.t_pad + t;
   float acc = (p.layer_reduce != TRIATTN_REDUCE_NONE && !p.first_chunk) ? *out_red : 0.f;
 #pragma unroll(kFinalizeUnroll)
-  for (int l = 0; l < p.L; ++l) {
+  for (int l = l_lo; l < l_hi; ++l) {
     float lv = -INFINITY;
     for (int kvh = h_begin; kvh < h_end; ++kvh) {
       float gv;
@@ -73,7 +80,7 @@ __global__ void __launch_bounds__(256) finalize_scores_kernel(const __grid_const
         gv = INFINITY;
       } else {
         const float* r = p.raw + ((((size_t)l * p.B + b) * p.Hkv + kvh) * (size_t)p.t_pad + t) * gp;
-        const float2* ms = s_ms + (size_t)l * nh + (size_t)(kvh - h_begin) * p.g;
+        const float2* ms = s_ms + (size_t)(l - l_lo) * nh + (size_t)(kvh - h_begin) * p.g;
         float mx = -INFINITY, sum = 0.f;
         for (int j0 = 0; j0 < p.g; j0 += 4) {
           float s[4];

@@ -253,7 +253,7 @@ def compress_layer_shared(
     d_seq, d_rs, d_kc, d_pre = meta[0], meta[1], meta[2], meta[3]
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     layout = view.layout(B, g, max_blocks, rope_interleaved=stats.rope_interleaved)
-    w = ops.prep_weights(stats, d_rs, offset_agg, flags)
+    w = ops.prep_weights_fused(stats, d_rs, offset_agg, flags)
     raw, mom = ops.score_paged(view, layout, bt, d_seq, w, offset_agg, int(stats.offsets.numel()), status)
     fin = ops.finalize_scores(layout, raw, mom, d_seq, d_pre if prefill_lens is not None else None, window, normalize,
                               _native.REDUCE_MAX, _native.REDUCE_MAX, _native.REDUCE_NONE)   # [L, B, 1, t_pad]
@@ -273,8 +273,8 @@ def compress_layer_shared(
     kept, removed = [], []
     for b, ids in enumerate(block_ids):
         req = num_required_blocks(keep_counts[b], bs)
-        kept.append([int(x) for x in ids[:req]])
-        removed.append([int(x) for x in ids[req:]])
+        kept.append(ids[:req] if isinstance(ids, np.ndarray) else [int(x) for x in ids[:req]])
+        removed.append(ids[req:] if isinstance(ids, np.ndarray) else [int(x) for x in ids[req:]])
     return CompressResult(keep=keep.view(L, B, keep_pitch), keep_counts=keep_counts, kept_block_ids=kept,
                           removed_block_ids=removed, device_status=bits, h2d_bytes=bt_host.nbytes + meta.numel() * 4,
                           d2h_bytes=4)
