@@ -92,9 +92,9 @@ def measured_peaks():
 # score_paged_umma_max_kernel_c1_2layers.md); K is read once and the raw scores are written once, so traffic grows
 # in proportion to the keys scored and a full launch is this figure x its keys.
 SCORE_DRAM_BYTES_PER_KEY_NCU = {
-    ("mean", 4): (1.074319e9 + 64.09e6) / 4194304.0,     # 271.4 B: 256 B of K + 16 B of raw scores
-    ("mean", 8): (4.299367e9 + 529.69e6) / 16777216.0,   # 287.8 B: 256 B of K + 32 B of raw scores
-    ("max", 4): (1.078619e9 + 64.30e6) / 4194304.0,      # 272.5 B
+    ("mean", 4): (1.074308e9 + 65.17e6) / 4194304.0,     # 271.7 B: 256 B of K + 16 B of raw scores
+    ("mean", 8): (4.299350e9 + 529.34e6) / 16777216.0,   # 287.8 B: 256 B of K + 32 B of raw scores
+    ("max", 4): (1.079208e9 + 66.39e6) / 4194304.0,      # 273.1 B
 }
 
 

@@ -309,6 +309,9 @@ def test_scorer_shape_sweep(hkv, g, D, bs, hnd, rope_style, score_path):
     (2, 4, 128, 16, True, "half"),
     (2, 3, 64, 32, True, "interleaved"),
     (1, 6, 128, 8, False, "interleaved"),
+    (2, 4, 128, 32, False, "interleaved"),  # tcgen05 path: two 16-token boxes per block, interleaved pairs
+    (1, 12, 128, 16, False, "half"),        # tcgen05 path: three virtual heads of 4
+    (3, 2, 128, 48, True, "half"),          # tcgen05 path: head-major 48-token blocks, half-filled column tiles
 ])
 def test_max_aggregation_scorer_shape_sweep(hkv, g, D, bs, hnd, rope_style):
     """The tensor-core scorer for max aggregation against the checker (one column tile per offset, running max)."""
