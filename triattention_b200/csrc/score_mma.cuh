@@ -246,20 +246,20 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
       s1[0] = s2[0] = 0.0;
     } else {
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
+      for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
-      for (int s = 4; s < 32; s <<= 1) {
-        s1[nt] += __shfl_xor_sync(kFull, s1[nt], s);
-        s2[nt] += __shfl_xor_sync(kFull, s2[nt], s);
+        for (int s = 4; s < 32; s <<= 1) {
+          s1[nt] += __shfl_xor_sync(kFull, s1[nt], s);
+          s2[nt] += __shfl_xor_sync(kFull, s2[nt], s);
+        }
+        if (lane < 4 && 4 * nt + lane < cur_nq) {
+          double* m = p.moments + (((size_t)l * p.B + b) * Hq + (size_t)cur_qbase + 4 * nt + lane) * 2;
+          atomicAdd(m, s1[nt]);
+          atomicAdd(m + 1, s2[nt]);
+        }
+        s1[nt] = 0.0;
+        s2[nt] = 0.0;
       }
-      if (lane < 4 && 4 * nt + lane < cur_nq) {
-        double* m = p.moments + (((size_t)l * p.B + b) * Hq + (size_t)cur_qbase + 4 * nt + lane) * 2;
-        atomicAdd(m, s1[nt]);
-        atomicAdd(m + 1, s2[nt]);
-      }
-      s1[nt] = 0.0;
-      s2[nt] = 0.0;
-    }
     }
   };
   // 4 consecutive weights starting at w -> this thread's column part, packed as (b0, b1)
@@ -317,37 +317,37 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
       raw_head = p.raw + (((size_t)l * p.B + b) * p.Hkv + kvh) * (size_t)p.t_pad * gp_total + sub * GP + rg;
     } else {
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      const int head = 4 * nt + b_head;
-      const bool on = head < cur_nq;
-      const float* w = p.weights + ((((size_t)l * p.B + b) * Hq + (size_t)cur_qbase + (on ? head : 0)) * 3) * F;
+      for (int nt = 0; nt < NT; ++nt) {
+        const int head = 4 * nt + b_head;
+        const bool on = head < cur_nq;
+        const float* w = p.weights + ((((size_t)l * p.B + b) * Hq + (size_t)cur_qbase + (on ? head : 0)) * 3) * F;
 #pragma unroll
-      for (int c = 0; c < NQ; ++c) {
+        for (int c = 0; c < NQ; ++c) {
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int d0 = 8 * (rt + 4 * c) + 4 * h;  // the thread's 4 consecutive dims of this MMA
+          for (int h = 0; h < 2; ++h) {
+            const int d0 = 8 * (rt + 4 * c) + 4 * h;  // the thread's 4 consecutive dims of this MMA
+            float x[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int d = d0 + e;
+              // half layout: rows re | im of the weight record are contiguous, so dim d is element d
+              x[e] = INTERLEAVED ? __ldg(w + (d & 1) * F + (d >> 1)) : __ldg(w + d);
+            }
+            pack_part(x, on, bri[nt][c][h][0], bri[nt][c][h][1]);
+          }
+        }
+        const float* wm = w + 2 * F;
+#pragma unroll
+        for (int j = 0; j < NQ; ++j) {
+          // 4 consecutive frequencies per magnitude MMA, in the order compute_item produces |k|
+          const int f0 = INTERLEAVED ? 4 * (rt + 4 * j) : 8 * (rt + 4 * (j >> 1)) + 4 * (j & 1);
           float x[4];
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int d = d0 + e;
-            // half layout: rows re | im of the weight record are contiguous, so dim d is element d
-            x[e] = INTERLEAVED ? __ldg(w + (d & 1) * F + (d >> 1)) : __ldg(w + d);
-          }
-          pack_part(x, on, bri[nt][c][h][0], bri[nt][c][h][1]);
+          for (int e = 0; e < 4; ++e) x[e] = __ldg(wm + f0 + e);
+          pack_part(x, on, bmg[nt][j][0], bmg[nt][j][1]);
         }
       }
-      const float* wm = w + 2 * F;
-#pragma unroll
-      for (int j = 0; j < NQ; ++j) {
-        // 4 consecutive frequencies per magnitude MMA, in the order compute_item produces |k|
-        const int f0 = INTERLEAVED ? 4 * (rt + 4 * j) : 8 * (rt + 4 * (j >> 1)) + 4 * (j & 1);
-        float x[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) x[e] = __ldg(wm + f0 + e);
-        pack_part(x, on, bmg[nt][j][0], bmg[nt][j][1]);
-      }
-    }
-    raw_head = p.raw + (((size_t)l * p.B + b) * p.Hkv + kvh) * (size_t)p.t_pad * gp_total + sub * GP + rt;
+      raw_head = p.raw + (((size_t)l * p.B + b) * p.Hkv + kvh) * (size_t)p.t_pad * gp_total + sub * GP + rt;
     }
   };
 
@@ -475,110 +475,110 @@ score_paged_mma_kernel(const __grid_constant__ ScoreParams p) {
         s2[0] += (double)t2;
       }
     } else {
-    constexpr int NCH = NT == 1 ? 2 : 1;  // accumulator chains per column tile (two independent chains in total)
-    float acc[NT][NCH][4];
-    auto mma_k0 = [&](bool first, float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                      uint32_t b1) {
-      if (first) mma_bf16_16816_first(d, a0, a1, a2, a3, b0, b1);
-      else mma_bf16_16816(d, a0, a1, a2, a3, b0, b1);
-    };
+      constexpr int NCH = NT == 1 ? 2 : 1;  // accumulator chains per column tile (two independent chains in total)
+      float acc[NT][NCH][4];
+      auto mma_k0 = [&](bool first, float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                        uint32_t b1) {
+        if (first) mma_bf16_16816_first(d, a0, a1, a2, a3, b0, b1);
+        else mma_bf16_16816(d, a0, a1, a2, a3, b0, b1);
+      };
 
-    // (hi, lo) bf16x2 pairs of two adjacent |k| values; lo is the bf16 of the exact remainder
-    auto split_pair = [&](float m0, float m1, uint32_t& hi, uint32_t& lo) { split_bf16x2_hi_lo(m0, m1, hi, lo); };
+      // (hi, lo) bf16x2 pairs of two adjacent |k| values; lo is the bf16 of the exact remainder
+      auto split_pair = [&](float m0, float m1, uint32_t& hi, uint32_t& lo) { split_bf16x2_hi_lo(m0, m1, hi, lo); };
 
-    if constexpr (!INTERLEAVED) {
+      if constexpr (!INTERLEAVED) {
 #pragma unroll
-      for (int q = 0; q < NQ / 2; ++q) {
-        constexpr int QI = NQ / 2;
-        const uint4 reA = lds128(rowA + 64u * q), reB = lds128(rowB + 64u * q);
-        const uint4 imA = lds128(rowA + 64u * q + D), imB = lds128(rowB + 64u * q + D);
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          mma_k0(q == 0, acc[nt][0], reA.x, reB.x, reA.y, reB.y, bri[nt][q][0][0], bri[nt][q][0][1]);
-          mma_k0(q == 0 && NCH == 2, acc[nt][NCH - 1], reA.z, reB.z, reA.w, reB.w, bri[nt][q][1][0], bri[nt][q][1][1]);
-          mma_bf16_16816(acc[nt][0], imA.x, imB.x, imA.y, imB.y, bri[nt][q + QI][0][0], bri[nt][q + QI][0][1]);
-          mma_bf16_16816(acc[nt][NCH - 1], imA.z, imB.z, imA.w, imB.w, bri[nt][q + QI][1][0], bri[nt][q + QI][1][1]);
-        }
-        const uint32_t rA[4] = {reA.x, reA.y, reA.z, reA.w}, rB[4] = {reB.x, reB.y, reB.z, reB.w};
-        const uint32_t iA[4] = {imA.x, imA.y, imA.z, imA.w}, iB[4] = {imB.x, imB.y, imB.z, imB.w};
-        uint32_t hA[4], lA[4], hB[4], lB[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float2 ma = sq_mag_bf16x2(rA[i], iA[i]);
-          const float2 mb = sq_mag_bf16x2(rB[i], iB[i]);
-          split_pair(sqrt_approx(ma.x), sqrt_approx(ma.y), hA[i], lA[i]);
-          split_pair(sqrt_approx(mb.x), sqrt_approx(mb.y), hB[i], lB[i]);
-        }
-#pragma unroll
-        for (int hh = 0; hh < 2; ++hh)
+        for (int q = 0; q < NQ / 2; ++q) {
+          constexpr int QI = NQ / 2;
+          const uint4 reA = lds128(rowA + 64u * q), reB = lds128(rowB + 64u * q);
+          const uint4 imA = lds128(rowA + 64u * q + D), imB = lds128(rowB + 64u * q + D);
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
-            const int j = 2 * q + hh;
-            mma_bf16_16816(acc[nt][hh % NCH], hA[2 * hh], hB[2 * hh], hA[2 * hh + 1], hB[2 * hh + 1], bmg[nt][j][0],
-                           bmg[nt][j][1]);
-            mma_bf16_16816(acc[nt][(hh ^ 1) % NCH], lA[2 * hh], lB[2 * hh], lA[2 * hh + 1], lB[2 * hh + 1], bmg[nt][j][0],
-                           bmg[nt][j][1]);
+            mma_k0(q == 0, acc[nt][0], reA.x, reB.x, reA.y, reB.y, bri[nt][q][0][0], bri[nt][q][0][1]);
+            mma_k0(q == 0 && NCH == 2, acc[nt][NCH - 1], reA.z, reB.z, reA.w, reB.w, bri[nt][q][1][0], bri[nt][q][1][1]);
+            mma_bf16_16816(acc[nt][0], imA.x, imB.x, imA.y, imB.y, bri[nt][q + QI][0][0], bri[nt][q + QI][0][1]);
+            mma_bf16_16816(acc[nt][NCH - 1], imA.z, imB.z, imA.w, imB.w, bri[nt][q + QI][1][0], bri[nt][q + QI][1][1]);
           }
+          const uint32_t rA[4] = {reA.x, reA.y, reA.z, reA.w}, rB[4] = {reB.x, reB.y, reB.z, reB.w};
+          const uint32_t iA[4] = {imA.x, imA.y, imA.z, imA.w}, iB[4] = {imB.x, imB.y, imB.z, imB.w};
+          uint32_t hA[4], lA[4], hB[4], lB[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 ma = sq_mag_bf16x2(rA[i], iA[i]);
+            const float2 mb = sq_mag_bf16x2(rB[i], iB[i]);
+            split_pair(sqrt_approx(ma.x), sqrt_approx(ma.y), hA[i], lA[i]);
+            split_pair(sqrt_approx(mb.x), sqrt_approx(mb.y), hB[i], lB[i]);
+          }
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+              const int j = 2 * q + hh;
+              mma_bf16_16816(acc[nt][hh % NCH], hA[2 * hh], hB[2 * hh], hA[2 * hh + 1], hB[2 * hh + 1], bmg[nt][j][0],
+                             bmg[nt][j][1]);
+              mma_bf16_16816(acc[nt][(hh ^ 1) % NCH], lA[2 * hh], lB[2 * hh], lA[2 * hh + 1], lB[2 * hh + 1], bmg[nt][j][0],
+                             bmg[nt][j][1]);
+            }
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < NQ; ++c) {
+          const uint4 xA = lds128(rowA + 64u * c), xB = lds128(rowB + 64u * c);
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            mma_k0(c == 0, acc[nt][0], xA.x, xB.x, xA.y, xB.y, bri[nt][c][0][0], bri[nt][c][0][1]);
+            mma_k0(c == 0 && NCH == 2, acc[nt][NCH - 1], xA.z, xB.z, xA.w, xB.w, bri[nt][c][1][0], bri[nt][c][1][1]);
+          }
+          const uint32_t wA[4] = {xA.x, xA.y, xA.z, xA.w}, wB[4] = {xB.x, xB.y, xB.z, xB.w};
+          float mA[4], mB[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            mA[i] = sqrt_approx(sq_mag_bf16_pair(wA[i]));
+            mB[i] = sqrt_approx(sq_mag_bf16_pair(wB[i]));
+          }
+          uint32_t hA[2], lA[2], hB[2], lB[2];
+          split_pair(mA[0], mA[1], hA[0], lA[0]);
+          split_pair(mA[2], mA[3], hA[1], lA[1]);
+          split_pair(mB[0], mB[1], hB[0], lB[0]);
+          split_pair(mB[2], mB[3], hB[1], lB[1]);
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            mma_bf16_16816(acc[nt][0], hA[0], hB[0], hA[1], hB[1], bmg[nt][c][0], bmg[nt][c][1]);
+            mma_bf16_16816(acc[nt][NCH - 1], lA[0], lB[0], lA[1], lB[1], bmg[nt][c][0], bmg[nt][c][1]);
+          }
+        }
       }
-    } else {
+      // columns 2*rt and 2*rt+1 of a column tile are the two weight parts of query slot 4*nt + rt
+      const int gA = tok0 + rg;
+      const bool okA = full || rg < valid;
+      const bool okB = full || rg + 8 < valid;
 #pragma unroll
-      for (int c = 0; c < NQ; ++c) {
-        const uint4 xA = lds128(rowA + 64u * c), xB = lds128(rowB + 64u * c);
+      for (int nt = 0; nt < NT; ++nt) {
+        float c4[4];  // the column tile's accumulator, chains summed
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          mma_k0(c == 0, acc[nt][0], xA.x, xB.x, xA.y, xB.y, bri[nt][c][0][0], bri[nt][c][0][1]);
-          mma_k0(c == 0 && NCH == 2, acc[nt][NCH - 1], xA.z, xB.z, xA.w, xB.w, bri[nt][c][1][0], bri[nt][c][1][1]);
+        for (int e = 0; e < 4; ++e) {
+          if constexpr (NCH == 2) c4[e] = acc[nt][0][e] + acc[nt][1][e];
+          else c4[e] = acc[nt][0][e];
         }
-        const uint32_t wA[4] = {xA.x, xA.y, xA.z, xA.w}, wB[4] = {xB.x, xB.y, xB.z, xB.w};
-        float mA[4], mB[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          mA[i] = sqrt_approx(sq_mag_bf16_pair(wA[i]));
-          mB[i] = sqrt_approx(sq_mag_bf16_pair(wB[i]));
-        }
-        uint32_t hA[2], lA[2], hB[2], lB[2];
-        split_pair(mA[0], mA[1], hA[0], lA[0]);
-        split_pair(mA[2], mA[3], hA[1], lA[1]);
-        split_pair(mB[0], mB[1], hB[0], lB[0]);
-        split_pair(mB[2], mB[3], hB[1], lB[1]);
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          mma_bf16_16816(acc[nt][0], hA[0], hB[0], hA[1], hB[1], bmg[nt][c][0], bmg[nt][c][1]);
-          mma_bf16_16816(acc[nt][NCH - 1], lA[0], lB[0], lA[1], lB[1], bmg[nt][c][0], bmg[nt][c][1]);
+        const float scA = c4[0] + c4[1];
+        const float scB = c4[2] + c4[3];
+        if (4 * nt + rt < cur_nq) {
+          float* out = raw_head + (size_t)gA * gp_total + 4 * nt;
+          float t1 = 0.f, t2 = 0.f;  // this tile's share, fixed order
+          if (okA) {
+            out[0] = scA;
+            t1 = scA;
+            t2 = scA * scA;
+          }
+          if (okB) {
+            out[(size_t)8 * gp_total] = scB;
+            t1 += scB;
+            t2 = fmaf(scB, scB, t2);
+          }
+          s1[nt] += (double)t1;
+          s2[nt] += (double)t2;
         }
       }
-    }
-    // columns 2*rt and 2*rt+1 of a column tile are the two weight parts of query slot 4*nt + rt
-    const int gA = tok0 + rg;
-    const bool okA = full || rg < valid;
-    const bool okB = full || rg + 8 < valid;
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      float c4[4];  // the column tile's accumulator, chains summed
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        if constexpr (NCH == 2) c4[e] = acc[nt][0][e] + acc[nt][1][e];
-        else c4[e] = acc[nt][0][e];
-      }
-      const float scA = c4[0] + c4[1];
-      const float scB = c4[2] + c4[3];
-      if (4 * nt + rt < cur_nq) {
-        float* out = raw_head + (size_t)gA * gp_total + 4 * nt;
-        float t1 = 0.f, t2 = 0.f;  // this tile's share, fixed order
-        if (okA) {
-          out[0] = scA;
-          t1 = scA;
-          t2 = scA * scA;
-        }
-        if (okB) {
-          out[(size_t)8 * gp_total] = scB;
-          t1 += scB;
-          t2 = fmaf(scB, scB, t2);
-        }
-        s1[nt] += (double)t1;
-        s2[nt] += (double)t2;
-      }
-    }
     }
   };
   // Item tt (keys tt*16 .. tt*16 + 15 of the stage) of KV head kvh, any block geometry.
