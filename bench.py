@@ -72,6 +72,8 @@ def parse_args():
     ap.add_argument("--workspace-mb", type=int, default=0,
                     help="cap the step's scratch (MB): the step is cut into chunks of as many layers as fit")
     ap.add_argument("--decode-steps", type=int, default=4096, help="--config c3: decode steps per request")
+    ap.add_argument("--cuda-graph", action="store_true",
+                    help="replay the step from a CUDA graph once a geometry repeats (engine option use_cuda_graph)")
     ap.add_argument("--sweep", action="store_true", help="length / batch / budget sweep on the Qwen3-8B shape")
     ap.add_argument("--sweep-points", default="", help="comma list of T:B:budget points (default: the built-in grid)")
     return ap.parse_args()
@@ -668,7 +670,7 @@ def measure(args, c, world, rank, local, config_idx):
     saver = PrefixSaver(caches, block_ids, k)
     agg = _native.OFFSETS_MAX if args.aggregation == "max" else _native.OFFSETS_MEAN
     comp = engine.PagedCompressor(stats, window=c["window"], offset_agg=agg,
-                                  use_cuda_graph=os.environ.get("TRIATTN_BENCH_CUDA_GRAPH") == "1",
+                                  use_cuda_graph=bool(args.cuda_graph),
                                   max_workspace_bytes=(args.workspace_mb << 20) if args.workspace_mb else None)
     seq_lens, round_starts, budgets = [T] * B, [T] * B, [k] * B
     keys_per_gpu = L * B * H * T

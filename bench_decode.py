@@ -48,7 +48,8 @@ def _percentiles(xs):
     return {"n": len(s), "p50_ms": pick(0.50), "p90_ms": pick(0.90), "p99_ms": pick(0.99), "mean_ms": statistics.mean(s)}
 
 
-def _simulate(path: str, c, R: int, decode_steps: int, wave: int, gap: int, device, rank: int, world: int):
+def _simulate(path: str, c, R: int, decode_steps: int, wave: int, gap: int, device, rank: int, world: int,
+              cuda_graph: bool = False):
     """One full run of the decode-interleaved workload through ``path`` ('hook' or 'engine').
 
     Returns (records, cache hash): one record per trigger (or per engine call) with its cached length and wall time.
@@ -116,12 +117,13 @@ def _simulate(path: str, c, R: int, decode_steps: int, wave: int, gap: int, devi
         sp = os.path.join(tmp.name, "stats.pt")
         synth.save_stats_pt(synth.SyntheticStats(full.q_mean_real[:, h0:h1].contiguous(), full.q_mean_imag[:, h0:h1].contiguous(),
                                                  full.q_abs_mean[:, h0:h1].contiguous(), inv, D, "half"), sp)
-        cfg = TriAttentionRuntimeConfig(kv_budget=budget, divide_length=slack, window_size=window, sparse_stats_path=sp)
+        cfg = TriAttentionRuntimeConfig(kv_budget=budget, divide_length=slack, window_size=window, sparse_stats_path=sp,
+                                        use_cuda_graph=cuda_graph)
         runner = types.SimpleNamespace(requests={}, kv_caches=caches, cache_config=types.SimpleNamespace(block_size=bs))
         hook_mod.install_runner_compression_hook(runner, cfg)
         hook = runner.triattention_apply_compression
     else:
-        comp = engine.PagedCompressor(stats, window=window)
+        comp = engine.PagedCompressor(stats, window=window, use_cuda_graph=cuda_graph)
 
     def compress(trig, step):
         if path == "hook":
@@ -227,7 +229,7 @@ def run_decode_interleaved(args, world, rank, local):
     for path in ("hook", "engine"):
         B.barrier(world)
         t0 = time.perf_counter()
-        rec, digest, T0 = _simulate(path, c, R, S, wave, gap, device, rank, world)
+        rec, digest, T0 = _simulate(path, c, R, S, wave, gap, device, rank, world, bool(getattr(args, "cuda_graph", False)))
         wall = time.perf_counter() - t0
         hashes[path] = digest
         k = c["budget"]
