@@ -830,7 +830,9 @@ def run_ours(args, world, rank, local):
         "e2e": {"value": keys_per_gpu * world / e2e_s, "unit": UNIT, "h2d_bytes_per_step": m["h2d"],
                 "d2h_bytes_per_step": m["d2h"], "ms_per_step": e2e_s * 1e3,
                 "api": "engine.PagedCompressor.compress (host block tables -> pinned -> H2D, kernels, D2H status)"},
-        "gpu_launches": (3 + 2 * m["n_chunks"]) * args.steps,
+        # prep, top-k, compaction + per chunk of layers: score, finalize (+ the tensor-map stamp of the tcgen05 scorer)
+        "gpu_launches": (3 + (3 if score_kernel_name(c, args.aggregation) == "score_paged_umma_max_kernel" else 2)
+                         * m["n_chunks"]) * args.steps,
         "clocks": m["clocks"], "device_status": m["device_status"],
     }
     if parity is not None:

@@ -171,6 +171,11 @@ int triattn_prep_weights_noalloc(const float* q_mean_real, const float* q_mean_i
  *   k_layer_ptrs : [L] device array of per-layer K base pointers (bf16)
  *   block_table  : [B, max_blocks_per_req] int32; seq_lens : [B] int32
  *   weights      : output of triattn_prep_weights with the same offset_agg / num_offsets
+ * TRIATTN_OFFSETS_MAX with head_dim 128, a block size that is a multiple of 16, at most 128 layers and
+ * block_stride a multiple of head_stride runs on the tcgen05 tensor cores: the call then also launches a
+ * one-warp kernel that writes one 128-byte TMA tensor map per layer into a ring inside the library image
+ * (8 calls deep per device, no allocation).  Calls on one stream are ordered and may be issued without limit;
+ * more than 8 such calls in flight on DIFFERENT streams of one device must be serialised by the caller.
  */
 int triattn_score_paged(const triattn_paged_layout* layout /* host */, const void* const* k_layer_ptrs,
                         const int32_t* block_table, const int32_t* seq_lens, const float* weights,

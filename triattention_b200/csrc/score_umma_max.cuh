@@ -375,7 +375,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) score_paged_umma_max_kernel(c
       if (i >= kUmmaStages) {
         // bounded: the producer arms tile i as soon as the stage's previous tile has been released
         bool armed = false;
-        for (uint32_t n = 0; n < kWaitLimit && !armed; ++n) {
+        for (uint32_t n = 0; n < (kWaitLimit << 4) && !armed; ++n) {  // ~0.2 s of 200 ns naps
           int a;
           asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(a) : "r"(smem_u32(&s_armed[stage])) : "memory");
           armed = a == i;
