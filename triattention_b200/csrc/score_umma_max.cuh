@@ -29,12 +29,14 @@
 //     adds the magnitude term and stores the 4 scores of its key as one 16-byte store.
 // Every wait is bounded; a wait that runs out sets TRIATTN_DEV_WAIT_TIMEOUT, all roles leave their loops, the
 // producer drains its copies, and the tensor memory is freed before the CTA exits.
-// What limits it (measured with per-role cycle counters): a tile's loads complete about 4000 cycles after they
-// were issued and the stage is released about 3500 cycles after that, so five stages turn over once per ~2000
-// cycles; halving the MMAs per tile, halving the loads per tile, a second producer warp, releasing stages
-// earlier and an L2 prefetch ahead of the loads all left the rate unchanged (the prefetch lowered it): the tiled
-// loads of one SM do not complete faster than ~16 bytes per cycle here, against ~24 for the untiled bulk copies
-// of the mean-aggregation kernel.
+// What limits it (measured with per-role cycle counters and with builds in which one consumer at a time does
+// nothing): with every consumer idle the ring alone streams the keys at 0.91 of the measured HBM bandwidth; the
+// whole kernel reaches 0.64, and leaving out the MMAs, the magnitude pass or the epilogue's TMEM reads lifts that
+// to 0.76, 0.75 and 0.68.  The gains rank like the shared-memory bytes each of them moves per 128-key tile
+// (operand reads of the tensor core 72 KB, magnitude pass 48 KB, epilogue 4 KB, on top of the 32 KB the TMA
+// writes): the shared-memory pipe, 128 bytes per cycle, is what the roles compete for.  Halving the MMAs per tile
+// (which removed 32 KB of operand re-reads), halving the loads per tile, a second producer warp, releasing stages
+// earlier and an L2 prefetch ahead of the loads did not change the rate by themselves.
 #pragma once
 
 #include "score_mma.cuh"
