@@ -261,10 +261,14 @@ def test_dense_api(manifest, score_cases, tmp_path):
     assert small_k.shape[2] == 100 and torch.equal(small_idx.cpu(), torch.arange(100))
 
 
-def test_engine_cuda_graph_replay_matches_eager():
-    """The batched step replayed from a CUDA graph gives the keep sets and caches of the eager call."""
+@pytest.mark.parametrize("agg", ["mean", "max"])
+def test_engine_cuda_graph_replay_matches_eager(agg):
+    """The batched step replayed from a CUDA graph gives the keep sets and caches of the eager call (with max
+    aggregation the capture also holds the kernel that stamps the tensor-core scorer's tensor maps)."""
     from gpu_utils import device_stats
-    from triattention_b200 import engine
+    from triattention_b200 import _native, engine
+
+    offset_agg = _native.OFFSETS_MAX if agg == "max" else _native.OFFSETS_MEAN
 
     gen = torch.Generator().manual_seed(synth.seed_for(3, 5))
     L, Hq, Hkv, D, bs, lens, budget = 2, 8, 2, 128, 16, [300, 257], 128
@@ -282,12 +286,12 @@ def test_engine_cuda_graph_replay_matches_eager():
                                         synth.make_values(Hkv, t, D, gen))
         caches.append(c)
     dstats = device_stats(stats, oracle.geometric_offsets())
-    eager = engine.PagedCompressor(dstats, window=32)
+    eager = engine.PagedCompressor(dstats, window=32, offset_agg=offset_agg)
     dc = [c.cuda() for c in caches]
     ref = eager.compress(ops.PagedCacheView.from_layers(dc, kv_axis=0), ids, lens, lens, [budget] * 2)
     ref_keep, ref_caches = ref.keep.clone(), [c.clone() for c in dc]
 
-    graphed = engine.PagedCompressor(dstats, window=32, use_cuda_graph=True)
+    graphed = engine.PagedCompressor(dstats, window=32, use_cuda_graph=True, offset_agg=offset_agg)
     work = [c.cuda() for c in caches]
     view = ops.PagedCacheView.from_layers(work, kv_axis=0)
     for round_ in range(4):  # eager, capture + replay, replay, replay
