@@ -593,7 +593,7 @@ def run_c2_legs(args, world, rank, local):
         res = engine.compress_layer_shared(view, stats, host_ids, seq, rs, bud, window=c["window"], timings=timings)
         e1.record()
         torch.cuda.synchronize()
-        return e0.elapsed_time(e1), timings["allreduce_ms"](), timings["allreduce_bytes"], res
+        return e0.elapsed_time(e1), timings["allreduce_ms"](), timings["allreduce_bytes"], res, timings["exchange"]
 
     for _ in range(2):
         shared_once()
@@ -609,7 +609,7 @@ def run_c2_legs(args, world, rank, local):
     same = bool(torch.equal(lo_t, hi_t))
     out["layer_shared"] = {"ms_per_step": sh_ms, "keys_per_s_per_gpu": keys_per_gpu / (sh_ms * 1e-3),
                            "keys_per_s_total": keys_per_gpu * world / (sh_ms * 1e-3),
-                           "collective": "NCCL all-reduce(MAX) of fp32 [L, B, t_pad] score rows",
+                           "collective": "NCCL " + runs[-1][4],
                            "allreduce_ms": ar_ms, "allreduce_share": ar_ms / sh_ms, "allreduce_bytes": runs[-1][2],
                            "rank_keep_sets_identical": same, "device_status": runs[-1][3].device_status}
     del caches, saver, view, runs, keep, lo_t, hi_t

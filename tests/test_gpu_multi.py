@@ -21,10 +21,10 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _build(seed=77):
+def _build(seed=77, layers=2):
     import synth
     gen = torch.Generator().manual_seed(seed)
-    L, Hq, Hkv, D, bs = 2, 16, 4, 128, 16
+    L, Hq, Hkv, D, bs = layers, 16, 4, 128, 16
     lens = [900, 1500]
     inv = synth.rope_inv_freq(D, 1e6)
     stats = synth.make_stats(L, Hq, D, inv, gen)
@@ -51,7 +51,7 @@ def _dstats(stats, dev):
                            torch.ones_like(stats.q_abs_mean).to(dev), stats.inv_freq.to(dev), offsets.to(dev))
 
 
-def _worker(rank: int, world: int, port: int, q):
+def _worker(rank: int, world: int, port: int, q, layers: int = 2):
     import torch.distributed as dist
     from triattention_b200 import engine, ops, tp
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -59,7 +59,7 @@ def _worker(rank: int, world: int, port: int, q):
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
-        stats, caches, ids, lens, _ = _build()
+        stats, caches, ids, lens, _ = _build(layers=layers)
         budgets, starts = [256, 512], list(lens)
         lo, hi = tp.head_range(4, rank, world)
         local = [c[:, :, :, lo:hi].contiguous().to(dev) for c in caches]     # this rank's KV heads
@@ -79,13 +79,14 @@ def _worker(rank: int, world: int, port: int, q):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_tp2_matches_single_gpu():
+@pytest.mark.parametrize("layers", [2, 3])  # 2: whole layers per rank (reduce-scatter + all-gather); 3: all-reduce
+def test_tp2_matches_single_gpu(layers):
     import torch.multiprocessing as mp
     from triattention_b200 import engine, ops
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, layers)) for r in range(2)]
     for p in procs:
         p.start()
     out = {}
@@ -96,7 +97,7 @@ def test_tp2_matches_single_gpu():
         p.join(timeout=120)
         assert p.exitcode == 0
     # single-GPU reference run with all heads
-    stats, caches, ids, lens, _ = _build()
+    stats, caches, ids, lens, _ = _build(layers=layers)
     budgets, starts = [256, 512], list(lens)
     dev = torch.device("cuda", 0)
     full = _dstats(stats, dev)

@@ -218,8 +218,10 @@ def compress_layer_shared(
     ``process_group`` of the fp32 rows ``[L, B, t_pad]`` makes them global, and the deterministic top-k then
     yields the same keep set on every rank.  ``stats`` must already be the rank's shard (``tp.shard_stats``).
     ``process_group=False`` skips the collective even when torch.distributed is initialised (a rank that holds
-    all heads).  ``timings``, if given, receives ``allreduce_ms`` (a callable: CUDA-event time of the collective,
-    valid after a synchronize) and ``allreduce_bytes``.
+    all heads).  ``timings``, if given, receives ``allreduce_ms`` (a callable: CUDA-event time of the collectives,
+    valid after a synchronize), ``allreduce_bytes`` and ``exchange`` (which form was used: when the layers divide
+    over the ranks, a reduce-scatter of the rows, a top-k on this rank's rows and an all-gather of the keep
+    indices replace the all-reduce).
     Returns keep ``[L, B, keep_pitch]`` (as ``CompressResult.keep``).
     """
     from . import tp as _tp
@@ -257,17 +259,36 @@ def compress_layer_shared(
     raw, mom = ops.score_paged(view, layout, bt, d_seq, w, offset_agg, int(stats.offsets.numel()), status)
     fin = ops.finalize_scores(layout, raw, mom, d_seq, d_pre if prefill_lens is not None else None, window, normalize,
                               _native.REDUCE_MAX, _native.REDUCE_MAX, _native.REDUCE_NONE)   # [L, B, 1, t_pad]
-    if timings is not None:
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-    if process_group is not False:
-        _tp.allreduce_shared_scores(fin, process_group)
-    if timings is not None:
-        e1.record()
-        timings["allreduce_ms"] = lambda: e0.elapsed_time(e1)
-        timings["allreduce_bytes"] = int(fin.numel()) * 4
     L = view.num_layers
-    keep = ops.select_topk(fin.view(L * B, fin.shape[-1]), d_seq, d_kc, B, 1, keep_pitch, status)  # rows (l, b)
+    rows = fin.view(L * B, fin.shape[-1])  # rows (l, b)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if timings is not None else None
+    scatter = process_group is not False and _tp.can_scatter_rows(L, process_group)
+    if ev:
+        ev[0].record()
+    if scatter:
+        # whole layers per rank: finished rows of this rank's layers -> top-k on them -> everybody's keep rows
+        mine = _tp.reduce_scatter_shared_scores(rows, process_group)
+        if ev:
+            ev[1].record()
+        keep_mine = ops.select_topk(mine, d_seq, d_kc, B, 1, keep_pitch, status)
+        if ev:
+            ev[2].record()
+        keep = _tp.all_gather_keep(keep_mine, process_group)
+        if ev:
+            ev[3].record()
+    else:
+        if process_group is not False:
+            _tp.allreduce_shared_scores(fin, process_group)
+        if ev:
+            ev[1].record()
+            ev[2].record()
+            ev[3].record()
+        keep = ops.select_topk(rows, d_seq, d_kc, B, 1, keep_pitch, status)
+    if timings is not None:
+        timings["allreduce_ms"] = lambda: ev[0].elapsed_time(ev[1]) + ev[2].elapsed_time(ev[3])
+        timings["allreduce_bytes"] = int(fin.numel()) * 4 + (int(keep.numel()) * 4 if scatter else 0)
+        timings["exchange"] = ("reduce-scatter(MAX) of the fp32 score rows + all-gather of the keep indices" if scatter
+                               else "all-reduce(MAX) of the fp32 score rows")
     ops.compact_paged(view, layout, bt, d_seq, keep, (B * keep_pitch, keep_pitch, 0), d_kc, status)
     bits = int(status.item())
     kept, removed = [], []

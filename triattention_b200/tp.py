@@ -7,9 +7,11 @@ awareness).  Scores, moments, group max, layer mean, top-k and compaction are al
 per-head mode needs no communication.
 
 Only the layer-shared keep set (one keep list for all heads = top-k of the max over heads,
-selector_hf.py:636-637) spans ranks: every rank reduces its local heads, one all-reduce(MAX) of the fp32
-``[B, t_pad]`` rows makes them global, and the deterministic top-k then yields identical keep sets on every
-rank without a broadcast.
+selector_hf.py:636-637) spans ranks: every rank reduces its local heads and the fp32 ``[L * B, t_pad]`` rows
+are combined by MAX.  When the layers divide over the ranks the exchange is a reduce-scatter (each rank
+receives the finished rows of its share of the layers), a top-k on those rows only, and an all-gather of the
+keep indices: half the bytes of an all-reduce on the wire and 1/N of the selection work per rank.  Otherwise
+one all-reduce(MAX) makes the rows global and the deterministic top-k yields identical keep sets everywhere.
 """
 from __future__ import annotations
 
@@ -46,3 +48,35 @@ def allreduce_shared_scores(local_head_max: torch.Tensor, group: Optional[dist.P
     if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
         dist.all_reduce(local_head_max, op=dist.ReduceOp.MAX, group=group)
     return local_head_max
+
+
+def _group_size(group) -> int:
+    if dist.is_available() and dist.is_initialized():
+        return dist.get_world_size(group)
+    return 1
+
+
+def can_scatter_rows(num_layers: int, group: Optional[dist.ProcessGroup] = None) -> bool:
+    """True when the reduce-scatter form of the exchange applies: several ranks and whole layers per rank."""
+    n = _group_size(group)
+    return n > 1 and num_layers % n == 0
+
+
+def reduce_scatter_shared_scores(rows: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+    """MAX-combine ``rows`` (``[R, t_pad]`` fp32, the same shape on every rank) and return this rank's
+    ``R / world`` consecutive finished rows."""
+    n = _group_size(group)
+    if rows.shape[0] % n:
+        raise ValueError(f"{rows.shape[0]} rows do not divide over {n} ranks")
+    out = torch.empty((rows.shape[0] // n, rows.shape[1]), dtype=rows.dtype, device=rows.device)
+    dist.reduce_scatter_tensor(out, rows.contiguous(), op=dist.ReduceOp.MAX, group=group)
+    return out
+
+
+def all_gather_keep(local_keep: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+    """Concatenate the ranks' keep rows (``[R / world, keep_pitch]`` int32) in rank order: ``[R, keep_pitch]``."""
+    n = _group_size(group)
+    out = torch.empty((local_keep.shape[0] * n, local_keep.shape[1]), dtype=local_keep.dtype, device=local_keep.device)
+    dist.all_gather_into_tensor(out, local_keep.contiguous(), group=group)
+    return out
+
