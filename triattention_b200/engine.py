@@ -257,8 +257,10 @@ def compress_layer_shared(
     layout = view.layout(B, g, max_blocks, rope_interleaved=stats.rope_interleaved)
     w = ops.prep_weights_fused(stats, d_rs, offset_agg, flags)
     raw, mom = ops.score_paged(view, layout, bt, d_seq, w, offset_agg, int(stats.offsets.numel()), status)
+    # max over this rank's KV heads (nothing to reduce with a single local head: the per-head fast kernel serves)
+    head_reduce = _native.REDUCE_MAX if view.num_kv_heads > 1 else _native.REDUCE_NONE
     fin = ops.finalize_scores(layout, raw, mom, d_seq, d_pre if prefill_lens is not None else None, window, normalize,
-                              _native.REDUCE_MAX, _native.REDUCE_MAX, _native.REDUCE_NONE)   # [L, B, 1, t_pad]
+                              _native.REDUCE_MAX, head_reduce, _native.REDUCE_NONE)   # [L, B, 1, t_pad]
     L = view.num_layers
     rows = fin.view(L * B, fin.shape[-1])  # rows (l, b)
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if timings is not None else None
