@@ -335,3 +335,45 @@ def test_flat_pool_entry_matches_slot_arithmetic():
         flat_pool.compact_request_kv_in_place_per_head(dk, dv, req_to_token.to(DEV), 1, keep.flip(1).to(DEV), T)
     with pytest.raises(ValueError, match="exceeds effective_len"):
         flat_pool.compact_request_kv_in_place_per_head(dk, dv, req_to_token.to(DEV), 1, keep.to(DEV), 100)
+
+
+def test_layer_shared_step_with_a_single_local_kv_head():
+    """A rank that holds one KV head has nothing to reduce over heads: the layer-shared step then finalises with the
+    per-head kernel.  Its keep rows must equal the ones the head-reducing kernel gives on the same cache."""
+    from gpu_utils import block_table_tensor, device_stats
+    from triattention_b200 import _native, engine
+
+    gen = torch.Generator().manual_seed(synth.seed_for(3, 9))
+    L, Hq, Hkv, D, bs, lens, budgets = 3, 4, 1, 128, 16, [700, 333], [256, 128]
+    inv = synth.rope_inv_freq(D, 1e6)
+    stats = synth.make_stats(L, Hq, D, inv, gen)
+    nblk = [(t + bs - 1) // bs for t in lens]
+    perm = synth.random_block_ids(sum(nblk), sum(nblk) + 4, gen)
+    ids = [perm[:nblk[0]], perm[nblk[0]:]]
+    caches = []
+    for _ in range(L):
+        c = synth.make_paged_layer(sum(nblk) + 4, bs, Hkv, D, kv_axis=0)
+        for b, t in enumerate(lens):
+            synth.write_tokens_to_paged(c, 0, ids[b], bs, synth.make_rotated_keys(Hkv, t, D, inv, gen),
+                                        synth.make_values(Hkv, t, D, gen))
+        caches.append(c)
+    ds = device_stats(stats, oracle.geometric_offsets())
+    work = [c.cuda() for c in caches]
+    view = ops.PagedCacheView.from_layers(work, kv_axis=0)
+    res = engine.compress_layer_shared(view, ds, ids, lens, lens, budgets, window=32, process_group=False,
+                                       reduce_stats_to_kv_heads=False)
+    assert res.device_status == 0
+    # the same selection through the staged entry points with the head reduction spelled out
+    ref_caches = [c.cuda() for c in caches]
+    rview = ops.PagedCacheView.from_layers(ref_caches, kv_axis=0)
+    bt = block_table_tensor(ids)
+    layout = rview.layout(2, Hq // Hkv, bt.shape[1])
+    meta = torch.tensor([lens, lens, budgets], dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    w = ops.prep_weights_fused(ds, meta[1])
+    raw, mom = ops.score_paged(rview, layout, bt, meta[0], w, status=status)
+    fin = ops.finalize_scores(layout, raw, mom, meta[0], None, 32, True, _native.REDUCE_MAX, _native.REDUCE_MAX,
+                              _native.REDUCE_NONE)
+    keep = ops.select_topk(fin.view(L * 2, fin.shape[-1]), meta[0], meta[2], 2, 1, max(budgets), status)
+    assert int(status.item()) == 0
+    assert torch.equal(res.keep.view(L * 2, -1), keep)
