@@ -600,7 +600,8 @@ int triattn_compress_paged(const triattn_paged_layout* layout, void* const* k_la
   // prep (also clears the moments) -> per chunk of layers: score -> finalize into the running rows -> top-k ->
   // compaction.  Score, top-k and compaction are programmatic dependents of the launch before them; finalize is
   // launched normally: with an unbroken chain of programmatic launches from the scorer to the compaction, the
-  // compaction ran 5 - 19 % slower on B200 (measured on shapes where it dominates), with any link normal it did not.
+  // compaction ran 5 - 19 % slower on B200 (measured on shapes where it dominates), with any link normal it did not
+  // (an SM that never runs empty between the kernels may keep the scorer's large shared-memory carve-out).
   rc = prep_weights_fused_impl(q_mean_real, q_mean_imag, q_abs_mean, freq_scale_sq, omega, offsets, round_start,
                                Y.num_layers, Y.num_reqs, Hq, F, num_offsets, offset_agg, flags, weights, moments, st,
                                false);
