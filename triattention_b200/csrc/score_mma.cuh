@@ -11,8 +11,9 @@
 //     register is moved between the load and the MMA (with keys as the A operand every A quad interleaves the
 //     words of two loads, which cost 57 moves per 16 keys and made this shape issue-bound).
 //   * re / im are the cached bf16 values themselves, so they go from shared memory into the MMA unchanged.
-//   * |k| = sqrt(re^2 + im^2) is computed in fp32 on the CUDA cores and split into a bf16 high part (by
-//     truncation) and the bf16 of the exact remainder; both parts extend the K dimension of the magnitude MMAs.
+//   * |k| = sqrt(re^2 + im^2) is computed in fp32 on the CUDA cores (re^2 + im^2 by mixed-precision FMAs straight
+//     from the packed bf16 pair) and split into its bf16 rounding and the bf16 of the exact remainder (four
+//     instructions per pair of values); both parts extend the K dimension of the magnitude MMAs.
 //   * The K dimension of a dot product may be visited in any order, so every thread reads whole 16-byte chunks
 //     of "its" two keys (rows lane/4 and lane/4+8 of the tile, chunks lane%4 + 4q) and the weight fragments are
 //     permuted once per CTA to match: no ldmatrix and no cross-lane reduction; a thread ends up with the two
