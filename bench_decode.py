@@ -110,7 +110,7 @@ def _simulate(path: str, c, R: int, decode_steps: int, wave: int, gap: int, devi
     records = []
 
     # ---- compression paths
-    if path == "hook":
+    if path in ("hook", "hook_batch"):
         # the hook loads its statistics from a file, as in serving: this rank's rows in the calibration format
         import tempfile
         tmp = tempfile.TemporaryDirectory()
@@ -122,6 +122,7 @@ def _simulate(path: str, c, R: int, decode_steps: int, wave: int, gap: int, devi
         runner = types.SimpleNamespace(requests={}, kv_caches=caches, cache_config=types.SimpleNamespace(block_size=bs))
         hook_mod.install_runner_compression_hook(runner, cfg)
         hook = runner.triattention_apply_compression
+        hook_batch = runner.triattention_apply_compression_batch
     else:
         comp = engine.PagedCompressor(stats, window=window, use_cuda_graph=cuda_graph)
 
@@ -141,6 +142,28 @@ def _simulate(path: str, c, R: int, decode_steps: int, wave: int, gap: int, devi
                     raise RuntimeError(f"hook did not compress request {r}: {out}")
                 records.append({"T": cur[r], "n": 1, "ms": dt * 1e3})
                 kept = list(runner.requests[req].block_ids[0])
+                pool.give(ids[r][len(kept):])
+                ids[r] = kept
+                cur[r] = int(out["cache_len_after"])
+        elif path == "hook_batch":
+            # the step's triggered requests through the batched hook: the per-request contract, one native call
+            reqs = []
+            for r in trig:
+                req = f"r{r}"
+                runner.requests[req] = types.SimpleNamespace(block_ids=(list(ids[r]),), num_computed_tokens=seen[r])
+                reqs.append((req, CompressionSignal(req, True, "length_threshold", cur[r] + 1, step, None, False, 0, 1)))
+            so = types.SimpleNamespace(num_scheduled_tokens={req: 1 for req, _ in reqs})
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            outs = hook_batch(reqs, so)
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t0
+            records.append({"T": [cur[r] for r in trig], "n": len(trig), "ms": dt * 1e3})
+            for r in trig:
+                out = outs[f"r{r}"]
+                if not out.get("applied"):
+                    raise RuntimeError(f"batched hook did not compress request {r}: {out}")
+                kept = list(runner.requests[f"r{r}"].block_ids[0])
                 pool.give(ids[r][len(kept):])
                 ids[r] = kept
                 cur[r] = int(out["cache_len_after"])
@@ -226,7 +249,7 @@ def run_decode_interleaved(args, world, rank, local):
     peak, peak_kind = B.measured_peaks()
     out = {}
     hashes = {}
-    for path in ("hook", "engine"):
+    for path in ("hook", "hook_batch", "engine"):
         B.barrier(world)
         t0 = time.perf_counter()
         rec, digest, T0 = _simulate(path, c, R, S, wave, gap, device, rank, world, bool(getattr(args, "cuda_graph", False)))
@@ -275,7 +298,7 @@ def run_decode_interleaved(args, world, rank, local):
         "e2e": {"value": hook_all["keys_per_s"] * world, "unit": B.UNIT, "api": "per-request hook "
                 "(install_runner_compression_hook contract)", "ms_per_trigger": hook_all["ms_per_trigger"],
                 "h2d_bytes_per_step": None, "d2h_bytes_per_step": 4},
-        "paths": out, "paths_leave_identical_caches": hashes["hook"] == hashes["engine"],
+        "paths": out, "paths_leave_identical_caches": hashes["hook"] == hashes["engine"] == hashes["hook_batch"],
         "roofline": {"bound": "hbm", "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                      "frac": out["engine"]["steady_state"].get("hbm_frac"),
                      "note": "steady-state triggers through the batched engine: (256 B per key + 1024 B per kept token) / time"},
@@ -284,8 +307,8 @@ def run_decode_interleaved(args, world, rank, local):
     if cpu:
         line["cpu_baseline"] = cpu
     print(json.dumps(line), flush=True)
-    if hashes["hook"] != hashes["engine"]:
-        raise SystemExit("hook path and engine path left different caches")
+    if not (hashes["hook"] == hashes["engine"] == hashes["hook_batch"]):
+        raise SystemExit("the hook, batched-hook and engine paths left different caches")
 
 
 # ----------------------------------------------------------------------------- sweep (BASELINE config 4)

@@ -10,6 +10,7 @@ Run where a checkout of the reference is available (default: a directory
     python tests/golden/make_golden.py --only bench_shapes   # only bench_shape_cases.npz (minutes of CPU time)
     python tests/golden/make_golden.py --only shipped_stats  # only shipped_stats_cases.npz
     python tests/golden/make_golden.py --only stats_loader   # only the stats_loader_cases entry of manifest.json
+    python tests/golden/make_golden.py --only runner_actions # only runner_action_cases.json
 
 The reference is imported unmodified, on CPU, with three test-side shims:
 
@@ -668,6 +669,20 @@ def gen_calibration_cases(out: dict):
     out["calibration_cases"] = {"file": "calibration_cases.npz", "cases": cases}
 
 
+def gen_runner_action_cases(out: dict):
+    """Events, state-store calls and fatal errors of the reference's worker-side action driver
+    (runtime/runner_compression_actions.py:11-237) on the scripted scenarios of tests/runner_action_scenarios.py."""
+    from triattention.vllm.runtime.executor import CompressionExecutionResult
+    from triattention.vllm.runtime.runner_compression_actions import execute_runner_compression_actions
+    from triattention.vllm.runtime.signals import CompressionSignal
+    import runner_action_scenarios as ras
+
+    cases = {sc["name"]: ras.run_scenario(execute_runner_compression_actions, CompressionSignal,
+                                          CompressionExecutionResult, sc) for sc in ras.scenarios()}
+    (HERE / "runner_action_cases.json").write_text(json.dumps(cases, indent=1, sort_keys=True))
+    out["runner_action_cases"] = {"file": "runner_action_cases.json", "cases": sorted(cases)}
+
+
 PARTIAL = {
     # --only <name>: regenerate one group of fixtures and merge it into manifest.json
     "calibration": lambda out: gen_calibration_cases(out),
@@ -675,6 +690,7 @@ PARTIAL = {
     "bench_shapes": lambda out: gen_bench_shape_cases(out),
     "shipped_stats": lambda out: gen_shipped_stats_cases(out),
     "stats_loader": lambda out: gen_stats_loader_cases(out),
+    "runner_actions": lambda out: gen_runner_action_cases(out),
 }
 
 
@@ -697,6 +713,7 @@ def main():
     gen_hook_cases(out)
     gen_input_patch_cases(out)
     gen_calibration_cases(out)
+    gen_runner_action_cases(out)
     (HERE / "manifest.json").write_text(json.dumps(out, indent=1, sort_keys=True))
     print("wrote", [p.name for p in HERE.iterdir()])
 

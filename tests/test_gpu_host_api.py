@@ -377,3 +377,65 @@ def test_layer_shared_step_with_a_single_local_kv_head():
     keep = ops.select_topk(fin.view(L * 2, fin.shape[-1]), meta[0], meta[2], 2, 1, max(budgets), status)
     assert int(status.item()) == 0
     assert torch.equal(res.keep.view(L * 2, -1), keep)
+
+
+def test_batched_hook_equals_the_per_request_hook(tmp_path):
+    """All triggered requests of a step through ``triattention_apply_compression_batch`` (one native call) against
+    the per-request hook called request after request: same result dictionaries, block tables and cache bytes."""
+    gen = torch.Generator().manual_seed(synth.seed_for(5, 1))
+    L, Hq, Hkv, D, bs, budget, window = 2, 8, 2, 128, 16, 256, 32
+    inv = synth.rope_inv_freq(D, 1e6)
+    stats = synth.make_stats(L, Hq, D, inv, gen)
+    sp = tmp_path / "s.pt"
+    synth.save_stats_pt(stats, sp)
+    lens = {"a": 900, "b": 100, "c": 640, "d": 1301}       # b is under budget, the others compress
+    nblk = {r: (t + bs - 1) // bs for r, t in lens.items()}
+    perm = synth.random_block_ids(sum(nblk.values()), sum(nblk.values()) + 6, gen)
+    ids, o = {}, 0
+    for r, n in nblk.items():
+        ids[r] = perm[o:o + n]
+        o += n
+    caches = []
+    for _ in range(L):
+        c = synth.make_paged_layer(sum(nblk.values()) + 6, bs, Hkv, D, kv_axis=0)
+        for r, t in lens.items():
+            synth.write_tokens_to_paged(c, 0, ids[r], bs, synth.make_rotated_keys(Hkv, t, D, inv, gen),
+                                        synth.make_values(Hkv, t, D, gen))
+        caches.append(c)
+
+    def make():
+        dc = [c.to(DEV) for c in caches]
+        cfg = TriAttentionRuntimeConfig(kv_budget=budget, window_size=window, sparse_stats_path=sp)
+        runner = types.SimpleNamespace(
+            requests={r: types.SimpleNamespace(block_ids=(list(ids[r]),), num_computed_tokens=t) for r, t in lens.items()},
+            kv_caches=dc, cache_config=types.SimpleNamespace(block_size=bs))
+        hook_mod.install_runner_compression_hook(runner, cfg)
+        return runner, dc
+
+    def sig(req):
+        return CompressionSignal(req_id=req, should_compress=True, reason="length_threshold",
+                                 estimated_cache_len=lens[req] + 1, step=3, kv_usage=None, protect_prefill=False,
+                                 prefill_len=0, scheduled_tokens=1)
+
+    so = types.SimpleNamespace(num_scheduled_tokens={r: 1 for r in lens})
+    order = ["a", "b", "zz", "c", "d"]                      # zz does not exist
+    one, one_caches = make()
+    want = {r: one.triattention_apply_compression(req_id=r, signal=sig(r) if r in lens else
+                                                  CompressionSignal(req_id=r, should_compress=True, reason="x",
+                                                                    estimated_cache_len=5, step=3, kv_usage=None,
+                                                                    protect_prefill=False, prefill_len=0, scheduled_tokens=1),
+                                                  scheduler_output=so) for r in order}
+    many, many_caches = make()
+    reqs = [(r, sig(r) if r in lens else CompressionSignal(req_id=r, should_compress=True, reason="x", estimated_cache_len=5,
+                                                            step=3, kv_usage=None, protect_prefill=False, prefill_len=0,
+                                                            scheduled_tokens=1)) for r in order]
+    got = many.triattention_apply_compression_batch(reqs, so)
+    assert got == want
+    assert want["a"]["applied"] and want["c"]["applied"] and want["d"]["applied"] and not want["b"]["applied"]
+    for r in lens:
+        assert many.requests[r].block_ids == one.requests[r].block_ids
+    for a, b in zip(many_caches, one_caches):
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+    # a second round on the same runners: the compressed requests are now under budget + slack on both paths
+    assert many.triattention_apply_compression_batch(reqs, so) == {
+        r: one.triattention_apply_compression(req_id=r, signal=s, scheduler_output=so) for r, s in reqs}

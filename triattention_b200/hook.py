@@ -181,6 +181,19 @@ def resolve_group_tensors(base_runner: Any) -> dict:
 
 
 # ------------------------------------------------------------------------------------------ group pipeline
+@dataclass
+class _Pending:
+    """A request that passed the host-side checks of the hook and is about to be compacted."""
+    req_id: Any
+    signal: Any
+    strict: bool
+    rt: Any
+    req_state: Any
+    original_ids: Any
+    mutable: list
+    block_size: int
+
+
 @dataclass(frozen=True)
 class GroupPipelineOutcome:
     cache_len_after: int
@@ -245,8 +258,11 @@ def _select_for_group(*, req_id, gid, layer_tensors, block_ids, block_size, tota
 def run_group_compaction_pipeline(*, req_id, signal, config, strict, num_computed_tokens, effective_tokens,
                                   budget_total, block_size, mutable_block_ids_by_group, group_tensors,
                                   select_keep_indices, select_keep_indices_for_group, shared_compact_fn,
-                                  per_head_compact_fn):
-    """Select and compact every KV-cache group of one request (hook_group_pipeline.py:42-155)."""
+                                  per_head_compact_fn, fused_results: Optional[dict] = None):
+    """Select and compact every KV-cache group of one request (hook_group_pipeline.py:42-155).
+
+    ``fused_results`` maps a group id to the result of a fused native step that has ALREADY run for this request
+    (the batched hook runs it for several requests at once); such a group is only finished here."""
     compacted_any = False
     cache_len_after = None
     label = "fallback"
@@ -266,7 +282,9 @@ def run_group_compaction_pipeline(*, req_id, signal, config, strict, num_compute
         # Default mode with the native selector and the native compaction: one fused call does the whole group.
         fused = getattr(select_keep_indices_for_group, "_fused_group_compress", None)
         fused_result = None
-        if (fused is not None and per_head_compact_fn is _NATIVE_PER_HEAD_COMPACT
+        if fused_results is not None and gid in fused_results:
+            fused_result = fused_results[gid]
+        elif (fused is not None and per_head_compact_fn is _NATIVE_PER_HEAD_COMPACT
                 and not bool(getattr(config, "preserve_dropped_tokens", False))
                 and config.pruning_mode == "per_head"
                 and config.per_head_selection_semantics == "hf_aligned_global_per_head"
@@ -365,6 +383,35 @@ def run_group_compaction_pipeline(*, req_id, signal, config, strict, num_compute
     return GroupPipelineOutcome(int(cache_len_after), str(label), reclaim_groups, mutable_block_ids_by_group)
 
 
+def fused_step_allowed(config, per_head_compact_fn=_NATIVE_PER_HEAD_COMPACT) -> bool:
+    """Configuration under which a KV-cache group is handled by the fused native step (default mode)."""
+    return (per_head_compact_fn is _NATIVE_PER_HEAD_COMPACT
+            and not bool(getattr(config, "preserve_dropped_tokens", False))
+            and config.pruning_mode == "per_head"
+            and config.per_head_selection_semantics == "hf_aligned_global_per_head")
+
+
+def compactable_groups(*, signal, num_computed_tokens, effective_tokens, budget_total, block_size,
+                       mutable_block_ids_by_group, group_tensors) -> list:
+    """The groups run_group_compaction_pipeline would work on, with the arguments of their selection step:
+    ``[(gid, layer_tensors, item)]``, item = keyword arguments of the fused step other than the tensors."""
+    out = []
+    for gid, block_ids in enumerate(mutable_block_ids_by_group):
+        if not block_ids:
+            continue
+        layer_tensors = group_tensors.get(gid)
+        if not layer_tensors:
+            continue
+        total = min(effective_tokens, len(block_ids) * block_size)
+        if total <= 0:
+            continue
+        out.append((gid, layer_tensors, dict(
+            block_ids=block_ids, total_tokens=total, prefill_len=min(int(signal.prefill_len), total),
+            protect_prefill=signal.protect_prefill, round_start=int(max(0, num_computed_tokens)),
+            budget_total=min(budget_total, total))))
+    return out
+
+
 # ------------------------------------------------------------------------------------------ hook factory
 def make_runner_compression_hook(base_runner: Any, config: TriAttentionRuntimeConfig) -> Callable[..., dict]:
     """Create the hook bound to ``base_runner`` (hook_impl.py:29-165)."""
@@ -375,7 +422,9 @@ def make_runner_compression_hook(base_runner: Any, config: TriAttentionRuntimeCo
     cache: dict = {"group_tensors": None}
     compressed_once: set = set()
 
-    def _hook(req_id: str, signal: CompressionSignal, scheduler_output: Any) -> dict:
+    def _plan(req_id: str, signal: CompressionSignal, scheduler_output: Any):
+        """Host-side part of a call up to the point where the cache is touched: a result dictionary when the
+        request is skipped, otherwise what the compaction step needs."""
         setattr(base_runner, "_triattention_active_req_id", req_id)
         strict = bool(config.enable_experimental_kv_compaction and config.require_triton_scoring)
         ctx = resolve_hook_request_context(base_runner=base_runner, req_id=req_id, scheduler_output=scheduler_output)
@@ -414,18 +463,25 @@ def make_runner_compression_hook(base_runner: Any, config: TriAttentionRuntimeCo
         if not isinstance(original_ids, (list, tuple)):
             return {"applied": False, "reason": "invalid_block_ids_container"}
         mutable = [[int(b) for b in g] if isinstance(g, (list, tuple)) else None for g in original_ids]
-
         if cache["group_tensors"] is None:
             cache["group_tensors"] = resolve_group_tensors(base_runner)
+        return _Pending(req_id=req_id, signal=signal, strict=strict, rt=rt, req_state=req_state,
+                        original_ids=original_ids, mutable=mutable, block_size=block_size)
+
+    def _finish(p: "_Pending", fused_results: Optional[dict] = None) -> dict:
+        """Selection, compaction and bookkeeping of one planned request."""
+        rt, original_ids, req_state = p.rt, p.original_ids, p.req_state
+        setattr(base_runner, "_triattention_active_req_id", p.req_id)
         out = run_group_compaction_pipeline(
-            req_id=req_id, signal=signal, config=config, strict=strict, num_computed_tokens=rt.num_computed_tokens,
-            effective_tokens=rt.effective_tokens, budget_total=rt.budget_total, block_size=block_size,
-            mutable_block_ids_by_group=mutable, group_tensors=cache["group_tensors"],
+            req_id=p.req_id, signal=p.signal, config=config, strict=p.strict, num_computed_tokens=rt.num_computed_tokens,
+            effective_tokens=rt.effective_tokens, budget_total=rt.budget_total, block_size=p.block_size,
+            mutable_block_ids_by_group=p.mutable, group_tensors=cache["group_tensors"],
             select_keep_indices=sel_layer, select_keep_indices_for_group=sel_group,
-            shared_compact_fn=compact_request_kv_in_place, per_head_compact_fn=compact_request_kv_in_place_per_head)
+            shared_compact_fn=compact_request_kv_in_place, per_head_compact_fn=compact_request_kv_in_place_per_head,
+            fused_results=fused_results)
         if isinstance(out, dict):
             return out
-        compressed_once.add(req_id)
+        compressed_once.add(p.req_id)
 
         reclaim_event = None
         if config.enable_experimental_block_reclaim and out.block_reclaim_groups:
@@ -438,13 +494,68 @@ def make_runner_compression_hook(base_runner: Any, config: TriAttentionRuntimeCo
             budget_total=rt.budget_total, recent_unabsorbed_tokens=rt.recent_unabsorbed_tokens,
             block_reclaim=reclaim_event).to_hook_result_dict()
 
+    def _hook(req_id: str, signal: CompressionSignal, scheduler_output: Any) -> dict:
+        p = _plan(req_id, signal, scheduler_output)
+        return p if isinstance(p, dict) else _finish(p)
+
+    def _hook_batch(requests, scheduler_output: Any) -> dict:
+        """All triggered requests of a step: ``requests`` = [(req_id, signal), ...]; returns {req_id: result} with
+        the dictionaries the per-request hook would return, in one native call for every request that is in the
+        default mode and has a single compactable KV-cache group (the others go through the per-request path)."""
+        results: dict = {}
+        pending = []
+        for req_id, signal in requests:
+            p = _plan(req_id, signal, scheduler_output)
+            if isinstance(p, dict):
+                results[req_id] = p
+            else:
+                pending.append(p)
+        fused_batch = getattr(sel_group, "_fused_group_compress_batch", None)
+        fused_for: dict = {}   # req_id -> {gid: selector result}
+        failed: dict = {}      # req_id -> soft failure result
+        if fused_batch is not None and fused_step_allowed(config) and len(pending) > 1:
+            by_group: dict = {}
+            for p in pending:
+                groups = compactable_groups(
+                    signal=p.signal, num_computed_tokens=p.rt.num_computed_tokens, effective_tokens=p.rt.effective_tokens,
+                    budget_total=p.rt.budget_total, block_size=p.block_size, mutable_block_ids_by_group=p.mutable,
+                    group_tensors=cache["group_tensors"])
+                if len(groups) == 1 and len({t.device for _, t in groups[0][1]}) == 1:
+                    gid, layer_tensors, item = groups[0]
+                    by_group.setdefault(gid, (layer_tensors, []))[1].append((p, item))
+            for gid, (layer_tensors, members) in by_group.items():
+                if len(members) < 2:
+                    continue
+                try:
+                    outs = fused_batch(caches=[t for _, t in layer_tensors], layer_indices=[i for i, _ in layer_tensors],
+                                       items=[item for _, item in members])
+                except FusedCompactionError as exc:
+                    first = layer_tensors[0][0] if layer_tensors else -1
+                    for p, _ in members:
+                        failed[p.req_id] = {"applied": False,
+                                            "reason": f"compaction_failed:g{gid}:l{first}:{type(exc).__name__}"}
+                    continue
+                except Exception as exc:
+                    raise RuntimeError(f"{TRITON_SCORING_REQUIRED_MARKER}:req={members[0][0].req_id}:gid={gid}:"
+                                       f"global_per_head:{type(exc).__name__}") from exc
+                for (p, _), res in zip(members, outs):
+                    if res is not None:
+                        fused_for[p.req_id] = {gid: res}
+        for p in pending:
+            results[p.req_id] = failed.get(p.req_id) or _finish(p, fused_for.get(p.req_id))
+        return results
+
     # TRIATTN_RUNTIME_PERF_PROFILE / TRIATTN_RUNTIME_NVTX: aggregated TRIATTN_PERF lines, NVTX range per call
-    return HookPerfProfile.from_env().wrap(_hook)
+    wrapped = HookPerfProfile.from_env().wrap(_hook)
+    setattr(wrapped, "batch", _hook_batch)
+    return wrapped
 
 
 def install_runner_compression_hook(base_runner: Any, config: TriAttentionRuntimeConfig) -> None:
     """Install the hook on the runner unless one is already present (hook_impl.py:174-185)."""
     if hasattr(base_runner, "triattention_apply_compression"):
         return
-    setattr(base_runner, "triattention_apply_compression",
-            make_runner_compression_hook(base_runner=base_runner, config=config))
+    hook = make_runner_compression_hook(base_runner=base_runner, config=config)
+    setattr(base_runner, "triattention_apply_compression", hook)
+    # all triggered requests of a step in one call (no counterpart in the reference, whose worker loops over them)
+    setattr(base_runner, "triattention_apply_compression_batch", getattr(hook, "batch", None))

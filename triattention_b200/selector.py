@@ -323,7 +323,76 @@ def build_triattention_selector(
             "cache_len_after": k,
         }
 
+    def _compress_group_fused_batch(*, caches: list, layer_indices: list, items: list) -> list:
+        """The fused default-mode step for SEVERAL requests of one KV-cache group in one native call.
+
+        ``items`` holds, per request, the keyword arguments of :func:`_compress_group_fused` other than ``caches``
+        and ``layer_indices``.  Returns one entry per item: the selector's result dictionary, or None for a request
+        that needs the staged path (same rules as the single-request form).  Results equal those of calling the
+        single-request form request after request: the scorer's moments and the top-k do not depend on the batch.
+        """
+        out: list = [None] * len(items)
+        if requested_mode != "per_head" or semantics != "hf_aligned_global_per_head" or not caches:
+            return out
+        todo = []
+        for n, it in enumerate(items):
+            total, budget = int(it["total_tokens"]), int(it["budget_total"])
+            if total <= budget:
+                continue
+            if it["protect_prefill"] and config.include_prefill_in_budget and int(it["prefill_len"]) > budget:
+                continue
+            k = min(budget, total)
+            if k > 0:
+                todo.append((n, k))
+        if not todo:
+            return out
+        from . import engine as _engine
+        agg = os.environ.get("TRIATTN_RUNTIME_DEBUG_GROUP_PERHEAD_AGG_MODE", "mean").strip().lower()
+        if agg not in {"mean", "max"}:
+            agg = "mean"
+        try:
+            view = ops.PagedCacheView.from_layers(caches, kv_axis=kv_axis_hint(caches[0]))
+            dstats = _packed([int(i) for i in layer_indices], view.device, None)
+            _group_of(dstats.num_heads, view.num_kv_heads)
+            comp = fused_engines.get(str(view.device))
+            if comp is None:
+                comp = _engine.PagedCompressor(dstats, use_cuda_graph=bool(getattr(config, "use_cuda_graph", False)))
+                fused_engines[str(view.device)] = comp
+            comp.stats = dstats
+            comp.window = int(config.window_size) if config.window_size > 0 else 0
+            comp.normalize = bool(config.sparse_normalize_scores)
+            comp.offset_agg, comp.flags = offset_agg, flags
+            comp.layer_reduce = _native.REDUCE_MAX if agg == "max" else _native.REDUCE_MEAN
+            ids, totals, starts, ks, prefill = [], [], [], [], []
+            for n, k in todo:
+                it = items[n]
+                b = it["block_ids"]
+                ids.append(b.tolist() if isinstance(b, torch.Tensor) else [int(x) for x in b])
+                totals.append(int(it["total_tokens"]))
+                starts.append(int(it["round_start"]))
+                ks.append(k)
+                prefill.append(int(it["prefill_len"]) if (it["protect_prefill"] and int(it["prefill_len"]) > 0) else 0)
+            res = comp.compress(view, ids, totals, starts, ks, prefill_lens=prefill if any(prefill) else None)
+            if res.device_status & ~_native.DEV_BAD_KEEP_INDEX:
+                raise _native.NativeLibraryError(f"device_status:{res.device_status}")
+        except _native.NativeLibraryError as exc:
+            raise RuntimeError(f"{TRITON_SCORING_REQUIRED_MARKER}:score_failed:{type(exc).__name__}") from exc
+        if res.device_status:
+            raise FusedCompactionError(f"device_status:{res.device_status}")
+        for row, (n, k) in enumerate(todo):
+            out[n] = {
+                "mode": "per_head",
+                "indices": res.keep[row][:, :k],  # a view of the engine's buffer, valid until its next call
+                "semantic": "hf_aligned_global_per_head",
+                "group_agg_mode": agg,
+                "debug_group_layer_indices": [int(i) for i in layer_indices],
+                "debug_recent_count": _recent(int(items[n]["total_tokens"])),
+                "cache_len_after": k,
+            }
+        return out
+
     setattr(_select_keep_indices, "_supports_paged", True)
     setattr(_select_keep_indices_for_group_per_head, "_supports_paged_group", True)
     setattr(_select_keep_indices_for_group_per_head, "_fused_group_compress", _compress_group_fused)
+    setattr(_select_keep_indices_for_group_per_head, "_fused_group_compress_batch", _compress_group_fused_batch)
     return _select_keep_indices, _select_keep_indices_for_group_per_head, "enabled"
