@@ -11,6 +11,7 @@ Run where a checkout of the reference is available (default: a directory
     python tests/golden/make_golden.py --only shipped_stats  # only shipped_stats_cases.npz
     python tests/golden/make_golden.py --only stats_loader   # only the stats_loader_cases entry of manifest.json
     python tests/golden/make_golden.py --only runner_actions # only runner_action_cases.json
+    python tests/golden/make_golden.py --only state_store    # only state_store_cases.json
 
 The reference is imported unmodified, on CPU, with three test-side shims:
 
@@ -683,6 +684,15 @@ def gen_runner_action_cases(out: dict):
     out["runner_action_cases"] = {"file": "runner_action_cases.json", "cases": sorted(cases)}
 
 
+def gen_state_store_cases(out: dict):
+    """Snapshots of the reference's RequestStateStore (runtime/state.py:35-153) along tests/state_store_scenario.py."""
+    from triattention.vllm.runtime.state import RequestStateStore
+    import state_store_scenario as sss
+
+    (HERE / "state_store_cases.json").write_text(json.dumps(sss.replay(RequestStateStore()), indent=1, sort_keys=True))
+    out["state_store_cases"] = {"file": "state_store_cases.json", "calls": len(sss.CALLS)}
+
+
 PARTIAL = {
     # --only <name>: regenerate one group of fixtures and merge it into manifest.json
     "calibration": lambda out: gen_calibration_cases(out),
@@ -691,6 +701,7 @@ PARTIAL = {
     "shipped_stats": lambda out: gen_shipped_stats_cases(out),
     "stats_loader": lambda out: gen_stats_loader_cases(out),
     "runner_actions": lambda out: gen_runner_action_cases(out),
+    "state_store": lambda out: gen_state_store_cases(out),
 }
 
 
@@ -714,6 +725,7 @@ def main():
     gen_input_patch_cases(out)
     gen_calibration_cases(out)
     gen_runner_action_cases(out)
+    gen_state_store_cases(out)
     (HERE / "manifest.json").write_text(json.dumps(out, indent=1, sort_keys=True))
     print("wrote", [p.name for p in HERE.iterdir()])
 

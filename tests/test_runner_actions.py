@@ -71,3 +71,42 @@ def test_runner_hook_executor_uses_the_batch_hook_when_present():
     out = ex.execute_batch([("a", None), ("b", None)], None)
     assert calls[-1] == ("batch", ["a", "b"]) and out["a"].reason == "under_budget" and out["a"].applied is False
     assert runner_actions.RunnerHookCompressionExecutor(types.SimpleNamespace()).execute("a", None, None).reason == "runner_hook_missing"
+
+
+def test_state_store_follows_the_reference_call_by_call():
+    """RequestStateStore against the reference's own snapshots (tests/golden/state_store_cases.json)."""
+    import state_store_scenario as sss
+    from triattention_b200.state import RequestStateStore
+
+    want = json.loads((Path(__file__).resolve().parent / "golden" / "state_store_cases.json").read_text())
+    got = json.loads(json.dumps(sss.replay(RequestStateStore())))
+    assert len(got) == len(want) == len(sss.CALLS)
+    for n, (g, w) in enumerate(zip(got, want)):
+        assert g == w, (n, sss.CALLS[n])
+
+
+def test_driver_with_the_real_state_store():
+    """The driver's bookkeeping lands in the store: counts, steps, lengths and the de-duplication of the next step."""
+    from triattention_b200.state import RequestStateStore
+    import logging
+    import types
+    store = RequestStateStore()
+    store.ensure("a", 100, False)
+    store.mark_trigger("a", "length_threshold", 4)
+    sig = CompressionSignal(req_id="a", should_compress=True, reason="length_threshold", estimated_cache_len=2177, step=4,
+                            kv_usage=None, protect_prefill=False, prefill_len=100, scheduled_tokens=1)
+    ex = ras.ScriptedExecutor({"a": ras.APPLIED}, runner_actions.CompressionExecutionResult)
+    log = logging.getLogger("t")
+    log.disabled = True
+    so = types.SimpleNamespace(scheduled_cached_reqs=types.SimpleNamespace(req_ids=["a"], num_computed_tokens=[2176]))
+    kw = dict(executor=ex, state_store=store, scheduler_output=so, strict_no_downgrade=False,
+              allowed_strict_skip_reasons=set(), logger=log, log_decisions=False)
+    ev = runner_actions.execute_runner_compression_actions(signals={"a": sig}, **kw)
+    st = store.get("a")
+    assert ev[0]["status"] == "applied" and st.compression_count == 1 and st.last_compression_step == 4
+    assert st.current_cache_len == 2049 and st.last_absorbed_cache_len == 2048 and st.nct_at_last_compression == 2176
+    # the scheduler repeats the signal one step later (batch-queue race): it must not run again
+    again = CompressionSignal(req_id="a", should_compress=True, reason="length_threshold", estimated_cache_len=2178, step=5,
+                              kv_usage=None, protect_prefill=False, prefill_len=100, scheduled_tokens=1)
+    ev = runner_actions.execute_runner_compression_actions(signals={"a": again}, **kw)
+    assert ev[0]["reason"] == "batch_queue_dedup" and ex.calls == ["a"] and store.get("a").compression_count == 1
