@@ -340,3 +340,48 @@ def test_scorer_is_repeatable_over_many_launches(agg, g):
         assert int(status.item()) == 0, f"launch {it}: device status {int(status.item())}"
         assert torch.equal(raw, raw0), f"launch {it}: raw scores differ"
         assert torch.equal(mom, mom0), f"launch {it}: moments differ"
+
+
+def test_max_aggregation_calls_on_two_streams():
+    """The tensor-core scorer for max aggregation keeps its per-layer tensor maps in a ring that is 8 calls deep:
+    calls issued alternately on two streams (6 in flight, different caches) must give what the same calls give
+    one after the other on one stream."""
+    L, B, Hkv, g, D, T = 3, 2, 2, 4, 128, 2048
+    nblk = T // BS
+    gen = torch.Generator(device=DEV).manual_seed(5)
+    cgen = torch.Generator().manual_seed(5)
+    inv = synth.rope_inv_freq(D, 1e6)
+    stats = synth.make_stats(L, Hkv * g, D, inv, cgen)
+    ds = device_stats(stats, oracle.geometric_offsets())
+    O = int(ds.offsets.numel())
+    agg = _native.OFFSETS_MAX
+    jobs = []
+    for j in range(6):
+        caches = [torch.randn((2, B * nblk + 2, BS, Hkv, D), generator=gen, device=DEV, dtype=torch.float32)
+                  .to(torch.bfloat16) for _ in range(L)]
+        perm = torch.randperm(B * nblk, generator=cgen)
+        ids = [perm[b * nblk:(b + 1) * nblk].tolist() for b in range(B)]
+        view = ops.PagedCacheView.from_layers(caches, kv_axis=0)
+        bt = block_table_tensor(ids)
+        jobs.append(dict(caches=caches, view=view, bt=bt, layout=view.layout(B, g, bt.shape[1])))
+    seq = torch.full((B,), T, dtype=torch.int32, device=DEV)
+    rs = torch.full((B,), T + 3, dtype=torch.int32, device=DEV)
+    w = ops.prep_weights_fused(ds, rs, agg)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    want = []
+    for job in jobs:
+        raw, mom = ops.score_paged(job["view"], job["layout"], job["bt"], seq, w, agg, O, status=status)
+        want.append((raw.clone(), mom.clone()))
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    got = []
+    for j, job in enumerate(jobs):
+        st = streams[j % 2]
+        st.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(st):
+            got.append(ops.score_paged(job["view"], job["layout"], job["bt"], seq, w, agg, O, status=status))
+    for st in streams:
+        st.synchronize()
+    assert int(status.item()) == 0
+    for j, ((raw, mom), (raw0, mom0)) in enumerate(zip(got, want)):
+        assert torch.equal(raw, raw0) and torch.equal(mom, mom0), j
