@@ -12,6 +12,7 @@ Run where a checkout of the reference is available (default: a directory
     python tests/golden/make_golden.py --only stats_loader   # only the stats_loader_cases entry of manifest.json
     python tests/golden/make_golden.py --only runner_actions # only runner_action_cases.json
     python tests/golden/make_golden.py --only state_store    # only state_store_cases.json
+    python tests/golden/make_golden.py --only effective_overrides  # only effective_override_cases.json
 
 The reference is imported unmodified, on CPU, with three test-side shims:
 
@@ -693,6 +694,17 @@ def gen_state_store_cases(out: dict):
     out["state_store_cases"] = {"file": "state_store_cases.json", "calls": len(sss.CALLS)}
 
 
+def gen_effective_override_cases(out: dict):
+    """Results of the reference's build_effective_sparse_overrides (runtime/effective_overrides.py:209-359) on the
+    scripted steps of tests/effective_override_scenarios.py."""
+    from triattention.vllm.runtime.effective_overrides import build_effective_sparse_overrides
+    import effective_override_scenarios as eos
+
+    cases = {sc["name"]: eos.run_scenario(build_effective_sparse_overrides, sc) for sc in eos.scenarios()}
+    (HERE / "effective_override_cases.json").write_text(json.dumps(cases, indent=1, sort_keys=True))
+    out["effective_override_cases"] = {"file": "effective_override_cases.json", "cases": sorted(cases)}
+
+
 PARTIAL = {
     # --only <name>: regenerate one group of fixtures and merge it into manifest.json
     "calibration": lambda out: gen_calibration_cases(out),
@@ -702,6 +714,7 @@ PARTIAL = {
     "stats_loader": lambda out: gen_stats_loader_cases(out),
     "runner_actions": lambda out: gen_runner_action_cases(out),
     "state_store": lambda out: gen_state_store_cases(out),
+    "effective_overrides": lambda out: gen_effective_override_cases(out),
 }
 
 
@@ -726,6 +739,7 @@ def main():
     gen_calibration_cases(out)
     gen_runner_action_cases(out)
     gen_state_store_cases(out)
+    gen_effective_override_cases(out)
     (HERE / "manifest.json").write_text(json.dumps(out, indent=1, sort_keys=True))
     print("wrote", [p.name for p in HERE.iterdir()])
 
