@@ -13,6 +13,7 @@ Run where a checkout of the reference is available (default: a directory
     python tests/golden/make_golden.py --only runner_actions # only runner_action_cases.json
     python tests/golden/make_golden.py --only state_store    # only state_store_cases.json
     python tests/golden/make_golden.py --only effective_overrides  # only effective_override_cases.json
+    python tests/golden/make_golden.py --only step_lifecycle # only step_lifecycle_cases.json
 
 The reference is imported unmodified, on CPU, with three test-side shims:
 
@@ -705,6 +706,26 @@ def gen_effective_override_cases(out: dict):
     out["effective_override_cases"] = {"file": "effective_override_cases.json", "cases": sorted(cases)}
 
 
+def gen_step_lifecycle_cases(out: dict):
+    """The reference's step life cycle (runtime/runner_state_updates.py + runner_compression_actions.py + state.py) along
+    tests/step_lifecycle_scenario.py: events and store snapshots after every step."""
+    import types
+    from triattention.vllm.runtime import runner_compression_actions as rca, runner_state_updates as rsu
+    from triattention.vllm.runtime.executor import CompressionExecutionResult
+    from triattention.vllm.runtime.signals import CompressionSignal
+    from triattention.vllm.runtime.state import RequestStateStore
+    import step_lifecycle_scenario as sls
+
+    mod = types.SimpleNamespace(
+        register_new_requests=rsu.register_new_requests, cleanup_finished_requests=rsu.cleanup_finished_requests,
+        mark_preemptions=rsu.mark_preemptions, mark_resumed=rsu.mark_resumed,
+        consume_runner_signals=rsu.consume_runner_signals,
+        execute_runner_compression_actions=rca.execute_runner_compression_actions)
+    res = sls.replay(mod, RequestStateStore(), CompressionSignal, CompressionExecutionResult)
+    (HERE / "step_lifecycle_cases.json").write_text(json.dumps(res, indent=1, sort_keys=True))
+    out["step_lifecycle_cases"] = {"file": "step_lifecycle_cases.json", "steps": len(sls.STEPS)}
+
+
 PARTIAL = {
     # --only <name>: regenerate one group of fixtures and merge it into manifest.json
     "calibration": lambda out: gen_calibration_cases(out),
@@ -715,6 +736,7 @@ PARTIAL = {
     "runner_actions": lambda out: gen_runner_action_cases(out),
     "state_store": lambda out: gen_state_store_cases(out),
     "effective_overrides": lambda out: gen_effective_override_cases(out),
+    "step_lifecycle": lambda out: gen_step_lifecycle_cases(out),
 }
 
 
@@ -740,6 +762,7 @@ def main():
     gen_runner_action_cases(out)
     gen_state_store_cases(out)
     gen_effective_override_cases(out)
+    gen_step_lifecycle_cases(out)
     (HERE / "manifest.json").write_text(json.dumps(out, indent=1, sort_keys=True))
     print("wrote", [p.name for p in HERE.iterdir()])
 

@@ -110,3 +110,17 @@ def test_driver_with_the_real_state_store():
                               kv_usage=None, protect_prefill=False, prefill_len=100, scheduled_tokens=1)
     ev = runner_actions.execute_runner_compression_actions(signals={"a": again}, **kw)
     assert ev[0]["reason"] == "batch_queue_dedup" and ex.calls == ["a"] and store.get("a").compression_count == 1
+
+
+def test_step_life_cycle_follows_the_reference():
+    """Arrivals, departures, preemptions, signals and actions over four steps: events and store snapshots after each
+    step equal the reference's (tests/golden/step_lifecycle_cases.json)."""
+    import step_lifecycle_scenario as sls
+    from triattention_b200.state import RequestStateStore
+
+    want = json.loads((Path(__file__).resolve().parent / "golden" / "step_lifecycle_cases.json").read_text())
+    got = json.loads(json.dumps(sls.replay(runner_actions, RequestStateStore(), CompressionSignal,
+                                           runner_actions.CompressionExecutionResult)))
+    assert len(got) == len(want)
+    for n, (g, w) in enumerate(zip(got, want)):
+        assert g == w, n

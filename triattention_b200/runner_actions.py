@@ -186,3 +186,77 @@ def execute_runner_compression_actions(*, executor: Any, state_store: Any, sched
             events.append(_event(req_id, signal, "skipped", result.reason, result.cache_len_after,
                                  details=result.details, block_reclaim=reclaim))
     return events
+
+
+# ------------------------------------------------------------------------------------------ step life cycle
+# What the worker does with a scheduler output BEFORE the actions of the step: keep the request-state store in step
+# with arrivals, departures, preemptions and with the cache lengths the signals report (the reference's
+# runtime/runner_state_updates.py:20-128).  The hook reads the lengths kept here.
+def full_prefill_len(request_like: Any) -> int:
+    """Prompt length of a new request from whichever field the engine version carries; the largest wins."""
+    seen = [0]
+    for attr in ("prompt_token_ids", "prefill_token_ids"):
+        ids = getattr(request_like, attr, None)
+        if ids is not None:
+            try:
+                seen.append(len(ids))
+            except Exception:
+                pass
+    for attr in ("prompt_token_ids_len", "num_prompt_tokens"):
+        raw = getattr(request_like, attr, None)
+        if raw is not None:
+            try:
+                seen.append(int(raw))
+            except (TypeError, ValueError):
+                pass
+    return max(seen)
+
+
+def register_new_requests(*, state_store: Any, scheduler_output: Any, protect_prefill: bool) -> None:
+    for new_req in scheduler_output.scheduled_new_reqs:
+        state_store.ensure(req_id=new_req.req_id, prefill_len=full_prefill_len(new_req), protect_prefill=protect_prefill)
+
+
+def cleanup_finished_requests(*, state_store: Any, scheduler_output: Any) -> None:
+    for req_id in scheduler_output.finished_req_ids:
+        state_store.remove(req_id)
+
+
+def mark_preemptions(*, state_store: Any, scheduler_output: Any) -> None:
+    for req_id in getattr(scheduler_output, "preempted_req_ids", None) or ():
+        state_store.mark_preempted(req_id)
+
+
+def mark_resumed(*, state_store: Any, scheduler_output: Any) -> None:
+    cached = getattr(scheduler_output, "scheduled_cached_reqs", None)
+    if cached is None:
+        return
+    resumed = getattr(cached, "resumed_req_ids", None)
+    if resumed is None:
+        resumed = getattr(cached, "req_ids", []) or []
+    for req_id in resumed:
+        state_store.mark_resumed(req_id)
+
+
+def consume_runner_signals(*, state_store: Any, scheduler_output: Any, last_step: int, logger: logging.Logger,
+                           log_decisions: bool, legacy_compressed_estimate: bool = False) -> tuple:
+    """``(step, signals)`` of the scheduler output, after recording every signal in the store.
+
+    Before a request's first compression its cache length is the scheduler's estimate; afterwards the worker keeps its
+    own count (previous length + tokens scheduled in this step), because the scheduler's snapshots may lag the
+    compaction in asynchronous scheduling (``legacy_compressed_estimate`` restores the scheduler's estimate, the
+    reference's TRIATTN_RUNTIME_LEGACY_COMPRESSED_ESTIMATE switch)."""
+    step = getattr(scheduler_output, "triattention_step", last_step + 1)
+    signals = getattr(scheduler_output, "triattention_signals", {})
+    for req_id, signal in signals.items():
+        state = state_store.ensure(req_id=req_id, prefill_len=signal.prefill_len, protect_prefill=signal.protect_prefill)
+        estimate = max(0, int(signal.estimated_cache_len))
+        if int(getattr(state, "compression_count", 0)) > 0 and not legacy_compressed_estimate:
+            estimate = max(0, int(getattr(state, "current_cache_len", 0))) + max(0, int(getattr(signal, "scheduled_tokens", 1)))
+        state_store.update_cache_len(req_id, estimate, step=signal.step)
+        if signal.should_compress:
+            state_store.mark_trigger(req_id, signal.reason, signal.step)
+            if log_decisions:
+                logger.debug("TriAttention trigger req=%s step=%d reason=%s len=%d mode=%s", req_id, signal.step,
+                             signal.reason, signal.estimated_cache_len, state.mode)
+    return step, signals
