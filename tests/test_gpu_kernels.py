@@ -265,6 +265,57 @@ def test_device_status_flags_bad_metadata():
     assert torch.equal(kc[1, 1], kb[1, 5])
 
 
+@pytest.mark.parametrize("preserve", [False, True])
+@pytest.mark.parametrize("batch", [1, 40])
+def test_compaction_grid_sizes(batch, preserve):
+    """Compaction picks its CTA size by the number of (layer, request, head, K/V) streams: a single request runs
+    the wide CTAs, 40 requests (640 streams) the narrow ones.  Either way slot r of every stream must hold token
+    keep[r], and with ``preserve_dropped`` the dropped tokens follow in ascending order."""
+    dev = "cuda"
+    g = torch.Generator().manual_seed(77 + batch)
+    T, bs, H, D, k = 1000, 16, 8, 128, 333
+    nblk = (T + bs - 1) // bs
+    total = batch * nblk + 3
+    perm = torch.randperm(total - 1, generator=g)[: batch * nblk] + 1
+    ids = [perm[b * nblk:(b + 1) * nblk].tolist() for b in range(batch)]
+    cache = torch.randn((2, total, bs, H, D), generator=g).to(torch.bfloat16).to(dev)
+    before = cache.clone()
+    view = ops.PagedCacheView.from_layers([cache], kv_axis=0)
+    bt = block_table_tensor(ids)
+    layout = view.layout(batch, 1, bt.shape[1])
+    keep = torch.stack([torch.stack([torch.randperm(T, generator=g)[:k].sort().values for _ in range(H)])
+                        for _ in range(batch)]).to(torch.int32).to(dev)                      # [B, H, k]
+    keep[0, 0, :50] = torch.arange(50, dtype=torch.int32)                                   # an unmoved prefix
+    keep[0, 0] = keep[0, 0].sort().values
+    if int((keep[0, 0, 1:] <= keep[0, 0, :-1]).sum()):                                      # duplicates after the edit
+        keep[0, 0] = torch.arange(k, dtype=torch.int32) * 3
+    seq = torch.full((batch,), T, dtype=torch.int32, device=dev)
+    kc = torch.full((batch,), k, dtype=torch.int32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    ops.compact_paged(view, layout, bt, seq, keep, (0, H * k, k), kc, status, preserve_dropped=preserve,
+                      max_dropped_rows=T - k if preserve else 0)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    hidx = torch.arange(H, device=dev).view(H, 1)
+    for b in range(batch):
+        btd = torch.as_tensor(ids[b], device=dev)
+        order = keep[b].long()
+        if preserve:
+            mask = torch.ones((H, T), dtype=torch.bool, device=dev)
+            mask[hidx, order] = False
+            dropped = torch.arange(T, device=dev).expand(H, T)[mask].view(H, T - k)
+            order = torch.cat([order, dropped], dim=1)
+        n = order.shape[1]
+        dst = torch.arange(n, device=dev)
+        for kv in (0, 1):
+            want = before[kv][btd[order // bs], order % bs, hidx]                              # [H, n, D]
+            got = cache[kv][btd[dst // bs], dst % bs].permute(1, 0, 2)
+            assert torch.equal(got, want), (b, kv)
+        if not preserve:                                                                       # the tail is untouched
+            tail = btd[(k + bs - 1) // bs:]
+            assert torch.equal(cache[:, tail], before[:, tail])
+
+
 def test_abi_rejects_bad_arguments():
     lib = _native.load()
     assert lib.triattn_select_topk(None, 1, 1, None, None, 1, 1, None, 1, None, None) == 1

@@ -391,8 +391,13 @@ static int compact_common(const triattn_paged_layout* layout, void* const* k_lay
   p.scratch_rows = scratch_rows;
   dim3 grid((unsigned)(Y.num_kv_heads * 2), (unsigned)Y.num_layers, (unsigned)Y.num_reqs);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (preserve) return launch_kernel(compact_paged_kernel<true>, grid, dim3(kCompactThreads), 0, st, pdl, p);
-  return launch_kernel(compact_paged_kernel<false>, grid, dim3(kCompactThreads), 0, st, pdl, p);
+  const bool small = (long long)grid.x * grid.y * grid.z < kCompactSmallGrid;
+  if (preserve) {
+    if (small) return launch_kernel(compact_paged_kernel<true, kCompactThreadsSmall>, grid, dim3(kCompactThreadsSmall), 0, st, pdl, p);
+    return launch_kernel(compact_paged_kernel<true, kCompactThreads>, grid, dim3(kCompactThreads), 0, st, pdl, p);
+  }
+  if (small) return launch_kernel(compact_paged_kernel<false, kCompactThreadsSmall>, grid, dim3(kCompactThreadsSmall), 0, st, pdl, p);
+  return launch_kernel(compact_paged_kernel<false, kCompactThreads>, grid, dim3(kCompactThreads), 0, st, pdl, p);
 }
 
 int triattn_compact_paged(const triattn_paged_layout* layout, void* const* k_layer_ptrs, void* const* v_layer_ptrs,

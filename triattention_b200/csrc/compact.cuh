@@ -10,15 +10,18 @@
 // block size) is computed once, by one lane per row, as a 32-bit offset in 16-byte units; the copy
 // then runs with all lanes on 16-byte pieces (32/lpr rows per instruction, lpr = pieces per row),
 // each row's offset broadcast by a shuffle.  A warp tile is up to 8 such instructions, so a CTA
-// keeps 8 warps x 8 x 512 bytes of reads in flight per barrier.
+// keeps 8 warps x 8 x 512 bytes of reads in flight per barrier.  A step with few streams (a single short request)
+// leaves most SMs empty and is bound by the serial chain of load-barrier-store round trips of one stream, so
+// such grids run 1024-thread CTAs: four times fewer round trips per stream.
 #pragma once
 
 #include "common.cuh"
 
 namespace triattn {
 
-constexpr int kCompactThreads = 256;
-constexpr int kCompactWarps = kCompactThreads / 32;
+constexpr int kCompactThreads = 256;        // grids that fill the device
+constexpr int kCompactThreadsSmall = 1024;  // grids of fewer CTAs than kCompactSmallGrid
+constexpr int kCompactSmallGrid = 512;
 constexpr int kCompactIters = 8;  // 16-byte pieces a lane holds per tile
 constexpr uint32_t kNoMove = 0xffffffffu;
 
@@ -54,8 +57,9 @@ __device__ __forceinline__ uint32_t slot_off16(const CompactParams& p, const int
                      (long long)head * p.head_stride) >> 3);
 }
 
-template <bool PRESERVE>
-__global__ void __launch_bounds__(kCompactThreads) compact_paged_kernel(const __grid_constant__ CompactParams p) {
+template <bool PRESERVE, int THREADS>
+__global__ void __launch_bounds__(THREADS) compact_paged_kernel(const __grid_constant__ CompactParams p) {
+  constexpr int kCompactWarps = THREADS / 32;
   grid_dependency_wait();  // no global access before the preceding kernel of the stream has completed
   trigger_dependents();
   const int which = blockIdx.x & 1;  // 0: K, 1: V
