@@ -124,3 +124,29 @@ def test_step_life_cycle_follows_the_reference():
     assert len(got) == len(want)
     for n, (g, w) in enumerate(zip(got, want)):
         assert g == w, n
+
+
+def test_legacy_estimate_switch_keeps_the_schedulers_length():
+    """After a compression the worker counts the cache length itself; the legacy switch takes the scheduler's
+    estimate instead (the reference's TRIATTN_RUNTIME_LEGACY_COMPRESSED_ESTIMATE)."""
+    import logging
+    import types
+    from triattention_b200.state import RequestStateStore
+
+    log = logging.getLogger("legacy_estimate")
+
+    def run(legacy):
+        store = RequestStateStore()
+        store.ensure(req_id="a", prefill_len=10, protect_prefill=False)
+        store.update_cache_len("a", 2177, step=1)
+        store.mark_compressed("a", step=1, cache_len=2048)
+        so = types.SimpleNamespace(triattention_step=2, triattention_signals={"a": CompressionSignal(
+            req_id="a", should_compress=False, reason="none", estimated_cache_len=2178, step=2, kv_usage=None,
+            protect_prefill=False, prefill_len=10, scheduled_tokens=1)})
+        runner_actions.consume_runner_signals(state_store=store, scheduler_output=so, last_step=1, logger=log,
+                                              log_decisions=False, legacy_compressed_estimate=legacy)
+        return store.get("a").current_cache_len
+
+    assert run(False) == 2049
+    assert run(True) == 2178
+    assert run(None) == (2178 if runner_actions.LEGACY_COMPRESSED_ESTIMATE else 2049)

@@ -11,6 +11,7 @@ bookkeeping and the event dictionaries (keys and values) are those of the refere
 from __future__ import annotations
 
 import logging
+import os
 from dataclasses import dataclass
 from typing import Any, Optional
 
@@ -192,6 +193,11 @@ def execute_runner_compression_actions(*, executor: Any, state_store: Any, sched
 # What the worker does with a scheduler output BEFORE the actions of the step: keep the request-state store in step
 # with arrivals, departures, preemptions and with the cache lengths the signals report (the reference's
 # runtime/runner_state_updates.py:20-128).  The hook reads the lengths kept here.
+# read once at import, like the reference's module constant (runner_state_updates.py:10-13)
+LEGACY_COMPRESSED_ESTIMATE = os.environ.get("TRIATTN_RUNTIME_LEGACY_COMPRESSED_ESTIMATE", "0").strip().lower() in {
+    "1", "true", "yes", "on"}
+
+
 def full_prefill_len(request_like: Any) -> int:
     """Prompt length of a new request from whichever field the engine version carries; the largest wins."""
     seen = [0]
@@ -239,13 +245,15 @@ def mark_resumed(*, state_store: Any, scheduler_output: Any) -> None:
 
 
 def consume_runner_signals(*, state_store: Any, scheduler_output: Any, last_step: int, logger: logging.Logger,
-                           log_decisions: bool, legacy_compressed_estimate: bool = False) -> tuple:
+                           log_decisions: bool, legacy_compressed_estimate: Optional[bool] = None) -> tuple:
     """``(step, signals)`` of the scheduler output, after recording every signal in the store.
 
     Before a request's first compression its cache length is the scheduler's estimate; afterwards the worker keeps its
     own count (previous length + tokens scheduled in this step), because the scheduler's snapshots may lag the
-    compaction in asynchronous scheduling (``legacy_compressed_estimate`` restores the scheduler's estimate, the
-    reference's TRIATTN_RUNTIME_LEGACY_COMPRESSED_ESTIMATE switch)."""
+    compaction in asynchronous scheduling.  ``legacy_compressed_estimate`` restores the scheduler's estimate; left at
+    None it follows the environment switch TRIATTN_RUNTIME_LEGACY_COMPRESSED_ESTIMATE, as the reference does."""
+    if legacy_compressed_estimate is None:
+        legacy_compressed_estimate = LEGACY_COMPRESSED_ESTIMATE
     step = getattr(scheduler_output, "triattention_step", last_step + 1)
     signals = getattr(scheduler_output, "triattention_signals", {})
     for req_id, signal in signals.items():
