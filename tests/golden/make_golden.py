@@ -14,6 +14,7 @@ Run where a checkout of the reference is available (default: a directory
     python tests/golden/make_golden.py --only state_store    # only state_store_cases.json
     python tests/golden/make_golden.py --only effective_overrides  # only effective_override_cases.json
     python tests/golden/make_golden.py --only step_lifecycle # only step_lifecycle_cases.json
+    python tests/golden/make_golden.py --only scheduler_side # only scheduler_side_cases.json
 
 The reference is imported unmodified, on CPU, with three test-side shims:
 
@@ -726,6 +727,28 @@ def gen_step_lifecycle_cases(out: dict):
     out["step_lifecycle_cases"] = {"file": "step_lifecycle_cases.json", "steps": len(sls.STEPS)}
 
 
+def gen_scheduler_side_cases(out: dict):
+    """The reference's trigger planner (runtime/planner.py), effective-length tracker (effective_len_tracker.py),
+    allocation-sync attributes (kv_allocation_sync.py) and block-pool reclaim (scheduler.py:29-52,338-564, called
+    unbound on a stand-in scheduler) along tests/scheduler_side_scenarios.py.  Importing the scheduler module needs
+    the serving engine the reference subclasses (installed in the build container)."""
+    from triattention.vllm.runtime import kv_allocation_sync
+    from triattention.vllm.runtime.effective_len_tracker import EffectiveCacheLenTracker
+    from triattention.vllm.runtime.planner import CompressionPlanner
+    from triattention.vllm.runtime.scheduler import TriAttentionScheduler
+    import scheduler_side_scenarios as sss
+
+    res = {
+        "planner": sss.replay_planner(CompressionPlanner),
+        "tracker": sss.replay_tracker(EffectiveCacheLenTracker()),
+        "allocation_sync": sss.replay_allocation_sync(kv_allocation_sync),
+        "reclaim": {c["name"]: sss.run_reclaim_case(TriAttentionScheduler._apply_compression_events,
+                                                    EffectiveCacheLenTracker, c) for c in sss.RECLAIM_CASES},
+    }
+    (HERE / "scheduler_side_cases.json").write_text(json.dumps(res, indent=1, sort_keys=True))
+    out["scheduler_side_cases"] = {"file": "scheduler_side_cases.json", "reclaim_cases": sorted(res["reclaim"])}
+
+
 PARTIAL = {
     # --only <name>: regenerate one group of fixtures and merge it into manifest.json
     "calibration": lambda out: gen_calibration_cases(out),
@@ -737,6 +760,7 @@ PARTIAL = {
     "state_store": lambda out: gen_state_store_cases(out),
     "effective_overrides": lambda out: gen_effective_override_cases(out),
     "step_lifecycle": lambda out: gen_step_lifecycle_cases(out),
+    "scheduler_side": lambda out: gen_scheduler_side_cases(out),
 }
 
 
@@ -763,6 +787,7 @@ def main():
     gen_state_store_cases(out)
     gen_effective_override_cases(out)
     gen_step_lifecycle_cases(out)
+    gen_scheduler_side_cases(out)
     (HERE / "manifest.json").write_text(json.dumps(out, indent=1, sort_keys=True))
     print("wrote", [p.name for p in HERE.iterdir()])
 

@@ -1,0 +1,72 @@
+"""Scheduler-side pieces (trigger planner, effective-length tracker, allocation-sync attributes, block-pool reclaim)
+against results of the reference's own code on the same scripted inputs (tests/golden/scheduler_side_cases.json,
+written by tests/golden/make_golden.py --only scheduler_side)."""
+from __future__ import annotations
+
+import json
+import sys
+from pathlib import Path
+
+import pytest
+
+HERE = Path(__file__).resolve().parent
+sys.path.insert(0, str(HERE))
+
+import scheduler_side_scenarios as sss  # noqa: E402
+from triattention_b200 import scheduler_side  # noqa: E402
+
+WANT = json.loads((HERE / "golden" / "scheduler_side_cases.json").read_text())
+
+
+def _plain(x):
+    return json.loads(json.dumps(x))
+
+
+def test_trigger_planner_follows_the_reference():
+    got = _plain(sss.replay_planner(scheduler_side.CompressionPlanner))
+    assert sorted(got) == sorted(WANT["planner"])
+    for name in got:
+        for n, (g, w) in enumerate(zip(got[name], WANT["planner"][name])):
+            assert g == w, (name, n)
+    # the cases cover both triggers, the latch (armed at 0.95, still armed at 0.7, released at 0.5) and its priority
+    reasons = {s["reason"] for sigs in got.values() for s in sigs}
+    assert reasons == {"none", "length_threshold", "kv_usage_threshold"}
+    pool = got["pool_pressure"]
+    assert [s["should_compress"] for s in pool[2:7]] == [True, True, False, False, False]
+
+
+def test_effective_length_tracker_follows_the_reference():
+    got = _plain(sss.replay_tracker(scheduler_side.EffectiveCacheLenTracker()))
+    assert len(got) == len(WANT["tracker"])
+    for n, (g, w) in enumerate(zip(got, WANT["tracker"])):
+        assert g == w, n
+
+
+def test_allocation_sync_attributes_follow_the_reference():
+    got = _plain(sss.replay_allocation_sync(scheduler_side))
+    assert len(got) == len(WANT["allocation_sync"])
+    for n, (g, w) in enumerate(zip(got, WANT["allocation_sync"])):
+        assert g == w, n
+
+
+@pytest.mark.parametrize("case", sss.RECLAIM_CASES, ids=[c["name"] for c in sss.RECLAIM_CASES])
+def test_block_pool_reclaim_follows_the_reference(case):
+    got = _plain(sss.run_reclaim_case(scheduler_side.apply_compression_events, scheduler_side.EffectiveCacheLenTracker,
+                                      case))
+    want = WANT["reclaim"][case["name"]]
+    assert got == want
+    if case["name"].startswith("error_"):
+        assert got["error"] and got["error"].startswith("TriAttention block reclaim")
+
+
+def test_reclaim_cases_exercise_the_pool():
+    """The fixtures are not vacuous: blocks are freed last-first, hashed ones are evicted first, appended blocks stay."""
+    two = WANT["reclaim"]["explicit_payload_two_groups"]
+    assert two["pool_calls"] == [["evict", 0, 230], ["evict", 0, 236], ["free", 0, list(range(236, 227, -1))],
+                                 ["free", 1, list(range(636, 627, -1))]]
+    assert two["offsets"] == {"a": 2177 - 2048}
+    late = WANT["reclaim"]["blocks_appended_after_the_hook"]
+    assert late["blocks"][0]["a"] == list(range(128)) + [137, 138, 139]
+    assert late["pool_calls"] == [["free", 0, list(range(136, 127, -1))]]
+    assert WANT["reclaim"]["no_payload_during_prefill"]["pool_calls"] == []
+    assert WANT["reclaim"]["payload_misses_a_group"]["blocks"][1]["a"] == list(range(300, 428))
