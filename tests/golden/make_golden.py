@@ -15,6 +15,7 @@ Run where a checkout of the reference is available (default: a directory
     python tests/golden/make_golden.py --only effective_overrides  # only effective_override_cases.json
     python tests/golden/make_golden.py --only step_lifecycle # only step_lifecycle_cases.json
     python tests/golden/make_golden.py --only scheduler_side # only scheduler_side_cases.json
+    python tests/golden/make_golden.py --only worker_runner  # only worker_runner_cases.json
 
 The reference is imported unmodified, on CPU, with three test-side shims:
 
@@ -749,6 +750,51 @@ def gen_scheduler_side_cases(out: dict):
     out["scheduler_side_cases"] = {"file": "scheduler_side_cases.json", "reclaim_cases": sorted(res["reclaim"])}
 
 
+def gen_worker_runner_cases(out: dict):
+    """The reference's model-runner proxy (runtime/runner.py, runner_output_bridge.py, input_adapter.py) along
+    tests/worker_runner_scenarios.py; methods that need no engine are called unbound on a stand-in."""
+    import logging
+    import types
+    from triattention.vllm.runtime import input_adapter, runner_output_bridge
+    from triattention.vllm.runtime.config import TriAttentionRuntimeConfig
+    from triattention.vllm.runtime.runner import TriAttentionModelRunner as Ref
+    from triattention.vllm.runtime.signals import CompressionSignal
+    from triattention.vllm.runtime.state import RequestStateStore
+    import worker_runner_scenarios as wrs
+
+    log = logging.getLogger("ref_runner_scenarios")
+    log.disabled = True
+
+    def stand_in(base_runner, config, store, last_step=0):
+        me = types.SimpleNamespace(config=config, state_store=store, _base_runner=base_runner, _logger=log,
+                                   _last_step=last_step)
+        me._get_actual_kv_from_block_table = types.MethodType(Ref._get_actual_kv_from_block_table, me)
+        return me
+
+    def self_trigger(base_runner, config, store, so, signals, last_step):
+        return Ref._supplement_worker_self_triggers(stand_in(base_runner, config, store, last_step), so, signals)
+
+    def trim(base_runner, store, so):
+        Ref._patch_scheduler_output_for_compressed_reqs(stand_in(base_runner, None, store), so)
+
+    def needs(store, so):
+        return Ref._needs_effective_input_overrides(stand_in(None, None, store), so)
+
+    cfg = TriAttentionRuntimeConfig(kv_budget=64, divide_length=16, protect_prefill=False, log_decisions=False,
+                                    enable_experimental_kv_compaction=True)
+    res = {
+        "self_trigger": {c["name"]: wrs.run_self_trigger(self_trigger, RequestStateStore, c)
+                         for c in wrs.self_trigger_cases(CompressionSignal)},
+        "trim": {c["name"]: wrs.run_trim(trim, RequestStateStore, c) for c in wrs.TRIM_CASES},
+        "overrides": {c["name"]: wrs.run_overrides(input_adapter.prepare_effective_input_overrides, needs,
+                                                   RequestStateStore, c) for c in wrs.OVERRIDE_CASES},
+        "attach": wrs.run_attach(runner_output_bridge),
+        "steps": wrs.run_steps(Ref, cfg, CompressionSignal),
+    }
+    (HERE / "worker_runner_cases.json").write_text(json.dumps(res, indent=1, sort_keys=True))
+    out["worker_runner_cases"] = {"file": "worker_runner_cases.json", "sections": sorted(res)}
+
+
 PARTIAL = {
     # --only <name>: regenerate one group of fixtures and merge it into manifest.json
     "calibration": lambda out: gen_calibration_cases(out),
@@ -761,6 +807,7 @@ PARTIAL = {
     "effective_overrides": lambda out: gen_effective_override_cases(out),
     "step_lifecycle": lambda out: gen_step_lifecycle_cases(out),
     "scheduler_side": lambda out: gen_scheduler_side_cases(out),
+    "worker_runner": lambda out: gen_worker_runner_cases(out),
 }
 
 
@@ -788,6 +835,7 @@ def main():
     gen_effective_override_cases(out)
     gen_step_lifecycle_cases(out)
     gen_scheduler_side_cases(out)
+    gen_worker_runner_cases(out)
     (HERE / "manifest.json").write_text(json.dumps(out, indent=1, sort_keys=True))
     print("wrote", [p.name for p in HERE.iterdir()])
 
