@@ -439,3 +439,80 @@ def test_batched_hook_equals_the_per_request_hook(tmp_path):
     # a second round on the same runners: the compressed requests are now under budget + slack on both paths
     assert many.triattention_apply_compression_batch(reqs, so) == {
         r: one.triattention_apply_compression(req_id=r, signal=s, scheduler_output=so) for r, s in reqs}
+
+
+def test_runner_proxy_step_with_the_real_hook(tmp_path):
+    """A whole worker step through ``worker_runner.TriAttentionModelRunner`` with the installed hook: the triggered
+    requests of the step are compacted in one native call, the events reach the engine's output, the request-state
+    store and the block lists are updated, and the caches equal those of the per-request hook."""
+    from triattention_b200 import worker_runner
+
+    gen = torch.Generator().manual_seed(synth.seed_for(5, 2))
+    L, Hq, Hkv, D, bs, budget, window = 2, 8, 2, 128, 16, 256, 32
+    inv = synth.rope_inv_freq(D, 1e6)
+    stats = synth.make_stats(L, Hq, D, inv, gen)
+    sp = tmp_path / "s.pt"
+    synth.save_stats_pt(stats, sp)
+    lens = {"a": 900, "b": 100, "c": 640}                   # b stays under the budget
+    nblk = {r: (t + bs - 1) // bs for r, t in lens.items()}
+    perm = synth.random_block_ids(sum(nblk.values()), sum(nblk.values()) + 6, gen)
+    ids, o = {}, 0
+    for r, n in nblk.items():
+        ids[r] = perm[o:o + n]
+        o += n
+    caches = []
+    for _ in range(L):
+        c = synth.make_paged_layer(sum(nblk.values()) + 6, bs, Hkv, D, kv_axis=0)
+        for r, t in lens.items():
+            synth.write_tokens_to_paged(c, 0, ids[r], bs, synth.make_rotated_keys(Hkv, t, D, inv, gen),
+                                        synth.make_values(Hkv, t, D, gen))
+        caches.append(c)
+    cfg = TriAttentionRuntimeConfig(kv_budget=budget, divide_length=64, window_size=window, sparse_stats_path=sp,
+                                    log_decisions=False)
+
+    def make():
+        dc = [c.to(DEV) for c in caches]
+        runner = types.SimpleNamespace(
+            requests={r: types.SimpleNamespace(block_ids=(list(ids[r]),), num_computed_tokens=t) for r, t in lens.items()},
+            kv_caches=dc, cache_config=types.SimpleNamespace(block_size=bs))
+        runner.execute_model = lambda scheduler_output, intermediate_tensors=None: types.SimpleNamespace(tag="out")
+        hook_mod.install_runner_compression_hook(runner, cfg)
+        return runner, dc
+
+    def sig(req, should=True):
+        return CompressionSignal(req_id=req, should_compress=should, reason="length_threshold" if should else "none",
+                                 estimated_cache_len=lens[req] + 1, step=2, kv_usage=None, protect_prefill=False,
+                                 prefill_len=lens[req], scheduled_tokens=1)
+
+    def step_output(step, signals):
+        return types.SimpleNamespace(triattention_step=step, triattention_signals=signals,
+                                     num_scheduled_tokens={r: 1 for r in lens}, scheduled_new_reqs=[],
+                                     finished_req_ids=[])
+
+    # reference run: the per-request hook, request after request, on its own copy of the caches
+    one, one_caches = make()
+    so = step_output(2, {})
+    want = {r: one.triattention_apply_compression(req_id=r, signal=sig(r), scheduler_output=so) for r in lens}
+
+    runner, dc = make()
+    proxy = worker_runner.TriAttentionModelRunner(runner, cfg)
+    out = proxy.execute_model(step_output(2, {r: sig(r) for r in lens}))
+    events = out.triattention_compression_events
+    assert [(e["req_id"], e["status"]) for e in events] == [("a", "applied"), ("b", "skipped"), ("c", "applied")]
+    for e in events:
+        assert e["reason"] == want[e["req_id"]]["reason"]
+        if e["status"] == "applied":
+            assert e["cache_len_after"] == budget and e["block_reclaim"]["groups"][0]["block_ids_after"] == \
+                list(ids[e["req_id"]][: budget // bs])
+    for r in lens:
+        assert runner.requests[r].block_ids == one.requests[r].block_ids
+    for x, y in zip(dc, one_caches):
+        assert torch.equal(x.view(torch.int16), y.view(torch.int16))
+    states = proxy.snapshot_states()
+    assert states["a"].compression_count == 1 and states["c"].compression_count == 1 and states["b"].compression_count == 0
+    assert states["a"].current_cache_len == budget + 1
+    # next step: nothing from the scheduler, and the worker's own count (257 + 1) is below budget + slack: no trigger
+    snap = [c.clone() for c in dc]
+    out = proxy.execute_model(step_output(3, {}))
+    assert out.triattention_compression_events == []
+    assert all(torch.equal(x, y) for x, y in zip(dc, snap))
