@@ -733,13 +733,38 @@ def gen_scheduler_side_cases(out: dict):
     allocation-sync attributes (kv_allocation_sync.py) and block-pool reclaim (scheduler.py:29-52,338-564, called
     unbound on a stand-in scheduler) along tests/scheduler_side_scenarios.py.  Importing the scheduler module needs
     the serving engine the reference subclasses (installed in the build container)."""
+    import types
     from triattention.vllm.runtime import kv_allocation_sync
     from triattention.vllm.runtime.effective_len_tracker import EffectiveCacheLenTracker
     from triattention.vllm.runtime.planner import CompressionPlanner
     from triattention.vllm.runtime.scheduler import TriAttentionScheduler
     import scheduler_side_scenarios as sss
 
+    # the scheduler's step: the reference's patched schedule / update_from_output around stand-ins for the engine's own
+    from triattention.vllm.runtime import integration_monkeypatch as im
+
+    class _RefStepApi:
+        @staticmethod
+        def attach(sched, cfg):
+            sched.triattention_config = cfg
+            sched._planner = CompressionPlanner(cfg)
+            sched._effective_len_tracker = EffectiveCacheLenTracker()
+            sched._prefill_lens, sched._length_threshold_cache, sched._triattention_step = {}, {}, 0
+            for name in ("_compute_length_threshold", "_resolve_prefill_len", "_has_active_effective_len_overrides"):
+                setattr(sched, name, types.MethodType(getattr(TriAttentionScheduler, name), sched))
+
+        @staticmethod
+        def schedule(sched, base_schedule):
+            im._ORIG_SCHED_SCHEDULE = base_schedule
+            return im._patched_scheduler_schedule(sched)
+
+        @staticmethod
+        def update(sched, so, mro, base_update):
+            im._ORIG_SCHED_UPDATE_FROM_OUTPUT = base_update
+            return im._patched_scheduler_update_from_output(sched, so, mro)
+
     res = {
+        "steps": {name: sss.run_scheduler_steps(_RefStepApi, over) for name, over in sss.STEP_CONFIGS.items()},
         "planner": sss.replay_planner(CompressionPlanner),
         "tracker": sss.replay_tracker(EffectiveCacheLenTracker()),
         "allocation_sync": sss.replay_allocation_sync(kv_allocation_sync),

@@ -200,3 +200,99 @@ def run_reclaim_case(apply_fn, tracker_cls, case: dict) -> dict:
         "tracker": {k: list(v) for k, v in sorted(sched._effective_len_tracker.snapshot().items())},
         "offsets": {r: getattr(q, "_triattention_effective_kv_offset", "absent") for r, q in requests.items()},
     }
+
+
+# ---------------------------------------------------------------------------------------------- the scheduler's step
+STEP_CONFIGS = {
+    "length_trigger": dict(pool_blocks=100),
+    "small_pool_caps_the_step": dict(pool_blocks=6),
+    "pool_pressure_trigger": dict(pool_blocks=100, enable_kv_usage_trigger=True, kv_usage_trigger=0.9, kv_usage_release=0.5),
+    "compression_disabled": dict(pool_blocks=100, disable_compression=True),
+    "protected_prompt": dict(pool_blocks=100, protect_prefill=True),
+}
+_STEP_CFG_BASE = dict(kv_budget=64, divide_length=16, protect_prefill=False, include_prefill_in_budget=False,
+                      enable_kv_usage_trigger=False, kv_usage_trigger=0.98, kv_usage_release=0.9, disable_compression=False,
+                      enable_experimental_block_reclaim=True, require_physical_reclaim=True, log_decisions=False)
+
+# per step: new requests (id, prompt tokens, computed so far), tokens scheduled, computed counters before the step,
+# pool usage, what comes back from the worker (events on the runner's output, or on the scheduler output)
+STEP_SCRIPT = [
+    dict(new=[("a", 70, 0), ("b", 20, 0)], sched={"a": 40, "b": 20}, computed={"a": 0, "b": 0}, usage=0.2),
+    dict(new=[("a", 70, 40)], sched={"a": 30, "b": 1, "ghost": 1}, computed={"a": 40, "b": 20}, usage=0.95),
+    dict(sched={"a": 1, "b": 1}, computed={"a": 70, "b": 21}, usage=0.7),
+    dict(sched={"a": 1, "b": 1}, computed={"a": 79, "b": 22}, usage=0.7,
+         events_on="runner", events=[dict(status="applied", req_id="a", cache_len_after=64, step=4, scheduled_tokens=1,
+                                          block_reclaim={"groups": [dict(gid=0, block_ids_after=[0, 1, 2, 3])]})]),
+    dict(sched={"a": 1, "b": 1}, computed={"a": 80, "b": 23}, usage=0.4),
+    dict(sched={"a": 1, "b": 1}, computed={"a": 95, "b": 24}, usage=0.4, finished=["b"],
+         events_on="scheduler", events=[dict(status="applied", req_id="a", cache_len_after=64, step=6, scheduled_tokens=1),
+                                        dict(status="skipped", req_id="b", cache_len_after=None, step=6)]),
+    dict(sched={"a": 1, "c": 1}, computed={"a": 96, "c": 300}, usage=0.4, resumed=["c"], prompt={"c": 250}),
+    dict(sched={"a": 1}, computed={"a": 97}, usage=0.4, finished=["a", "c"]),
+]
+
+
+def run_scheduler_steps(api, cfg_over: dict) -> list:
+    """``api.attach(scheduler, cfg)``, ``api.schedule(scheduler, base_schedule)``,
+    ``api.update(scheduler, scheduler_output, model_runner_output, base_update)``."""
+    over = dict(cfg_over)
+    pool_blocks = over.pop("pool_blocks")
+    cfg = types.SimpleNamespace(**{**_STEP_CFG_BASE, **over})
+    log = []
+    pool = _Pool(log, 0)
+    pool.num_gpu_blocks = pool_blocks
+    manager = types.SimpleNamespace(req_to_blocks={"a": [_Block(i, False) for i in range(6)]}, num_cached_block={},
+                                    block_pool=pool)
+    kvm = types.SimpleNamespace(usage=0.0, block_pool=pool,
+                                coordinator=types.SimpleNamespace(single_type_managers=[manager]))
+    sched = types.SimpleNamespace(requests={}, kv_cache_manager=kvm, running=[], block_size=16,
+                                  max_num_scheduled_tokens=8192)
+    api.attach(sched, cfg)
+    caps = []
+    out = []
+    for st in STEP_SCRIPT:
+        for r, n in st["computed"].items():
+            if r in sched.requests:
+                sched.requests[r].num_computed_tokens = n
+            else:
+                sched.requests[r] = types.SimpleNamespace(num_computed_tokens=n, num_prompt_tokens=st.get("prompt", {}).get(r, 0))
+        for r, prompt, _done in st.get("new", []):
+            sched.requests[r].num_prompt_tokens = prompt
+        sched.running = list(sched.requests.values())
+        kvm.usage = st["usage"]
+        so = types.SimpleNamespace(
+            num_scheduled_tokens=dict(st["sched"]), finished_req_ids=list(st.get("finished", [])),
+            scheduled_new_reqs=[types.SimpleNamespace(req_id=r, num_computed_tokens=done, prompt_token_ids=[0] * prompt)
+                                for r, prompt, done in st.get("new", [])],
+            scheduled_cached_reqs=types.SimpleNamespace(req_ids=[r for r in st["sched"] if r in sched.requests],
+                                                        resumed_req_ids=list(st.get("resumed", []))))
+
+        def base_schedule(s, _so=so):
+            caps.append(s.max_num_scheduled_tokens)
+            return _so
+
+        got = api.schedule(sched, base_schedule)
+        rec = {"step": got.triattention_step, "cap_seen": caps[-1], "cap_after": sched.max_num_scheduled_tokens,
+               "signals": {k: dataclasses.asdict(v) for k, v in got.triattention_signals.items()},
+               "effective_markers": {r: getattr(q, "_triattention_effective_num_computed_tokens", "absent")
+                                     for r, q in sched.requests.items()}}
+        mro = types.SimpleNamespace()
+        if st.get("events_on") == "runner":
+            mro.triattention_compression_events = st["events"]
+        elif st.get("events_on") == "scheduler":
+            so.triattention_compression_events = st["events"]
+        stats = types.SimpleNamespace(kv_cache_usage=-1.0)
+        outputs = api.update(sched, so, mro, lambda s, a, b, _stats=stats: {0: types.SimpleNamespace(scheduler_stats=_stats),
+                                                                             1: types.SimpleNamespace()})
+        rec.update({
+            "usage_in_stats": outputs[0].scheduler_stats.kv_cache_usage,
+            "blocks": {r: [b.block_id for b in bl] for r, bl in manager.req_to_blocks.items()},
+            "pool_calls": list(log),
+            "tracker": {k: list(v) for k, v in sorted(sched._effective_len_tracker.snapshot().items())},
+            "prefill_lens": dict(sched._prefill_lens), "thresholds": dict(sched._length_threshold_cache),
+            "offsets": {r: getattr(q, "_triattention_effective_kv_offset", "absent") for r, q in sched.requests.items()},
+        })
+        for r in st.get("finished", []):
+            sched.requests.pop(r, None)
+        out.append(rec)
+    return out

@@ -70,3 +70,32 @@ def test_reclaim_cases_exercise_the_pool():
     assert late["pool_calls"] == [["free", 0, list(range(136, 127, -1))]]
     assert WANT["reclaim"]["no_payload_during_prefill"]["pool_calls"] == []
     assert WANT["reclaim"]["payload_misses_a_group"]["blocks"][1]["a"] == list(range(300, 428))
+
+
+class _StepApi:
+    attach = staticmethod(scheduler_side.attach_scheduler_state)
+    schedule = staticmethod(scheduler_side.schedule_with_signals)
+    update = staticmethod(scheduler_side.update_from_output_with_events)
+
+
+@pytest.mark.parametrize("name", sorted(sss.STEP_CONFIGS))
+def test_scheduler_steps_follow_the_reference(name):
+    """Eight scheduling steps (chunked prefill, decode, a trigger, events returning on the runner's output and on the
+    scheduler output, a resumed and two finished requests) through schedule / update_from_output."""
+    got = _plain(sss.run_scheduler_steps(_StepApi, sss.STEP_CONFIGS[name]))
+    want = WANT["steps"][name]
+    assert len(got) == len(want)
+    for n, (g, w) in enumerate(zip(got, want)):
+        assert g == w, (name, n)
+
+
+def test_scheduler_step_fixtures_are_not_vacuous():
+    steps = WANT["steps"]["length_trigger"]
+    assert steps[3]["signals"]["a"]["should_compress"] and steps[3]["signals"]["a"]["estimated_cache_len"] == 80
+    assert steps[3]["pool_calls"] == [["free", 0, [5, 4]]] and steps[3]["usage_in_stats"] == 0.7
+    assert steps[4]["signals"]["a"]["estimated_cache_len"] == 66 and not steps[4]["signals"]["a"]["should_compress"]
+    assert steps[4]["effective_markers"]["a"] == 65
+    assert WANT["steps"]["small_pool_caps_the_step"][0]["cap_seen"] == 16
+    assert all(s["cap_after"] == 8192 for s in WANT["steps"]["small_pool_caps_the_step"])
+    assert WANT["steps"]["pool_pressure_trigger"][1]["signals"]["b"]["reason"] == "kv_usage_threshold"
+    assert WANT["steps"]["compression_disabled"][3]["signals"] == {}

@@ -1,7 +1,7 @@
 """Scheduler-side neighbours of the compression step: who asks for it and who frees what it left over.
 
-Four small pieces of the reference's engine-core process, kept free of any engine import (they work on the
-attributes the reference reads, so the reference's scheduler subclass can bind them as they are):
+The reference's additions to the engine-core process, kept free of any engine import (they work on the
+attributes the reference reads, so the reference's scheduler subclass or its patches can bind them as they are):
 
 * :class:`CompressionPlanner` - the trigger: cache length >= budget + divide_length (+ the prompt when it is
   protected outside the budget), or KV-pool pressure with hysteresis (``runtime/planner.py:9-62``).  Its
@@ -15,6 +15,10 @@ attributes the reference reads, so the reference's scheduler subclass can bind t
   shrink the request's block list of each KV-cache group to the prefix the worker kept and return the old tail
   blocks to the pool, with the consistency checks and the batch-queue fall-backs of
   ``runtime/scheduler.py:29-52,338-564``.
+* the scheduler's step around the engine's own ``schedule`` / ``update_from_output``: :func:`schedule_with_signals`
+  (allocation markers, the token cap of a small pool, prompt lengths, the sparse signal dictionary) and
+  :func:`update_from_output_with_events` (``runtime/scheduler.py:123-336,566-595``,
+  ``runtime/integration_monkeypatch.py:89-216``).
 """
 from __future__ import annotations
 
@@ -313,3 +317,168 @@ def apply_compression_events(scheduler: Any, compression_events: Iterable[dict])
                     freed = True
         if freed:
             update_request_effective_kv_offset(request=request, cache_len_after=after)
+
+
+# ------------------------------------------------------------------------------------------------ the scheduler's step
+# What the reference adds around the engine scheduler's ``schedule`` and ``update_from_output``
+# (runtime/scheduler.py:84-336,566-595 and the patched forms in runtime/integration_monkeypatch.py:89-216), as
+# functions over a scheduler object that carries the six attributes set by :func:`attach_scheduler_state`.
+def attach_scheduler_state(scheduler: Any, config: Optional[TriAttentionRuntimeConfig] = None) -> None:
+    cfg = config or TriAttentionRuntimeConfig.from_env()
+    scheduler.triattention_config = cfg
+    scheduler._planner = CompressionPlanner(cfg)
+    scheduler._effective_len_tracker = EffectiveCacheLenTracker()
+    scheduler._prefill_lens = {}
+    scheduler._length_threshold_cache = {}
+    scheduler._triattention_step = 0
+
+
+def _prompt_len(request_like: Any) -> int:
+    from .runner_actions import full_prefill_len  # the same "largest of the fields that exist" rule on both sides
+    return full_prefill_len(request_like)
+
+
+def _threshold_for(cfg: Any, prefill_len: int) -> int:
+    extra = max(0, int(prefill_len)) if (cfg.protect_prefill and not cfg.include_prefill_in_budget) else 0
+    return cfg.kv_budget + cfg.divide_length + extra
+
+
+def _known_prefill_len(scheduler: Any, req_id: Any) -> int:
+    if req_id in scheduler._prefill_lens:
+        return scheduler._prefill_lens[req_id]
+    request = scheduler.requests.get(req_id)
+    return 0 if request is None else request.num_prompt_tokens
+
+
+def _remember_prefill_len(scheduler: Any, req_id: Any, prefill_len: int) -> None:
+    scheduler._prefill_lens[req_id] = prefill_len
+    scheduler._length_threshold_cache[req_id] = _threshold_for(scheduler.triattention_config, prefill_len)
+
+
+def sync_prefill_lens(scheduler: Any, scheduler_output: Any) -> None:
+    """Prompt lengths and thresholds of arriving requests (the tracker is reset only at a request's FIRST
+    appearance: a chunked prefill lists it again), forgotten for finished ones, recovered for resumed ones."""
+    for new_req in scheduler_output.scheduled_new_reqs:
+        if new_req.req_id not in scheduler._prefill_lens:
+            scheduler._effective_len_tracker.reset_request(new_req.req_id, new_req.num_computed_tokens)
+        _remember_prefill_len(scheduler, new_req.req_id, _prompt_len(new_req))
+    for req_id in scheduler_output.finished_req_ids:
+        request = scheduler.requests.get(req_id)
+        if request is not None:
+            clear_request_allocation_sync_state(request)
+        scheduler._prefill_lens.pop(req_id, None)
+        scheduler._length_threshold_cache.pop(req_id, None)
+        scheduler._effective_len_tracker.remove_request(req_id)
+    cached = getattr(scheduler_output, "scheduled_cached_reqs", None)
+    resumed = [] if cached is None else getattr(cached, "resumed_req_ids", None)
+    if resumed is None:
+        resumed = getattr(cached, "req_ids", []) or []
+    for req_id in resumed:
+        if req_id not in scheduler._prefill_lens:
+            _remember_prefill_len(scheduler, req_id, _known_prefill_len(scheduler, req_id))
+
+
+def build_signals(scheduler: Any, scheduler_output: Any) -> dict:
+    """Signals of the step, sparse: only requests that trigger now or have been compressed before (those still need
+    their effective length on the worker).  An uncompressed request below its threshold costs one dictionary lookup
+    and one comparison."""
+    from .effective_overrides import scheduled_token_items
+
+    cfg = scheduler.triattention_config
+    by_pool = bool(cfg.enable_kv_usage_trigger)
+    kv_usage = scheduler.kv_cache_manager.usage if by_pool else None
+    off = bool(cfg.disable_compression)
+    tracker = scheduler._effective_len_tracker
+    signals: dict = {}
+    for _key, req_id, scheduled in scheduled_token_items(scheduler_output):
+        request = scheduler.requests.get(req_id)
+        if request is None:
+            continue
+        compressed = tracker.has_effective_len_override(req_id)
+        base = (tracker.observe_num_computed(req_id=req_id, num_computed_tokens=request.num_computed_tokens)
+                if compressed else request.num_computed_tokens)
+        estimate = base + scheduled
+        if not compressed and not by_pool:
+            if off:
+                continue
+            threshold = scheduler._length_threshold_cache.get(req_id)
+            if threshold is None:
+                _remember_prefill_len(scheduler, req_id, _known_prefill_len(scheduler, req_id))
+                threshold = scheduler._length_threshold_cache[req_id]
+            if estimate < threshold:
+                continue
+        prefill_len = scheduler._prefill_lens.get(req_id)
+        if prefill_len is None:
+            prefill_len = _known_prefill_len(scheduler, req_id)
+            _remember_prefill_len(scheduler, req_id, prefill_len)
+        signal = scheduler._planner.build_signal(req_id=req_id, estimated_cache_len=estimate, prefill_len=prefill_len,
+                                                 step=scheduler._triattention_step, kv_usage=kv_usage,
+                                                 scheduled_tokens=scheduled)
+        if signal.should_compress or compressed:
+            signals[req_id] = signal
+    return signals
+
+
+def max_chunk_for_compression(scheduler: Any, cfg: Any) -> Optional[int]:
+    """Largest number of tokens a step may schedule so that budget + chunk still fits the physical pool (minus one
+    block of slack); None when no cap applies."""
+    pool = getattr(getattr(scheduler, "kv_cache_manager", None), "block_pool", None)
+    total = getattr(pool, "num_gpu_blocks", 0) if pool is not None else 0
+    if pool is None or total <= 0:
+        return None
+    block_size = int(getattr(scheduler, "block_size", 16) or 16)
+    headroom = total * block_size - cfg.kv_budget
+    return max(1, headroom - block_size) if headroom > 0 else None
+
+
+def schedule_with_signals(scheduler: Any, base_schedule: Any) -> Any:
+    """``base_schedule(scheduler)`` with the allocation markers refreshed before it, the step's token cap lowered
+    around it when the pool is small, and ``triattention_step`` / ``triattention_signals`` attached to its result."""
+    running = getattr(scheduler, "running", None)
+    if isinstance(running, list):
+        for request in running:
+            prepare_request_effective_num_computed(request)
+    cfg = getattr(scheduler, "triattention_config", None)
+    saved_cap = None
+    if cfg and not cfg.disable_compression:
+        cap = max_chunk_for_compression(scheduler, cfg)
+        current = getattr(scheduler, "max_num_scheduled_tokens", None)
+        if cap is not None and current is not None and cap < current:
+            saved_cap, scheduler.max_num_scheduled_tokens = current, cap
+    scheduler_output = base_schedule(scheduler)
+    if saved_cap is not None:
+        scheduler.max_num_scheduled_tokens = saved_cap
+    if cfg is None:
+        return scheduler_output
+    scheduler._triattention_step += 1
+    sync_prefill_lens(scheduler, scheduler_output)
+    idle = (cfg.disable_compression and not cfg.enable_kv_usage_trigger
+            and not scheduler._effective_len_tracker.has_any_effective_len_overrides())
+    scheduler_output.triattention_step = scheduler._triattention_step
+    scheduler_output.triattention_signals = {} if idle else build_signals(scheduler, scheduler_output)
+    return scheduler_output
+
+
+def update_from_output_with_events(scheduler: Any, scheduler_output: Any, model_runner_output: Any,
+                                   base_update: Any) -> Any:
+    """``base_update(scheduler, scheduler_output, model_runner_output)``, then the compression events of the step -
+    from the runner's output, else (asynchronous scheduling) from the scheduler output - are applied and the pool
+    usage in the returned statistics is brought up to date."""
+    outputs = base_update(scheduler, scheduler_output, model_runner_output)
+    if getattr(scheduler, "triattention_config", None) is None:
+        return outputs
+    events = getattr(model_runner_output, "triattention_compression_events", None) or \
+        getattr(scheduler_output, "triattention_compression_events", None)
+    if events:
+        apply_compression_events(scheduler, events)
+        if isinstance(outputs, dict):
+            usage = float(scheduler.kv_cache_manager.usage)
+            for engine_output in outputs.values():
+                stats = getattr(engine_output, "scheduler_stats", None)
+                if stats is not None:
+                    stats.kv_cache_usage = usage
+    for req_id in scheduler_output.finished_req_ids:
+        scheduler._prefill_lens.pop(req_id, None)
+        scheduler._length_threshold_cache.pop(req_id, None)
+        scheduler._effective_len_tracker.remove_request(req_id)
+    return outputs
