@@ -105,3 +105,59 @@ def test_trigger_compress_reclaim_loop():
     assert all(len(f) == 1 for f in pool.freed) and len(pool.freed) == len(triggers)
     assert scheduler_side.prepare_request_effective_num_computed(request) == \
         sched._effective_len_tracker.observe_num_computed("r", request.num_computed_tokens)
+
+
+def test_loop_through_the_top_level_entry_points():
+    """The same request through ``schedule_with_signals`` -> ``TriAttentionModelRunner.execute_model`` ->
+    ``update_from_output_with_events``: the entry points an engine binds, nothing called in between."""
+    from triattention_b200 import worker_runner
+    from triattention_b200.config import TriAttentionRuntimeConfig
+
+    cfg = TriAttentionRuntimeConfig(kv_budget=BUDGET, divide_length=SLACK, window_size=8, log_decisions=False)
+    pool = _Pool()
+    pool.num_gpu_blocks = 1000
+    manager = types.SimpleNamespace(req_to_blocks={"r": []}, num_cached_block={}, block_pool=pool)
+    request = types.SimpleNamespace(num_computed_tokens=0, num_prompt_tokens=PROMPT)
+    sched = types.SimpleNamespace(
+        kv_cache_manager=types.SimpleNamespace(coordinator=types.SimpleNamespace(single_type_managers=[manager]),
+                                               block_pool=pool, usage=0.1),
+        block_size=BS, requests={"r": request}, running=[request], max_num_scheduled_tokens=8192)
+    scheduler_side.attach_scheduler_state(sched, cfg)
+
+    worker_blocks = {"r": []}
+    hook = _Hook(worker_blocks)
+    base_runner = types.SimpleNamespace(requests={"r": types.SimpleNamespace(num_computed_tokens=0)})
+    base_runner.triattention_apply_compression = lambda req_id, signal, scheduler_output: \
+        hook.execute(req_id, signal, scheduler_output).details
+    base_runner.execute_model = lambda scheduler_output, intermediate_tensors=None: types.SimpleNamespace()
+    proxy = worker_runner.TriAttentionModelRunner(base_runner, cfg)
+
+    def base_schedule(s):
+        n_new = PROMPT if s._triattention_step == 0 else 1
+        held = getattr(request, scheduler_side.EFFECTIVE_NUM_COMPUTED_ATTR, None)
+        held = request.num_computed_tokens if held is None else held      # what the allocation patch would use
+        while len(manager.req_to_blocks["r"]) * BS < held + n_new:
+            manager.req_to_blocks["r"].append(pool.take())
+        new = [types.SimpleNamespace(req_id="r", num_computed_tokens=0, prompt_token_ids=[0] * PROMPT)] if n_new > 1 else []
+        return types.SimpleNamespace(num_scheduled_tokens={"r": n_new}, scheduled_new_reqs=new, finished_req_ids=[],
+                                     scheduled_cached_reqs=None)
+
+    triggers = []
+    for step in range(1, 122):
+        so = scheduler_side.schedule_with_signals(sched, base_schedule)
+        worker_blocks["r"] = [b.block_id for b in manager.req_to_blocks["r"]]
+        base_runner.requests["r"].num_computed_tokens = request.num_computed_tokens
+        output = proxy.execute_model(so)
+        request.num_computed_tokens += so.num_scheduled_tokens["r"]
+        scheduler_side.update_from_output_with_events(sched, so, output, lambda s, a, b: {})
+        if output.triattention_compression_events:
+            triggers.append(step)
+            assert [b.block_id for b in manager.req_to_blocks["r"]] == worker_blocks["r"]
+            assert len(worker_blocks["r"]) == BUDGET // BS
+    # The first trigger is the scheduler's (70 + 10 tokens = budget + slack).  Later ones are the worker's own: its
+    # count starts at budget + 1 after a compression (the step's token is already in) and the self-trigger adds the
+    # step's token once more, so it fires two steps before the scheduler would - every 14 steps, as in the reference.
+    assert triggers == [11, 25, 39, 53, 67, 81, 95, 109]
+    assert proxy.snapshot_states()["r"].compression_count == len(triggers)
+    assert len(pool.freed) == len(triggers)
+    assert sched._effective_len_tracker.snapshot()["r"] == (BUDGET + 121 - triggers[-1], request.num_computed_tokens)
