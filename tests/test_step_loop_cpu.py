@@ -160,4 +160,5 @@ def test_loop_through_the_top_level_entry_points():
     assert triggers == [11, 25, 39, 53, 67, 81, 95, 109]
     assert proxy.snapshot_states()["r"].compression_count == len(triggers)
     assert len(pool.freed) == len(triggers)
-    assert sched._effective_len_tracker.snapshot()["r"] == (BUDGET + 121 - triggers[-1], request.num_computed_tokens)
+    # the tracker last looked at the request when step 121 was scheduled: 120 steps done, the last compaction in step 109
+    assert sched._effective_len_tracker.snapshot()["r"] == (BUDGET + 120 - triggers[-1], request.num_computed_tokens - 1)
