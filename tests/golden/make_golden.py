@@ -16,6 +16,7 @@ Run where a checkout of the reference is available (default: a directory
     python tests/golden/make_golden.py --only step_lifecycle # only step_lifecycle_cases.json
     python tests/golden/make_golden.py --only scheduler_side # only scheduler_side_cases.json
     python tests/golden/make_golden.py --only worker_runner  # only worker_runner_cases.json
+    python tests/golden/make_golden.py --only input_patch_closures  # only input_patch_closure_cases.json
 
 The reference is imported unmodified, on CPU, with three test-side shims:
 
@@ -820,6 +821,30 @@ def gen_worker_runner_cases(out: dict):
     out["worker_runner_cases"] = {"file": "worker_runner_cases.json", "sections": sorted(res)}
 
 
+def gen_input_patch_closure_cases(out: dict):
+    """The reference's patched prepare_pos_seq_lens / compute_slot_mappings closures
+    (runtime/input_patch_vllm_backend.py:105-244) with its own override state, on CPU tensors, along
+    tests/input_patch_closure_scenarios.py."""
+    from triattention.vllm.runtime import input_adapter, input_patch_state, input_patch_vllm_backend as be
+    import input_patch_closure_scenarios as ipc
+
+    class _RefApi:
+        make_prepare = staticmethod(be.make_patched_prepare_pos_seq_lens)
+        make_slots = staticmethod(be.make_patched_compute_slot_mappings)
+
+        @staticmethod
+        def scope(ov):
+            return input_adapter.active_effective_input_overrides(input_adapter.EffectiveInputOverrides(**ov))
+
+        @staticmethod
+        def consumed():
+            return input_patch_state.active_effective_overrides_consumed()
+
+    res = {c["name"]: ipc.run_case(_RefApi, c, "cpu") for c in ipc.CASES}
+    (HERE / "input_patch_closure_cases.json").write_text(json.dumps(res, indent=1, sort_keys=True))
+    out["input_patch_closure_cases"] = {"file": "input_patch_closure_cases.json", "cases": sorted(res)}
+
+
 PARTIAL = {
     # --only <name>: regenerate one group of fixtures and merge it into manifest.json
     "calibration": lambda out: gen_calibration_cases(out),
@@ -833,6 +858,7 @@ PARTIAL = {
     "step_lifecycle": lambda out: gen_step_lifecycle_cases(out),
     "scheduler_side": lambda out: gen_scheduler_side_cases(out),
     "worker_runner": lambda out: gen_worker_runner_cases(out),
+    "input_patch_closures": lambda out: gen_input_patch_closure_cases(out),
 }
 
 
@@ -861,6 +887,7 @@ def main():
     gen_step_lifecycle_cases(out)
     gen_scheduler_side_cases(out)
     gen_worker_runner_cases(out)
+    gen_input_patch_closure_cases(out)
     (HERE / "manifest.json").write_text(json.dumps(out, indent=1, sort_keys=True))
     print("wrote", [p.name for p in HERE.iterdir()])
 

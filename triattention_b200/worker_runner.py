@@ -13,6 +13,7 @@ input preparation of the engine learns the overrides of the step - is a context 
 from __future__ import annotations
 
 import logging
+import os
 import time
 from contextlib import contextmanager
 from dataclasses import dataclass
@@ -199,6 +200,7 @@ def prepare_effective_input_overrides(*, base_runner: Any, state_store: Any, sch
 
 
 _ACTIVE: Optional[EffectiveInputOverrides] = None
+_FLAGS = {"consumed": False, "validated": False}  # of the scope in progress: seen by the patched input preparation / checked once
 
 
 def current_effective_input_overrides() -> Optional[EffectiveInputOverrides]:
@@ -206,14 +208,37 @@ def current_effective_input_overrides() -> Optional[EffectiveInputOverrides]:
     return _ACTIVE
 
 
+def mark_effective_overrides_consumed() -> None:
+    _FLAGS["consumed"] = True
+
+
+def effective_overrides_consumed() -> bool:
+    return bool(_FLAGS["consumed"])
+
+
+def mapping_validated(mark: bool = False) -> bool:
+    """Has the batch packing of this scope been checked against the expected rows already?  ``mark`` records it."""
+    if mark:
+        _FLAGS["validated"] = True
+    return bool(_FLAGS["validated"])
+
+
+def assert_effective_overrides_consumed() -> None:
+    if not _FLAGS["consumed"]:
+        raise RuntimeError("TRIATTN_EFFECTIVE_OVERRIDES_NOT_CONSUMED:"
+                           "runtime_overrides_activated_but_patched_input_prep_not_observed")
+
+
 @contextmanager
 def active_effective_input_overrides(overrides: EffectiveInputOverrides) -> Iterator[EffectiveInputOverrides]:
     global _ACTIVE
     _ACTIVE = overrides
+    _FLAGS["consumed"] = _FLAGS["validated"] = False
     try:
         yield overrides
     finally:
         _ACTIVE = None
+        _FLAGS["consumed"] = _FLAGS["validated"] = False
 
 
 def execute_base_model_with_effective_overrides(*, base_runner: Any, state_store: Any, scheduler_output: Any,
@@ -235,6 +260,11 @@ def execute_base_model_with_effective_overrides(*, base_runner: Any, state_store
         with override_scope(overrides):
             output = base_runner.execute_model(scheduler_output=scheduler_output,
                                                intermediate_tensors=intermediate_tensors)
+            # a runner with device-side request states must have gone through the patched input preparation
+            if override_scope is active_effective_input_overrides and (
+                    getattr(base_runner, "req_states", None) is not None
+                    or os.environ.get("TRIATTN_DEBUG_ENABLE_V1_OVERRIDE_PATH", "0") == "1"):
+                assert_effective_overrides_consumed()
     if isinstance(perf_out, dict):
         perf_out["override_prep_ms"] = (t1 - t0) * 1e3 if use_effective_overrides else 0.0
         perf_out["base_exec_ms"] = (clock() - t1) * 1e3
