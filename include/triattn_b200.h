@@ -211,6 +211,24 @@ int triattn_finalize_scores(const triattn_paged_layout* layout /* host */, const
                             float* scores_out, void* stream);
 
 /*
+ * triattn_finalize_scores with layer_reduce NONE for tensor-parallel layer-shared selection, exchange included:
+ * the L*B*Ho output rows are dealt to the ranks in runs of rows/num_ranks, and every row is stored straight into
+ * the receive buffer of the rank that owns it - recv_ptrs[owner], a device array of num_ranks pointers, each to
+ * a [num_ranks, rows/num_ranks, t_pad] fp32 buffer (peer memory reachable from this device; the own buffer
+ * included) - at slot [rank][row % (rows/num_ranks)], by plain stores.  After a barrier across the ranks each
+ * owner holds everybody's values of its rows; triattn_max_over_slots folds them.  rows must divide by num_ranks.
+ * Replaces the all-reduce / reduce-scatter of score rows a layer-shared step would otherwise need
+ * (the reference runs this mode on one device: selector_hf.py:636-667).
+ */
+int triattn_finalize_scores_scatter(const triattn_paged_layout* layout /* host */, const float* raw_scores,
+                                    const double* moments, const int32_t* seq_lens, const int32_t* prefill_lens,
+                                    int window, int normalize, int group_reduce, int head_reduce,
+                                    float* const* recv_ptrs /* device array */, int num_ranks, int rank, void* stream);
+
+/* out[i] = max over s < num_slots of slots[s * elems_per_slot + i]; both pointers 16-byte aligned. */
+int triattn_max_over_slots(const float* slots, int num_slots, int64_t elems_per_slot, float* out, void* stream);
+
+/*
  * Per-row top-k with deterministic lowest-index tie-break; indices come out ascending.
  * Row r belongs to request b = (r / rows_per_req_inner) % num_reqs, has seq_lens[b] valid scores and
  * keeps keep_counts[b] of them (clamped to the row length).

@@ -328,3 +328,50 @@ def test_abi_rejects_bad_arguments():
     assert rc == 2  # group size 80 is beyond the supported 64
     with pytest.raises(_native.NativeLibraryError):
         _native.check(rc, "score_paged")
+
+
+@pytest.mark.parametrize("hkv,g", [(1, 8), (2, 4)])
+def test_finalize_scatter_and_max_over_slots(hkv, g):
+    """The scattered form of the per-layer finalize: two "ranks" (two sets of raw scores on this device, two receive
+    buffers) store their rows into the owner's slots; folding an owner's slots must give, bit for bit, the maximum of
+    the two ranks' ordinary finalize outputs for the owner's rows.  One local KV head takes the fast kernel, two (with
+    the maximum over heads) the general one."""
+    dev = "cuda"
+    gen = torch.Generator(device=dev).manual_seed(41 + hkv)
+    L, B, bs, nblk, window = 4, 3, 16, 9, 8
+    t_pad = bs * nblk
+    gp = _native.load().triattn_padded_group(g)
+    layout = _native.PagedLayout(num_layers=L, num_reqs=B, num_kv_heads=hkv, group_size=g, head_dim=128, block_size=bs,
+                                 num_blocks=64, max_blocks_per_req=nblk, block_stride=bs * hkv * 128,
+                                 token_stride=hkv * 128, head_stride=128, rope_interleaved=0, reserved=0)
+    seq = torch.tensor([t_pad, 77, 130], dtype=torch.int32, device=dev)
+    pre = torch.tensor([0, 5, 0], dtype=torch.int32, device=dev)
+    head_reduce = _native.REDUCE_MAX if hkv > 1 else _native.REDUCE_NONE
+    ranks, rows = 2, L * B
+    rpr = rows // ranks
+    recv = [torch.full((ranks, rpr, t_pad), float("nan"), dtype=torch.float32, device=dev) for _ in range(ranks)]
+    ptrs = torch.tensor([r.data_ptr() for r in recv], dtype=torch.int64, device=dev)
+    plain = []
+    for rank in range(ranks):
+        raw = torch.randn((L, B, hkv, t_pad, gp), generator=gen, device=dev)
+        n = seq.view(1, B, 1, 1, 1).double()
+        valid = (torch.arange(t_pad, device=dev).view(1, 1, 1, t_pad, 1) < seq.view(1, B, 1, 1, 1))
+        x = torch.where(valid, raw.double(), torch.zeros((), dtype=torch.float64, device=dev))[..., :g]
+        mom = torch.stack([x.sum(3), (x * x).sum(3)], dim=-1).reshape(L, B, hkv * g, 2).contiguous()
+        plain.append(ops.finalize_scores(layout, raw, mom, seq, pre, window, True, _native.REDUCE_MAX, head_reduce,
+                                         _native.REDUCE_NONE))
+        ops.finalize_scores_scatter(layout, raw, mom, seq, pre, window, True, _native.REDUCE_MAX, head_reduce, ptrs, rank)
+    torch.cuda.synchronize()
+    want = torch.maximum(plain[0], plain[1]).view(rows, t_pad)             # rows (l, b), one head per row
+    for owner in range(ranks):
+        got = ops.max_over_slots(recv[owner])                               # [rpr, t_pad]
+        for i in range(rpr):
+            r = owner * rpr + i
+            n_tok = int(seq[r % B])
+            assert torch.equal(got[i, :n_tok], want[r, :n_tok]), (owner, i)
+        # guards arrive as +inf: the last `window` tokens and the protected prompt of request 1
+        b1 = [i for i in range(rpr) if (owner * rpr + i) % B == 1][0]
+        assert bool(torch.isinf(got[b1, :5]).all()) and bool(torch.isinf(got[b1, 77 - window:77]).all())
+    # odd element count: the scalar path of the fold
+    x = torch.randn((3, 7), generator=gen, device=dev)
+    assert torch.equal(ops.max_over_slots(x), x.max(dim=0).values)

@@ -38,6 +38,8 @@ EXPORTED_SYMBOLS = (
     "triattn_score_paged",
     "triattn_score_paged_cuda_cores",
     "triattn_finalize_scores",
+    "triattn_finalize_scores_scatter",
+    "triattn_max_over_slots",
     "triattn_select_topk",
     "triattn_compact_paged",
     "triattn_compact_preserve_scratch_bytes",
@@ -102,6 +104,10 @@ def _declare(lib) -> None:
     lib.triattn_score_paged_cuda_cores.argtypes = [LP, P, P, P, P, c_int, c_int, P, P, P, P]
     lib.triattn_finalize_scores.restype = c_int
     lib.triattn_finalize_scores.argtypes = [LP, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, P]
+    lib.triattn_finalize_scores_scatter.restype = c_int
+    lib.triattn_finalize_scores_scatter.argtypes = [LP, P, P, P, P, c_int, c_int, c_int, c_int, P, c_int, c_int, P]
+    lib.triattn_max_over_slots.restype = c_int
+    lib.triattn_max_over_slots.argtypes = [P, c_int, c_int64, P, P]
     lib.triattn_select_topk.restype = c_int
     lib.triattn_select_topk.argtypes = [P, c_int, c_int64, P, P, c_int, c_int, P, c_int, P, P]
     lib.triattn_compact_paged.restype = c_int

@@ -195,10 +195,15 @@ int score_paged_impl(const triattn_paged_layout* layout, const void* const* k_la
                      const int32_t* seq_lens, const float* weights, int offset_agg, int num_offsets,
                      float* raw_scores, double* moments, uint32_t* device_status, cudaStream_t st,
                      const StageOpts& opt);
+struct ScatterOut {
+  float* const* ptrs = nullptr;  // [ranks] device pointers to the ranks' receive buffers
+  int rows = 0, rank = 0;        // output rows per rank; this rank
+};
 int finalize_scores_impl(const triattn_paged_layout* layout, const float* raw_scores, const double* moments,
                          const int32_t* seq_lens, const int32_t* prefill_lens, int window, int normalize,
                          int group_reduce, int head_reduce, int layer_reduce, int l_total, bool first_chunk,
-                         bool last_chunk, float* scores_out, cudaStream_t st, bool pdl);
+                         bool last_chunk, float* scores_out, cudaStream_t st, bool pdl,
+                         const ScatterOut& scatter = ScatterOut{});
 
 }  // namespace
 
@@ -320,6 +325,35 @@ int triattn_finalize_scores(const triattn_paged_layout* layout, const float* raw
   return finalize_scores_impl(layout, raw_scores, moments, seq_lens, prefill_lens, window, normalize, group_reduce,
                               head_reduce, layer_reduce, layout->num_layers, true, true, scores_out,
                               static_cast<cudaStream_t>(stream), false);
+}
+
+int triattn_finalize_scores_scatter(const triattn_paged_layout* layout, const float* raw_scores, const double* moments,
+                                    const int32_t* seq_lens, const int32_t* prefill_lens, int window, int normalize,
+                                    int group_reduce, int head_reduce, float* const* recv_ptrs, int num_ranks, int rank,
+                                    void* stream) {
+  int rc = validate_layout(layout);
+  if (rc != TRIATTN_OK) return rc;
+  if (!recv_ptrs || num_ranks <= 0 || rank < 0 || rank >= num_ranks) return TRIATTN_ERR_INVALID_ARGUMENT;
+  const long long rows = (long long)layout->num_layers * layout->num_reqs *
+                         (head_reduce != TRIATTN_REDUCE_NONE ? 1 : layout->num_kv_heads);
+  if (rows % num_ranks != 0) return TRIATTN_ERR_INVALID_ARGUMENT;
+  ScatterOut sc;
+  sc.ptrs = recv_ptrs;
+  sc.rows = (int)(rows / num_ranks);
+  sc.rank = rank;
+  return finalize_scores_impl(layout, raw_scores, moments, seq_lens, prefill_lens, window, normalize, group_reduce,
+                              head_reduce, TRIATTN_REDUCE_NONE, layout->num_layers, true, true, nullptr,
+                              static_cast<cudaStream_t>(stream), false, sc);
+}
+
+int triattn_max_over_slots(const float* slots, int num_slots, int64_t elems_per_slot, float* out, void* stream) {
+  if (!slots || !out || num_slots <= 0 || elems_per_slot <= 0) return TRIATTN_ERR_INVALID_ARGUMENT;
+  if (!aligned16(slots) || !aligned16(out)) return TRIATTN_ERR_MISALIGNED;
+  const size_t n = (size_t)elems_per_slot;
+  const size_t work = (n & 3) == 0 ? n / 4 : n;
+  const unsigned blocks = (unsigned)std::min<size_t>((work + 255) / 256, (size_t)kSMs * 8);
+  max_over_slots_kernel<<<std::max(1u, blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(slots, num_slots, n, out);
+  return check_launch();
 }
 
 static int select_topk_impl(const float* scores, int num_rows, int64_t row_stride, const int32_t* seq_lens,
@@ -804,8 +838,10 @@ int score_paged_impl(const triattn_paged_layout* layout, const void* const* k_la
 int finalize_scores_impl(const triattn_paged_layout* layout, const float* raw_scores, const double* moments,
                          const int32_t* seq_lens, const int32_t* prefill_lens, int window, int normalize,
                          int group_reduce, int head_reduce, int layer_reduce, int l_total, bool first_chunk,
-                         bool last_chunk, float* scores_out, cudaStream_t st, bool pdl) {
-  if (!raw_scores || !moments || !seq_lens || !scores_out) return TRIATTN_ERR_INVALID_ARGUMENT;
+                         bool last_chunk, float* scores_out, cudaStream_t st, bool pdl, const ScatterOut& scatter) {
+  if (!raw_scores || !moments || !seq_lens || (!scores_out && !scatter.ptrs)) return TRIATTN_ERR_INVALID_ARGUMENT;
+  if (scatter.ptrs && (layer_reduce != TRIATTN_REDUCE_NONE || scatter.rows <= 0 || scatter.rank < 0))
+    return TRIATTN_ERR_INVALID_ARGUMENT;
   if (group_reduce != TRIATTN_REDUCE_MAX && group_reduce != TRIATTN_REDUCE_MEAN) return TRIATTN_ERR_INVALID_ARGUMENT;
   if (head_reduce != TRIATTN_REDUCE_NONE && head_reduce != TRIATTN_REDUCE_MAX) return TRIATTN_ERR_INVALID_ARGUMENT;
   if (layer_reduce < TRIATTN_REDUCE_NONE || layer_reduce > TRIATTN_REDUCE_MAX) return TRIATTN_ERR_INVALID_ARGUMENT;
@@ -833,6 +869,9 @@ int finalize_scores_impl(const triattn_paged_layout* layout, const float* raw_sc
   p.first_chunk = first_chunk ? 1 : 0;
   p.last_chunk = last_chunk ? 1 : 0;
   p.gp = gp;
+  p.scatter_out = scatter.ptrs;
+  p.scatter_rows = scatter.rows;
+  p.scatter_rank = scatter.rank;
   const int Ho = head_reduce != TRIATTN_REDUCE_NONE ? 1 : Y.num_kv_heads;
   dim3 grid((unsigned)((t_pad + 255) / 256), (unsigned)Ho, (unsigned)Y.num_reqs);
   // (mean, 1/std) of the rows a CTA normalises with live in its shared memory

@@ -34,7 +34,19 @@ struct FinalizeParams {
   // call, l_total those of the whole step.  With a layer reduction, every call but the first continues from
   // the value already in `out` and only the last one divides the mean.
   int l_total, first_chunk, last_chunk;
+  // Scatter mode (layer_reduce NONE, tensor-parallel layer-shared selection): output row r = (l * B + b) * Ho + ho
+  // belongs to rank r / scatter_rows and is stored straight into THAT rank's receive buffer - a peer pointer, plain
+  // stores over NVLink - at slot [scatter_rank][r % scatter_rows], so the exchange rides on the stores of this kernel.
+  float* const* scatter_out;  // [ranks] device pointers to the ranks' [ranks, scatter_rows, t_pad] buffers, or null
+  int scatter_rows, scatter_rank;
 };
+
+// where the value of output row `row` (layer_reduce NONE), token t, goes
+__device__ __forceinline__ float* finalize_row_dst(const FinalizeParams& p, size_t row, int t) {
+  if (p.scatter_out == nullptr) return p.out + row * (size_t)p.t_pad + t;
+  const size_t owner = row / (size_t)p.scatter_rows, local = row - owner * (size_t)p.scatter_rows;
+  return p.scatter_out[owner] + ((size_t)p.scatter_rank * p.scatter_rows + local) * (size_t)p.t_pad + t;
+}
 
 // one thread per (request, output head, token); gp = query-head slots per KV head in the raw layout.
 // Dynamic shared memory: (mean, 1/std) of the L x (heads this CTA reduces) rows it normalises with.
@@ -107,7 +119,7 @@ __global__ void __launch_bounds__(256) finalize_scores_kernel(const __grid_const
     }
     const bool first = l == 0 && p.first_chunk;
     if (p.layer_reduce == TRIATTN_REDUCE_NONE) {
-      p.out[(((size_t)l * p.B + b) * Ho + ho) * (size_t)p.t_pad + t] = lv;
+      *finalize_row_dst(p, ((size_t)l * p.B + b) * Ho + ho, t) = lv;
     } else if (p.layer_reduce == TRIATTN_REDUCE_MAX) {
       acc = first ? lv : fmaxf(acc, lv);
     } else {
@@ -152,7 +164,7 @@ __global__ void __launch_bounds__(256) finalize_scores_fast_kernel(const __grid_
   if (guarded) {
     // +inf survives max and sum over layers and the division of the mean
     if (LR == TRIATTN_REDUCE_NONE) {
-      for (int l = 0; l < p.L; ++l) out[(size_t)l * out_layer_stride] = INFINITY;
+      for (int l = 0; l < p.L; ++l) *finalize_row_dst(p, ((size_t)l * p.B + b) * p.Hkv + kvh, t) = INFINITY;
     } else {
       *out = INFINITY;
     }
@@ -179,7 +191,7 @@ __global__ void __launch_bounds__(256) finalize_scores_fast_kernel(const __grid_
     const float lv = group_mean ? __fdiv_rn(sum, (float)G) : mx;
     const bool first = l == 0 && first_chunk;
     if (LR == TRIATTN_REDUCE_NONE) {
-      out[(size_t)l * out_layer_stride] = lv;
+      *finalize_row_dst(p, ((size_t)l * p.B + b) * p.Hkv + kvh, t) = lv;
     } else if (LR == TRIATTN_REDUCE_MAX) {
       acc = first ? lv : fmaxf(acc, lv);
     } else {
@@ -205,6 +217,32 @@ __global__ void __launch_bounds__(256) finalize_scores_fast_kernel(const __grid_
   }
   if (LR == TRIATTN_REDUCE_MEAN && p.last_chunk) acc = __fdiv_rn(acc, (float)p.l_total);
   if (LR != TRIATTN_REDUCE_NONE) *out = acc;
+}
+
+// out[i] = max over the `slots` receive slots of x[s * n + i]: the owner's half of the scattered exchange.
+__global__ void __launch_bounds__(256) max_over_slots_kernel(const float* __restrict__ x, int slots, size_t n,
+                                                             float* __restrict__ out) {
+  grid_dependency_wait();
+  trigger_dependents();
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  if ((n & 3) == 0) {
+    const size_t n4 = n >> 2;
+    const float4* x4 = reinterpret_cast<const float4*>(x);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+      float4 m = __ldcs(x4 + i);
+      for (int s = 1; s < slots; ++s) {
+        const float4 v = __ldcs(x4 + (size_t)s * n4 + i);
+        m.x = fmaxf(m.x, v.x); m.y = fmaxf(m.y, v.y); m.z = fmaxf(m.z, v.z); m.w = fmaxf(m.w, v.w);
+      }
+      reinterpret_cast<float4*>(out)[i] = m;
+    }
+  } else {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+      float m = x[i];
+      for (int s = 1; s < slots; ++s) m = fmaxf(m, x[(size_t)s * n + i]);
+      out[i] = m;
+    }
+  }
 }
 
 }  // namespace triattn

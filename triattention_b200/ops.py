@@ -265,6 +265,36 @@ def finalize_scores(layout: PagedLayout, raw: torch.Tensor, moments: torch.Tenso
     return out
 
 
+def finalize_scores_scatter(layout: PagedLayout, raw: torch.Tensor, moments: torch.Tensor, seq_lens: torch.Tensor,
+                            prefill_lens: Optional[torch.Tensor], window: int, normalize: bool, group_reduce: int,
+                            head_reduce: int, recv_ptrs: torch.Tensor, rank: int) -> None:
+    """Per-layer score rows, each stored into the receive buffer of the rank that owns it
+    (``triattn_finalize_scores_scatter``).  ``recv_ptrs``: int64 device tensor with one pointer per rank to that
+    rank's ``[ranks, rows / ranks, t_pad]`` fp32 buffer, valid on this device (peer mappings; the own buffer
+    included)."""
+    lib = _native.load()
+    _require_cuda(recv_ptrs, "recv_ptrs")
+    if recv_ptrs.dtype != torch.int64 or not recv_ptrs.is_contiguous():
+        raise ValueError("recv_ptrs must be a contiguous int64 tensor of device pointers")
+    _native.check(lib.triattn_finalize_scores_scatter(
+        ctypes.byref(layout), _ptr(raw), _ptr(moments), _ptr(seq_lens), _ptr(prefill_lens), int(window),
+        1 if normalize else 0, group_reduce, head_reduce, _ptr(recv_ptrs), int(recv_ptrs.numel()), int(rank), _stream()),
+        "finalize_scores_scatter")
+
+
+def max_over_slots(slots: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``slots`` ``[S, ...]`` fp32 -> elementwise maximum over the first axis (``triattn_max_over_slots``)."""
+    lib = _native.load()
+    _require_cuda(slots, "slots")
+    if slots.dtype != torch.float32 or not slots.is_contiguous():
+        raise ValueError("slots must be a contiguous fp32 tensor")
+    if out is None:
+        out = torch.empty(slots.shape[1:], dtype=torch.float32, device=slots.device)
+    _native.check(lib.triattn_max_over_slots(_ptr(slots), int(slots.shape[0]), int(out.numel()), _ptr(out), _stream()),
+                  "max_over_slots")
+    return out
+
+
 def select_topk(scores: torch.Tensor, seq_lens: torch.Tensor, keep_counts: torch.Tensor, num_reqs: int,
                 rows_per_req_inner: int, keep_pitch: int, status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Ascending keep indices ``[rows, keep_pitch]`` int32 (``triattn_select_topk``); ``scores`` is ``[rows, stride]``."""
