@@ -70,9 +70,15 @@ def _worker(rank: int, world: int, port: int, q, layers: int = 2):
         per_head = res.keep.cpu()
         local2 = [c[:, :, :, lo:hi].contiguous().to(dev) for c in caches]
         view2 = ops.PagedCacheView.from_layers(local2, kv_axis=0)
-        res2 = engine.compress_layer_shared(view2, shard, ids, lens, starts, budgets, window=32)
-        q.put((rank, per_head, res2.keep.cpu(), res.device_status | res2.device_status,
-               [c.cpu() for c in local2]))
+        timings = {}
+        res2 = engine.compress_layer_shared(view2, shard, ids, lens, starts, budgets, window=32, timings=timings)
+        # a second step on the same buffers (the peer-store form reuses its receive slots), lengths as they are now
+        lens2 = [256, 512]
+        res3 = engine.compress_layer_shared(view2, shard, [i[:16] for i in [ids[0]]] + [ids[1][:32]], lens2, starts,
+                                            [200, 400], window=32)
+        print(f"rank {rank} layers {layers}: exchange = {timings['exchange']}", flush=True)
+        q.put((rank, per_head, res2.keep.cpu(), res.device_status | res2.device_status | res3.device_status,
+               [c.cpu() for c in local2], timings["exchange"], res3.keep.cpu()))
         dist.barrier()
     finally:
         dist.destroy_process_group()
@@ -91,8 +97,8 @@ def test_tp2_matches_single_gpu(layers):
         p.start()
     out = {}
     for _ in procs:
-        rank, per_head, shared, status, caches = q.get(timeout=300)
-        out[rank] = (per_head.clone(), shared.clone(), status, [c.clone() for c in caches])
+        rank, per_head, shared, status, caches, exchange, shared3 = q.get(timeout=300)
+        out[rank] = (per_head.clone(), shared.clone(), status, [c.clone() for c in caches], exchange, shared3.clone())
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
@@ -107,9 +113,14 @@ def test_tp2_matches_single_gpu(layers):
     one2 = [c.to(dev) for c in caches]
     res2 = engine.compress_layer_shared(ops.PagedCacheView.from_layers(one2, kv_axis=0), full, ids, lens, starts, budgets,
                                         window=32)
+    res3 = engine.compress_layer_shared(ops.PagedCacheView.from_layers(one2, kv_axis=0), full,
+                                        [ids[0][:16], ids[1][:32]], [256, 512], starts, [200, 400], window=32)
     for rank in (0, 1):
-        per_head, shared, status, shard_caches = out[rank]
+        per_head, shared, status, shard_caches, exchange, shared3 = out[rank]
         assert status == 0
+        # whole layers per rank: peer stores (or the NCCL reduce-scatter where symmetric memory is unavailable)
+        assert exchange.startswith(("peer stores", "reduce-scatter") if layers == 2 else "all-reduce"), exchange
+        assert torch.equal(shared3, res3.keep.cpu())
         assert torch.equal(per_head, res.keep.cpu()[:, 2 * rank: 2 * rank + 2])       # heads of this rank, no collective
         assert torch.equal(shared, res2.keep.cpu())                                   # identical on every rank
         for l in range(len(caches)):

@@ -259,15 +259,38 @@ def compress_layer_shared(
     raw, mom = ops.score_paged(view, layout, bt, d_seq, w, offset_agg, int(stats.offsets.numel()), status)
     # max over this rank's KV heads (nothing to reduce with a single local head: the per-head fast kernel serves)
     head_reduce = _native.REDUCE_MAX if view.num_kv_heads > 1 else _native.REDUCE_NONE
-    fin = ops.finalize_scores(layout, raw, mom, d_seq, d_pre if prefill_lens is not None else None, window, normalize,
-                              _native.REDUCE_MAX, head_reduce, _native.REDUCE_NONE)   # [L, B, 1, t_pad]
     L = view.num_layers
-    rows = fin.view(L * B, fin.shape[-1])  # rows (l, b)
+    t_pad = max_blocks * bs
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if timings is not None else None
     scatter = process_group is not False and _tp.can_scatter_rows(L, process_group)
+    peers = None
+    if scatter:
+        group = process_group if process_group is not None else None
+        peers = _tp.peer_row_exchange(L * B // _tp._group_size(group), t_pad, dev, group)
+    fin = None
+    if peers is not None:
+        # the exchange rides on the finalize: every row goes straight into the slot of the rank that owns its layer
+        ops.finalize_scores_scatter(layout, raw, mom, d_seq, d_pre if prefill_lens is not None else None, window,
+                                    normalize, _native.REDUCE_MAX, head_reduce, peers.ptrs, peers.rank)
+    else:
+        fin = ops.finalize_scores(layout, raw, mom, d_seq, d_pre if prefill_lens is not None else None, window,
+                                  normalize, _native.REDUCE_MAX, head_reduce, _native.REDUCE_NONE)   # [L, B, 1, t_pad]
+        rows = fin.view(L * B, fin.shape[-1])  # rows (l, b)
     if ev:
         ev[0].record()
-    if scatter:
+    if peers is not None:
+        peers.barrier()                                    # all ranks' stores into this rank's slots are complete
+        slots, folded = peers.views(L * B // peers.world, t_pad)
+        mine = ops.max_over_slots(slots, folded)
+        if ev:
+            ev[1].record()
+        keep_mine = ops.select_topk(mine, d_seq, d_kc, B, 1, keep_pitch, status)
+        if ev:
+            ev[2].record()
+        keep = _tp.all_gather_keep(keep_mine, process_group)   # also the barrier that frees the slots for the next step
+        if ev:
+            ev[3].record()
+    elif scatter:
         # whole layers per rank: finished rows of this rank's layers -> top-k on them -> everybody's keep rows
         mine = _tp.reduce_scatter_shared_scores(rows, process_group)
         if ev:
@@ -288,9 +311,12 @@ def compress_layer_shared(
         keep = ops.select_topk(rows, d_seq, d_kc, B, 1, keep_pitch, status)
     if timings is not None:
         timings["allreduce_ms"] = lambda: ev[0].elapsed_time(ev[1]) + ev[2].elapsed_time(ev[3])
-        timings["allreduce_bytes"] = int(fin.numel()) * 4 + (int(keep.numel()) * 4 if scatter else 0)
-        timings["exchange"] = ("reduce-scatter(MAX) of the fp32 score rows + all-gather of the keep indices" if scatter
-                               else "all-reduce(MAX) of the fp32 score rows")
+        timings["allreduce_bytes"] = L * B * t_pad * 4 + (int(keep.numel()) * 4 if scatter else 0)
+        timings["exchange"] = (
+            "peer stores of the fp32 score rows inside finalize (symmetric memory) + barrier + fold, all-gather of the "
+            "keep indices" if peers is not None else
+            "reduce-scatter(MAX) of the fp32 score rows + all-gather of the keep indices" if scatter
+            else "all-reduce(MAX) of the fp32 score rows")
     ops.compact_paged(view, layout, bt, d_seq, keep, (B * keep_pitch, keep_pitch, 0), d_kc, status)
     bits = int(status.item())
     kept, removed = [], []

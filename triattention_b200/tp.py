@@ -80,3 +80,79 @@ def all_gather_keep(local_keep: torch.Tensor, group: Optional[dist.ProcessGroup]
     dist.all_gather_into_tensor(out, local_keep.contiguous(), group=group)
     return out
 
+
+
+# ------------------------------------------------------------------------------------------------ peer-store exchange
+class PeerRowExchange:
+    """Receive buffers for the scattered form of the layer-shared exchange.
+
+    Every rank owns ``rows_per_rank`` consecutive score rows and holds ``[world, rows_per_rank, t_pad]`` fp32 receive
+    slots in symmetric memory (``torch.distributed._symmetric_memory``: the same allocation on every rank, mapped
+    into every peer's address space; multicast binding is switched off - plain peer stores are all that is used).
+    ``ptrs`` is the int64 device tensor of the ranks' buffer addresses that ``ops.finalize_scores_scatter`` stores
+    through; ``barrier`` is a one-element NCCL all-reduce: when it has completed on this rank, every rank's finalize
+    has, and with it all stores into this rank's slots.  The buffer is sized for the largest step seen so far.
+    """
+
+    def __init__(self, capacity_floats: int, device: torch.device, group=None):
+        import os
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.capacity = int(capacity_floats)
+        self._flat = symm_mem.empty(self.capacity, dtype=torch.float32, device=device)
+        self._handle = symm_mem.rendezvous(self._flat, self.group)
+        ptrs = [int(p) for p in self._handle.buffer_ptrs]
+        if len(ptrs) != self.world or any(p == 0 for p in ptrs) or ptrs[self.rank] != self._flat.data_ptr():
+            raise RuntimeError("symmetric memory did not return one mapped buffer per rank")
+        self.ptrs = torch.tensor(ptrs, dtype=torch.int64, device=device)
+        self._folded = torch.empty(self.capacity // self.world, dtype=torch.float32, device=device)
+        self._token = torch.zeros(1, dtype=torch.float32, device=device)
+
+    def views(self, rows_per_rank: int, t_pad: int):
+        """``(slots [world, rows_per_rank, t_pad], folded [rows_per_rank, t_pad])`` over the front of the buffers."""
+        n = rows_per_rank * t_pad
+        return (self._flat[: self.world * n].view(self.world, rows_per_rank, t_pad),
+                self._folded[:n].view(rows_per_rank, t_pad))
+
+    def barrier(self) -> None:
+        dist.all_reduce(self._token, group=self.group)
+
+
+_PEER_EXCHANGES: dict = {}
+
+
+def peer_row_exchange(rows_per_rank: int, t_pad: int, device: torch.device, group=None) -> Optional[PeerRowExchange]:
+    """Exchange buffers large enough for this step (made, or grown, collectively: every rank asks with the same
+    shape in the same step), or None where symmetric memory cannot be set up - then the NCCL reduce-scatter serves.
+    ``TRIATTN_TP_PEER_STORES=0`` switches the peer-store form off."""
+    import os
+
+    if os.environ.get("TRIATTN_TP_PEER_STORES", "1").strip().lower() in {"0", "false", "no", "off"}:
+        return None
+    if not (dist.is_available() and dist.is_initialized()) or torch.device(device).type != "cuda":
+        return None
+    if dist.get_backend(group) != "nccl":
+        return None
+    world = dist.get_world_size(group)
+    need = world * int(rows_per_rank) * int(t_pad)
+    key = (id(group), str(device))
+    have = _PEER_EXCHANGES.get(key, "unset")
+    if have is None or (have != "unset" and have.capacity >= need):
+        return have
+    try:
+        made: Optional[PeerRowExchange] = PeerRowExchange(need, device, group)
+    except Exception as exc:  # no permission for the handle exchange, an older torch, no peer access ...
+        import logging
+        logging.getLogger(__name__).warning("peer-store exchange unavailable (%s: %s); using NCCL reduce-scatter",
+                                            type(exc).__name__, str(exc)[:200])
+        made = None
+    # all ranks take the same road: one rank without the buffers sends everybody to NCCL, for good
+    ok = torch.tensor([1 if made is not None else 0], dtype=torch.int32, device=device)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+    _PEER_EXCHANGES[key] = made if int(ok.item()) == 1 else None
+    return _PEER_EXCHANGES[key]
