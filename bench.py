@@ -583,7 +583,7 @@ def run_c2_legs(args, world, rank, local):
     del comp
     torch.cuda.empty_cache()
 
-    # ---- layer-shared selection: all-reduce(MAX) of [L, B, t_pad] fp32 rows
+    # ---- layer-shared selection: the [L, B, t_pad] fp32 rows cross the ranks (peer stores, else NCCL)
     def shared_once():
         saver.restore()
         timings = {}
@@ -610,7 +610,7 @@ def run_c2_legs(args, world, rank, local):
     same = bool(torch.equal(lo_t, hi_t))
     out["layer_shared"] = {"ms_per_step": sh_ms, "keys_per_s_per_gpu": keys_per_gpu / (sh_ms * 1e-3),
                            "keys_per_s_total": keys_per_gpu * world / (sh_ms * 1e-3),
-                           "collective": "NCCL " + runs[-1][4],
+                           "collective": runs[-1][4] if runs[-1][4].startswith("peer stores") else "NCCL " + runs[-1][4],
                            "allreduce_ms": ar_ms, "allreduce_share": ar_ms / sh_ms, "allreduce_bytes": runs[-1][2],
                            "runs_ms": [round(r[0], 3) for r in runs], "runs_exchange_ms": [round(r[1], 3) for r in runs],
                            "rank_keep_sets_identical": same, "device_status": runs[-1][3].device_status}

@@ -8,10 +8,13 @@ per-head mode needs no communication.
 
 Only the layer-shared keep set (one keep list for all heads = top-k of the max over heads,
 selector_hf.py:636-637) spans ranks: every rank reduces its local heads and the fp32 ``[L * B, t_pad]`` rows
-are combined by MAX.  When the layers divide over the ranks the exchange is a reduce-scatter (each rank
-receives the finished rows of its share of the layers), a top-k on those rows only, and an all-gather of the
-keep indices: half the bytes of an all-reduce on the wire and 1/N of the selection work per rank.  Otherwise
-one all-reduce(MAX) makes the rows global and the deterministic top-k yields identical keep sets everywhere.
+are combined by MAX.  When the layers divide over the ranks each rank finishes the rows of its share of the
+layers only: the finalize kernel stores every row straight into the owner's receive slot over NVLink
+(:class:`PeerRowExchange`, symmetric memory, plain peer stores), the owner folds the slots, runs the top-k on
+its rows, and an all-gather of the keep indices completes the step; without symmetric memory a NCCL
+reduce-scatter(MAX) moves the rows instead (half the bytes of an all-reduce on the wire and 1/N of the
+selection work per rank either way).  Otherwise one all-reduce(MAX) makes the rows global and the
+deterministic top-k yields identical keep sets everywhere.
 """
 from __future__ import annotations
 
