@@ -198,6 +198,7 @@ int score_paged_impl(const triattn_paged_layout* layout, const void* const* k_la
 struct ScatterOut {
   float* const* ptrs = nullptr;  // [ranks] device pointers to the ranks' receive buffers
   int rows = 0, rank = 0;        // output rows per rank; this rank
+  int shift = 0;                 // first layer this rank visits
 };
 int finalize_scores_impl(const triattn_paged_layout* layout, const float* raw_scores, const double* moments,
                          const int32_t* seq_lens, const int32_t* prefill_lens, int window, int normalize,
@@ -341,6 +342,8 @@ int triattn_finalize_scores_scatter(const triattn_paged_layout* layout, const fl
   sc.ptrs = recv_ptrs;
   sc.rows = (int)(rows / num_ranks);
   sc.rank = rank;
+  // start with the layers of the next rank: at any moment the ranks store into different owners
+  sc.shift = (int)(((long long)((rank + 1) % num_ranks) * layout->num_layers) / num_ranks);
   return finalize_scores_impl(layout, raw_scores, moments, seq_lens, prefill_lens, window, normalize, group_reduce,
                               head_reduce, TRIATTN_REDUCE_NONE, layout->num_layers, true, true, nullptr,
                               static_cast<cudaStream_t>(stream), false, sc);
@@ -872,6 +875,7 @@ int finalize_scores_impl(const triattn_paged_layout* layout, const float* raw_sc
   p.scatter_out = scatter.ptrs;
   p.scatter_rows = scatter.rows;
   p.scatter_rank = scatter.rank;
+  p.scatter_shift = scatter.shift;
   const int Ho = head_reduce != TRIATTN_REDUCE_NONE ? 1 : Y.num_kv_heads;
   dim3 grid((unsigned)((t_pad + 255) / 256), (unsigned)Ho, (unsigned)Y.num_reqs);
   // (mean, 1/std) of the rows a CTA normalises with live in its shared memory

@@ -39,6 +39,10 @@ struct FinalizeParams {
   // stores over NVLink - at slot [scatter_rank][r % scatter_rows], so the exchange rides on the stores of this kernel.
   float* const* scatter_out;  // [ranks] device pointers to the ranks' [ranks, scatter_rows, t_pad] buffers, or null
   int scatter_rows, scatter_rank;
+  // Layers are visited starting at scatter_shift (and wrapping): each rank begins with the layers of a different
+  // owner, so that at no time all ranks store into the same GPU (its NVLink ingress would carry the whole exchange).
+  // 0 unless scatter_out is set: with a layer reduction the order of the layers is part of the result.
+  int scatter_shift;
 };
 
 // where the value of output row `row` (layer_reduce NONE), token t, goes
@@ -64,8 +68,10 @@ __global__ void __launch_bounds__(256) finalize_scores_kernel(const __grid_const
   int ho = blockIdx.y, l_lo = 0, l_hi = p.L;
   if (p.layer_reduce == TRIATTN_REDUCE_NONE) {
     l_lo = blockIdx.y / Ho;
-    l_hi = l_lo + 1;
     ho = blockIdx.y - l_lo * Ho;
+    l_lo += p.scatter_shift;
+    if (l_lo >= p.L) l_lo -= p.L;
+    l_hi = l_lo + 1;
   }
   const int h_begin = p.head_reduce != TRIATTN_REDUCE_NONE ? 0 : ho;
   const int h_end = p.head_reduce != TRIATTN_REDUCE_NONE ? p.Hkv : ho + 1;
@@ -175,6 +181,11 @@ __global__ void __launch_bounds__(256) finalize_scores_fast_kernel(const __grid_
   const bool first_chunk = p.first_chunk != 0;
   float acc = (LR != TRIATTN_REDUCE_NONE && !first_chunk) ? *out : 0.f;
 
+  // the layer visited at step l of the loops below (identity unless the scatter mode rotates the order)
+  auto at = [&](int l) {
+    const int m = l + p.scatter_shift;
+    return m >= p.L ? m - p.L : m;
+  };
   // z-normalise, reduce over the G query heads; then fold layer l into the accumulator / the output
   auto layer = [&](const float4 (&q)[NQ], int l) {
     const float2* msl = s_ms + (size_t)l * G;
@@ -205,15 +216,15 @@ __global__ void __launch_bounds__(256) finalize_scores_fast_kernel(const __grid_
 #pragma unroll
     for (int i = 0; i < kFinalizePrefetch; ++i)
 #pragma unroll
-      for (int n = 0; n < NQ; ++n) q[i][n] = r[(size_t)(l0 + i) * raw_layer_stride + n];
+      for (int n = 0; n < NQ; ++n) q[i][n] = r[(size_t)at(l0 + i) * raw_layer_stride + n];
 #pragma unroll
-    for (int i = 0; i < kFinalizePrefetch; ++i) layer(q[i], l0 + i);
+    for (int i = 0; i < kFinalizePrefetch; ++i) layer(q[i], at(l0 + i));
   }
   for (; l0 < p.L; ++l0) {
     float4 q[NQ];
 #pragma unroll
-    for (int n = 0; n < NQ; ++n) q[n] = r[(size_t)l0 * raw_layer_stride + n];
-    layer(q, l0);
+    for (int n = 0; n < NQ; ++n) q[n] = r[(size_t)at(l0) * raw_layer_stride + n];
+    layer(q, at(l0));
   }
   if (LR == TRIATTN_REDUCE_MEAN && p.last_chunk) acc = __fdiv_rn(acc, (float)p.l_total);
   if (LR != TRIATTN_REDUCE_NONE) *out = acc;
