@@ -593,7 +593,8 @@ def run_c2_legs(args, world, rank, local):
         res = engine.compress_layer_shared(view, stats, host_ids, seq, rs, bud, window=c["window"], timings=timings)
         e1.record()
         torch.cuda.synchronize()
-        return e0.elapsed_time(e1), timings["allreduce_ms"](), timings["allreduce_bytes"], res, timings["exchange"]
+        return (e0.elapsed_time(e1), timings["allreduce_ms"](), timings["allreduce_bytes"], res, timings["exchange"],
+                timings.get("multicast_bound"))
 
     for _ in range(2):
         shared_once()
@@ -612,7 +613,7 @@ def run_c2_legs(args, world, rank, local):
                            "keys_per_s_total": keys_per_gpu * world / (sh_ms * 1e-3),
                            "collective": runs[-1][4] if runs[-1][4].startswith("peer stores") else "NCCL " + runs[-1][4],
                            "allreduce_ms": ar_ms, "allreduce_share": ar_ms / sh_ms, "allreduce_bytes": runs[-1][2],
-                           "runs_ms": [round(r[0], 3) for r in runs], "runs_exchange_ms": [round(r[1], 3) for r in runs],
+                           "multicast_bound": runs[-1][5], "runs_ms": [round(r[0], 3) for r in runs], "runs_exchange_ms": [round(r[1], 3) for r in runs],
                            "rank_keep_sets_identical": same, "device_status": runs[-1][3].device_status}
     del caches, saver, view, runs, keep, lo_t, hi_t
     torch.cuda.empty_cache()

@@ -76,7 +76,8 @@ def _worker(rank: int, world: int, port: int, q, layers: int = 2):
         lens2 = [256, 512]
         res3 = engine.compress_layer_shared(view2, shard, [i[:16] for i in [ids[0]]] + [ids[1][:32]], lens2, starts,
                                             [200, 400], window=32)
-        print(f"rank {rank} layers {layers}: exchange = {timings['exchange']}", flush=True)
+        print(f"rank {rank} layers {layers}: exchange = {timings['exchange']}; multicast bound: "
+              f"{timings.get('multicast_bound')}", flush=True)
         q.put((rank, per_head, res2.keep.cpu(), res.device_status | res2.device_status | res3.device_status,
                [c.cpu() for c in local2], timings["exchange"], res3.keep.cpu()))
         dist.barrier()

@@ -312,6 +312,8 @@ def compress_layer_shared(
     if timings is not None:
         timings["allreduce_ms"] = lambda: ev[0].elapsed_time(ev[1]) + ev[2].elapsed_time(ev[3])
         timings["allreduce_bytes"] = L * B * t_pad * 4 + (int(keep.numel()) * 4 if scatter else 0)
+        if peers is not None:
+            timings["multicast_bound"] = peers.multicast_bound
         timings["exchange"] = (
             "peer stores of the fp32 score rows inside finalize (symmetric memory) + barrier + fold, all-gather of the "
             "keep indices" if peers is not None else

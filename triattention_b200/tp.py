@@ -113,6 +113,10 @@ class PeerRowExchange:
         if len(ptrs) != self.world or any(p == 0 for p in ptrs) or ptrs[self.rank] != self._flat.data_ptr():
             raise RuntimeError("symmetric memory did not return one mapped buffer per rank")
         self.ptrs = torch.tensor(ptrs, dtype=torch.int64, device=device)
+        try:  # informational: with the switch above no multicast object should be bound to the buffers
+            self.multicast_bound = int(getattr(self._handle, "multicast_ptr", 0) or 0) != 0
+        except Exception:
+            self.multicast_bound = None
         self._folded = torch.empty(self.capacity // self.world, dtype=torch.float32, device=device)
         self._token = torch.zeros(1, dtype=torch.float32, device=device)
 
