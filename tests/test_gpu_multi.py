@@ -1,8 +1,10 @@
 """Multi-GPU parity (needs >= 2 CUDA devices; skipped otherwise): tensor-parallel sharding by KV head.
 
 Two NCCL ranks each hold half of the KV heads.  Per-head mode: every rank's keep rows equal the rows the
-single-GPU run produces for those heads (no communication).  Layer-shared mode: one all-reduce(MAX) of the
-score rows and both ranks produce the keep set of the single-GPU run.  NVLS is disabled for the test.
+single-GPU run produces for those heads (no communication).  Layer-shared mode: the score rows cross the ranks -
+stored into the owner's slots by the finalize kernel when the layers divide over the ranks (symmetric memory; NCCL
+reduce-scatter where that is unavailable), one all-reduce(MAX) otherwise - and both ranks produce the keep set of
+the single-GPU run, over two consecutive steps.  NVLS is disabled for the test.
 """
 from __future__ import annotations
 

@@ -220,8 +220,9 @@ def compress_layer_shared(
     ``process_group=False`` skips the collective even when torch.distributed is initialised (a rank that holds
     all heads).  ``timings``, if given, receives ``allreduce_ms`` (a callable: CUDA-event time of the collectives,
     valid after a synchronize), ``allreduce_bytes`` and ``exchange`` (which form was used: when the layers divide
-    over the ranks, a reduce-scatter of the rows, a top-k on this rank's rows and an all-gather of the keep
-    indices replace the all-reduce).
+    over the ranks each rank finishes its own layers only - the finalize kernel stores every row into the owner's
+    receive slot over NVLink (``tp.PeerRowExchange``), or a NCCL reduce-scatter moves the rows - followed by a
+    top-k on this rank's rows and an all-gather of the keep indices; otherwise one all-reduce).
     Returns keep ``[L, B, keep_pitch]`` (as ``CompressResult.keep``).
     """
     from . import tp as _tp
