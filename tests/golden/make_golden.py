@@ -764,7 +764,16 @@ def gen_scheduler_side_cases(out: dict):
             im._ORIG_SCHED_UPDATE_FROM_OUTPUT = base_update
             return im._patched_scheduler_update_from_output(sched, so, mro)
 
+    def ref_alloc(manager, request, num_new_tokens, *args, base_allocate, **kwargs):
+        im._ORIG_KVCACHE_ALLOCATE_SLOTS = base_allocate
+        return im._patched_kv_cache_allocate_slots(manager, request, num_new_tokens, *args, **kwargs)
+
+    from triattention.vllm.runtime.signals import CompressionSignal
+
     res = {
+        "alloc": {c["name"]: sss.run_alloc_case(ref_alloc, c) for c in sss.ALLOC_CASES},
+        "boundary": sss.run_boundary_predicates(im._scheduler_output_has_compression_boundary,
+                                                im._batch_queue_has_pending_compression_boundary, CompressionSignal),
         "steps": {name: sss.run_scheduler_steps(_RefStepApi, over) for name, over in sss.STEP_CONFIGS.items()},
         "planner": sss.replay_planner(CompressionPlanner),
         "tracker": sss.replay_tracker(EffectiveCacheLenTracker()),

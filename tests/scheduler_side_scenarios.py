@@ -296,3 +296,55 @@ def run_scheduler_steps(api, cfg_over: dict) -> list:
             sched.requests.pop(r, None)
         out.append(rec)
     return out
+
+
+# ---------------------------------------------------------------------------------------------- slot allocation
+ALLOC_CASES = [
+    dict(name="no_reclaim", computed=500, attrs={}),
+    dict(name="offset_applied", computed=500, attrs={"_triattention_effective_kv_offset": 120}, kwargs={"x": 1}),
+    dict(name="offset_larger_than_progress", computed=100, attrs={"_triattention_effective_kv_offset": 120}),
+    dict(name="progress_zero", computed=0, attrs={"_triattention_effective_kv_offset": 120}),
+    dict(name="non_integer_progress", computed="12", attrs={"_triattention_effective_kv_offset": 5}),
+    dict(name="base_raises", computed=500, attrs={"_triattention_effective_kv_offset": 120}, raises=True),
+    dict(name="stale_marker_without_offset", computed=500, attrs={"_triattention_effective_num_computed_tokens": 300}),
+]
+
+
+def run_alloc_case(fn, case) -> dict:
+    """``fn(manager, request, num_new_tokens, *args, base_allocate, **kwargs)``"""
+    req = types.SimpleNamespace(num_computed_tokens=case["computed"], **case["attrs"])
+    seen = {}
+
+    def base(manager, request, num_new_tokens, *args, **kwargs):
+        seen.update(computed=request.num_computed_tokens, num_new=num_new_tokens, args=list(args), kwargs=dict(kwargs))
+        if case.get("raises"):
+            raise ValueError("pool exhausted")
+        return "blocks"
+
+    out = {"error": None, "returned": None}
+    try:
+        out["returned"] = fn("mgr", req, 7, "extra", base_allocate=base, **case.get("kwargs", {}))
+    except ValueError as exc:
+        out["error"] = str(exc)
+    out["seen"] = seen
+    out["computed_after"] = req.num_computed_tokens
+    out["marker_after"] = getattr(req, "_triattention_effective_num_computed_tokens", "absent")
+    return out
+
+
+def run_boundary_predicates(has_boundary, queue_pending, signal_cls) -> dict:
+    def sig(should):
+        return signal_cls(req_id="a", should_compress=should, reason="none", estimated_cache_len=1, step=1, kv_usage=None,
+                          protect_prefill=False, prefill_len=0, scheduled_tokens=1)
+
+    so = types.SimpleNamespace
+    marked, plain = so(_triattention_force_boundary_sync=True), so()
+    return {
+        "boundary": [has_boundary(so()), has_boundary(so(triattention_signals={})),
+                     has_boundary(so(triattention_signals={"a": sig(False)})),
+                     has_boundary(so(triattention_signals={"a": sig(False), "b": sig(True)})),
+                     has_boundary(so(triattention_signals=[sig(True)]))],
+        "queue": [queue_pending(None), queue_pending([]), queue_pending([("f", plain, "e")]),
+                  queue_pending([("f", plain), ("f", marked, "e")]), queue_pending([("f",), "junk", (1, marked)]),
+                  queue_pending(5)],
+    }

@@ -99,3 +99,19 @@ def test_scheduler_step_fixtures_are_not_vacuous():
     assert all(s["cap_after"] == 8192 for s in WANT["steps"]["small_pool_caps_the_step"])
     assert WANT["steps"]["pool_pressure_trigger"][1]["signals"]["b"]["reason"] == "kv_usage_threshold"
     assert WANT["steps"]["compression_disabled"][3]["signals"] == {}
+
+
+@pytest.mark.parametrize("case", sss.ALLOC_CASES, ids=lambda c: c["name"])
+def test_slot_allocation_sees_the_effective_length(case):
+    got = _plain(sss.run_alloc_case(scheduler_side.allocate_slots_with_effective_length, case))
+    assert got == WANT["alloc"][case["name"]]
+
+
+def test_boundary_predicates_follow_the_reference():
+    from triattention_b200.signals import CompressionSignal
+
+    got = sss.run_boundary_predicates(scheduler_side.scheduler_output_has_compression_boundary,
+                                      scheduler_side.batch_queue_has_pending_compression_boundary, CompressionSignal)
+    assert got == WANT["boundary"]
+    assert WANT["alloc"]["offset_applied"]["seen"] == {"args": ["extra"], "computed": 380, "num_new": 7,
+                                                       "kwargs": {"delay_cache_blocks": True, "x": 1}}

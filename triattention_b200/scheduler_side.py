@@ -482,3 +482,48 @@ def update_from_output_with_events(scheduler: Any, scheduler_output: Any, model_
         scheduler._length_threshold_cache.pop(req_id, None)
         scheduler._effective_len_tracker.remove_request(req_id)
     return outputs
+
+
+# ------------------------------------------------------------------------------------------------ slot allocation
+def allocate_slots_with_effective_length(manager: Any, request: Any, num_new_tokens: int, *args: Any,
+                                         base_allocate: Any, **kwargs: Any) -> Any:
+    """``base_allocate(manager, request, num_new_tokens, ...)`` - the engine's ``KVCacheManager.allocate_slots`` -
+    seeing the request's EFFECTIVE progress.
+
+    A request whose blocks were given back holds fewer tokens than its logical ``num_computed_tokens``; for the
+    duration of the call the counter is replaced by the effective value (and put back whatever happens), so that
+    the engine allocates for the cache as it is.  The compacted layout no longer matches the engine's prefix-hash
+    chain, so the call also asks it not to commit prefix-cache hashes (``delay_cache_blocks=True``).  Requests
+    without a reclaim go straight through (``runtime/integration_monkeypatch.py:243-284``)."""
+    prepare_request_effective_num_computed(request)  # waiting (preempted) requests are not refreshed by the schedule step
+    effective = resolve_request_effective_num_computed(request)
+    logical = getattr(request, "num_computed_tokens", None)
+    if effective is None or not isinstance(logical, int) or effective >= logical:
+        return base_allocate(manager, request, num_new_tokens, *args, **kwargs)
+    request.num_computed_tokens = int(effective)
+    try:
+        return base_allocate(manager, request, num_new_tokens, *args, **{**kwargs, "delay_cache_blocks": True})
+    finally:
+        request.num_computed_tokens = logical
+
+
+def scheduler_output_has_compression_boundary(scheduler_output: Any) -> bool:
+    """Does this step carry a trigger?  An asynchronous engine must not let its batch queue run ahead of such a step
+    (``runtime/integration_monkeypatch.py:287-291``)."""
+    signals = getattr(scheduler_output, "triattention_signals", None)
+    if not isinstance(signals, dict) or not signals:
+        return False
+    return any(bool(getattr(sig, "should_compress", False)) for sig in signals.values())
+
+
+def batch_queue_has_pending_compression_boundary(batch_queue: Any) -> bool:
+    """Is a step marked ``_triattention_force_boundary_sync`` still waiting in the engine's batch queue (entries
+    ``(future, scheduler_output, ...)``)?  (``runtime/integration_monkeypatch.py:294-307``)"""
+    if batch_queue is None:
+        return False
+    try:
+        entries = list(batch_queue)
+    except Exception:
+        return False
+    return any(isinstance(e, tuple) and len(e) >= 2 and bool(getattr(e[1], "_triattention_force_boundary_sync", False))
+               for e in entries)
