@@ -130,3 +130,34 @@ def test_step_profile_line(monkeypatch):
         "TRIATTN_PERF steps=2 trig_steps=1 override_steps=2 compress_calls=3 applied=1 skipped=1 errors=1 "
         "avg_ms(total=20.00 state=1.00 compress=2.00 reclaim=3.00 override_prep=4.00 base_exec=5.00) "
         "top_skip_reasons=under_budget:1 cudagraph_modes={'FULL': 1}")
+
+
+def test_worker_installs_the_proxy_with_the_first_signal(monkeypatch):
+    """The engine's runner is left alone until a scheduler output carries TriAttention signals; then the hook is
+    installed on it and it is wrapped (once), and the model directory is taken from the engine's model config."""
+    monkeypatch.delenv("TRIATTN_DEBUG_EARLY_INSTALL_PROXY", raising=False)
+    base = types.SimpleNamespace(requests={}, tag="engine runner")
+    worker = types.SimpleNamespace(model_runner=base, model_config=types.SimpleNamespace(model=" /models/qwen3 "))
+    cfg = TriAttentionRuntimeConfig(kv_budget=64, divide_length=16)
+    worker_runner.prepare_worker(worker, cfg)
+    assert worker.model_runner is base and worker._triattention_runner_proxy_installed is False
+    assert str(cfg.model_path) == "/models/qwen3"
+    calls = []
+    run = lambda w, so: calls.append(type(w.model_runner).__name__) or "ran"
+    assert worker_runner.worker_execute_model(worker, types.SimpleNamespace(triattention_signals={}), run) == "ran"
+    assert worker.model_runner is base
+    installed = []
+    monkeypatch.setattr("triattention_b200.hook.install_runner_compression_hook",
+                        lambda base_runner, config: installed.append((base_runner, config)))
+    so = types.SimpleNamespace(triattention_signals={"a": object()})
+    worker_runner.worker_execute_model(worker, so, run)
+    worker_runner.worker_execute_model(worker, so, run)
+    assert isinstance(worker.model_runner, worker_runner.TriAttentionModelRunner)
+    assert worker.model_runner.tag == "engine runner"            # everything else passes through to the engine's runner
+    assert installed == [(base, cfg)] and worker._triattention_runner_proxy_installed is True
+    assert calls == ["SimpleNamespace", "TriAttentionModelRunner", "TriAttentionModelRunner"]
+    # eager installation for debugging
+    monkeypatch.setenv("TRIATTN_DEBUG_EARLY_INSTALL_PROXY", "1")
+    other = types.SimpleNamespace(model_runner=types.SimpleNamespace(requests={}), model_config=None)
+    worker_runner.prepare_worker(other, TriAttentionRuntimeConfig(kv_budget=64, divide_length=16, model_path="/m"))
+    assert isinstance(other.model_runner, worker_runner.TriAttentionModelRunner)

@@ -387,3 +387,57 @@ class TriAttentionModelRunner:
 
     def snapshot_states(self) -> dict:
         return self.state_store.snapshot()
+
+
+# ------------------------------------------------------------------------------------------------ worker wiring
+# What the reference's worker subclass adds around the engine worker (runtime/worker.py:18-84): the engine's own
+# model runner stays untouched through warm-up, graph capture and every step without a TriAttention signal; the
+# first step that carries one installs the hook on it and wraps it in the proxy.
+def backfill_model_path(worker: Any, config: TriAttentionRuntimeConfig) -> None:
+    """The model directory (where the rotary configuration lives) from the engine's model config when the
+    environment did not name one."""
+    if config.model_path is not None:
+        return
+    path = getattr(getattr(worker, "model_config", None), "model", None)
+    if isinstance(path, str) and path.strip():
+        from pathlib import Path
+        config.model_path = Path(path.strip())
+
+
+def prepare_worker(worker: Any, config: Optional[TriAttentionRuntimeConfig] = None) -> None:
+    """After the engine's ``init_device``: remember the configuration; install at once only when
+    ``TRIATTN_DEBUG_EARLY_INSTALL_PROXY=1``."""
+    if isinstance(getattr(worker, "model_runner", None), TriAttentionModelRunner):
+        return
+    worker._triattention_runtime_config = config or TriAttentionRuntimeConfig.from_env()
+    backfill_model_path(worker, worker._triattention_runtime_config)
+    worker._triattention_runner_proxy_installed = False
+    if os.environ.get("TRIATTN_DEBUG_EARLY_INSTALL_PROXY", "0") == "1":
+        ensure_runner_proxy(worker)
+
+
+def ensure_runner_proxy(worker: Any, install_hook: Optional[Callable[..., None]] = None, **proxy_kwargs: Any) -> None:
+    """Install the compression hook on ``worker.model_runner`` and replace it by the proxy (once)."""
+    if getattr(worker, "_triattention_runner_proxy_installed", False):
+        return
+    if isinstance(worker.model_runner, TriAttentionModelRunner):
+        worker._triattention_runner_proxy_installed = True
+        return
+    config = getattr(worker, "_triattention_runtime_config", None) or TriAttentionRuntimeConfig.from_env()
+    backfill_model_path(worker, config)
+    base_runner = worker.model_runner
+    if install_hook is None:
+        from .hook import install_runner_compression_hook as install_hook
+    install_hook(base_runner=base_runner, config=config)
+    worker.model_runner = TriAttentionModelRunner(base_runner, config, **proxy_kwargs)
+    worker._triattention_runner_proxy_installed = True
+    _log.info("TriAttention runner proxy installed: budget=%d divide_length=%d stats_path=%s model_path=%s "
+              "protect_prefill=%s window_size=%s", config.kv_budget, config.divide_length, config.sparse_stats_path,
+              config.model_path, config.protect_prefill, config.window_size)
+
+
+def worker_execute_model(worker: Any, scheduler_output: Any, base_execute_model: Callable[[Any, Any], Any]) -> Any:
+    """The worker's ``execute_model``: the proxy goes in with the first scheduler output that carries signals."""
+    if getattr(scheduler_output, "triattention_signals", None):
+        ensure_runner_proxy(worker)
+    return base_execute_model(worker, scheduler_output)
